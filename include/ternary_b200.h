@@ -1,0 +1,207 @@
+/*
+ * ternary_b200 — C ABI of the B200 (sm_100a) BitNet b1.58 ternary linear path.
+ *
+ * Drop-in boundary for the NSOS runtime's packed BitLinear path.  Every entry point
+ *   - is extern "C", takes plain pointers and sizes, and returns an int status
+ *     (0 = ok, negative = rejected by validation, nothing was launched);
+ *   - never throws, never allocates device memory, never synchronises unless its comment
+ *     says so; all work is enqueued on the caller's stream (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream);
+ *   - borrows every pointer: the owner keeps buffers alive until the stream has drained.
+ * Device-side waits are bounded; a kernel that gives up records a code readable with
+ * tbl_device_status().
+ *
+ * Numeric contract (identical to the reference's CPU packed path):
+ *   weight_scale = float(sum_i double|w_i| / n) + 1e-8f, sequential sum;
+ *   t = w/(weight_scale+1e-8f) > 0.5 ? +1 : (< -0.5 ? -1 : 0);
+ *   2-bit code t+1 at bits 2*(i%16) of word i/16, i = n*K + k;
+ *   per row: m = max|x|, q = round_half_even(x * (qmax/(m+1e-8f))), act_scale = (m+1e-8f)/qmax;
+ *   acc = sum_k q*t (int32);  y = float(acc) * (act_scale*weight_scale) [* magnitude[n]] [+ bias[n]].
+ */
+#ifndef TERNARY_B200_H
+#define TERNARY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define TBL_OK 0
+#define TBL_ERR_INVALID_ARG (-1)   /* null pointer, non-positive size, bad flag          */
+#define TBL_ERR_SHAPE (-2)         /* K % 16 != 0, M*N > INT_MAX, M out of a kernel's range */
+#define TBL_ERR_OVERFLOW (-3)      /* K > INT_MAX/254: int32 accumulation could overflow  */
+#define TBL_ERR_SCALE (-4)         /* weight_scale not finite or not > 0                  */
+#define TBL_ERR_BITS (-5)          /* activation bits outside [2,8]                       */
+#define TBL_ERR_ALIGNMENT (-6)     /* a device pointer is not 16-byte aligned             */
+#define TBL_ERR_WORKSPACE (-7)     /* workspace too small                                 */
+#define TBL_ERR_CODE (-8)          /* packed words contain the illegal code 0b11          */
+#define TBL_ERR_CUDA (-9)          /* a CUDA runtime call or launch failed                */
+#define TBL_ERR_UNSUPPORTED (-10)  /* descriptor mode this library does not implement     */
+
+const char* tbl_status_string(int status);
+
+/* Library/ABI version (bumped when a signature changes). */
+int tbl_abi_version(void);
+
+/* ---- flags ------------------------------------------------------------------------- */
+/* rms_mode: input RMSNorm applied before quantisation (eps 1e-6).
+ *   0 none; 1 parallel reduction (fast, sum order differs from the CPU reference by
+ *   rounding); 2 reference order (sequential fp32 sum, bit-identical to Tensor::rmsnorm). */
+#define TBL_RMS_NONE 0
+#define TBL_RMS_FAST 1
+#define TBL_RMS_REFERENCE_ORDER 2
+/* tie rule for the quantiser: 0 = round-half-to-even (the default x86-64 reference build),
+ * 1 = round-half-away-from-zero (the reference's scalar build and MoE decode kernel). */
+#define TBL_TIE_EVEN 0
+#define TBL_TIE_AWAY 1
+
+/* ---- offline packer (host) ---------------------------------------------------------- */
+
+/* Number of uint32 words of the canonical packing of an [N,K] matrix.
+ * Replaces: size computation in BitLinear::pack_weights, OXN/nsos/src/bitlinear.cpp:162-166. */
+int64_t tbl_packed_words(int N, int K);
+
+/* Absmean-ternarises w_host (fp32 [N,K], row-major) and writes the canonical 2-bit words
+ * and the per-matrix scale.  Host-only, sequential double sum (bit-exact with the reference).
+ * Replaces: BitLinear::pack_weights (OXN/nsos/src/bitlinear.cpp:152-193), tensor_abs_mean
+ * (OXN/nsos/src/tensor.cpp:2097-2102), BitLinear::quantize_weights
+ * (OXN/nsos/src/bitlinear.cpp:1359-1379), BitNetAdapter::pack_weights_microsoft_style
+ * (OXN/nsos/src/bitnet_adapter.cpp:570-588). */
+int tbl_pack_weights(const float* w_host, int N, int K, uint32_t* words_host, float* weight_scale);
+
+/* Decodes canonical words to int8 {-1,0,+1} [N,K] on the host (code 3 decodes to 0).
+ * Replaces: BitNetAdapter::unpack_weights_microsoft_style_to_i8,
+ * OXN/nsos/src/bitnet_adapter.cpp:590-606. */
+int tbl_unpack_weights_i8(const uint32_t* words_host, int N, int K, int8_t* t_host);
+
+/* Validates an imported packed state: sizes, finite positive scale, no code 0b11, finite
+ * magnitude/bias (either may be NULL).
+ * Replaces: the checks of BitLinear::prepare_packed_state, OXN/nsos/src/bitlinear.cpp:834-900. */
+int tbl_validate_packed(const uint32_t* words_host, int64_t n_words, int N, int K,
+                        float weight_scale, const float* magnitude_host, const float* bias_host);
+
+/* ---- device: weight expansion for the tensor-core GEMM ------------------------------- */
+
+/* Expands canonical words (device) into int8 {-1,0,+1} [N,K] row-major (device), the K-major
+ * operand the tcgen05 GEMM reads through TMA.  Mirrors the unpacked copy the reference keeps
+ * beside its packed words (BitLinear::unpacked_weights_i8, OXN/nsos/src/bitlinear.cpp:186-188). */
+int tbl_expand_weights_i8(const uint32_t* words_dev, int N, int K, int8_t* w_i8_dev, void* stream);
+
+/* ---- device: activation quantiser --------------------------------------------------- */
+
+/* Per-row absmax quantiser: x fp32 [M,K] -> q int8 [M,K] + act_scales fp32 [M]
+ * (+ optional q_sums int32 [M] = sum_k q, NULL to skip).  row_index (device int32 [M], may be
+ * NULL) gathers input rows: output row i is computed from x row row_index[i].
+ * Replaces: BitLinear::quantize_activations_bitnet (OXN/nsos/src/bitlinear.cpp:240-291),
+ * launch_quantize_activations_bitnet_kernel (OXN/nsos/src/cuda/bitnet_kernels.cu:70-130,296-304)
+ * and, with rms_mode != 0, the Tensor::rmsnorm(1e-6) in BitLinear::forward
+ * (OXN/nsos/src/bitlinear.cpp:460-463). */
+int tbl_quantize_rows(const float* x_dev, const int32_t* row_index_dev, int M, int K, int bits,
+                      int rms_mode, int tie_mode, int8_t* q_dev, float* act_scales_dev,
+                      int32_t* q_sums_dev, void* stream);
+
+/* ---- device: GEMV / GEMM on already-quantised activations ----------------------------- */
+
+/* Bytes of scratch tbl_gemv needs for (M,K). */
+size_t tbl_gemv_workspace_bytes(int M, int K);
+
+/* Decode GEMV, 1 <= M <= 64: y[M,N] = epilogue(q[M,K] x ternary[N,K]^T).
+ * acc_debug (device int32 [M,N], may be NULL) receives the raw accumulators.
+ * Replaces: launch_bitnet_gemv_scaled (OXN/nsos/src/cuda/kernels.cu:1027-1066,1110-1130) and,
+ * for 1 < M <= 64, launch_bitnet_gemm + launch_bitnet_apply_act_scales_kernel
+ * (OXN/nsos/src/cuda/kernels.cu:966-1022, OXN/nsos/src/cuda/bitnet_kernels.cu:140-149). */
+int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* words_dev,
+             float weight_scale, const float* magnitude_dev, const float* bias_dev,
+             int M, int K, int N, float* y_dev, int32_t* acc_debug_dev,
+             void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* Prefill GEMM on tcgen05 int8 tensor cores (any M >= 1, intended for M >= 128):
+ * y[M,N] = epilogue(q[M,K] x w_i8[N,K]^T), accumulators in tensor memory.
+ * w_i8_dev is the output of tbl_expand_weights_i8.  Needs K % 16 == 0.
+ * Replaces: launch_bitnet_gemm + launch_bitnet_apply_act_scales_kernel + the magnitude/bias
+ * tensor ops of bitnet_gemm_158bit_gpu (OXN/nsos/src/bitnet_gpu_dispatch.cpp:157-171). */
+int tbl_gemm(const int8_t* q_dev, const float* act_scales_dev, const int8_t* w_i8_dev,
+             float weight_scale, const float* magnitude_dev, const float* bias_dev,
+             int M, int K, int N, float* y_dev, int32_t* acc_debug_dev, void* stream);
+
+/* ---- device: the fused layer forward -------------------------------------------------- */
+
+/* Bytes of scratch tbl_linear_forward needs for (M,K,N). */
+size_t tbl_linear_workspace_bytes(int M, int K, int N);
+
+/* x fp32 [M,K] (device) -> y fp32 [M,N] (device): [RMSNorm] -> quantise -> ternary GEMV
+ * (M <= 64, packed words) or tcgen05 GEMM (M > 64 when w_i8_dev != NULL) -> two-scale
+ * epilogue [* magnitude] [+ bias].  w_i8_dev may be NULL: then every M runs on the packed words.
+ * Replaces: bitnet_gemm_158bit_gpu (OXN/nsos/include/bitnet_gpu_dispatch.h:46-51,
+ * OXN/nsos/src/bitnet_gpu_dispatch.cpp:65-174) and the packed branch of BitLinear::forward
+ * (OXN/nsos/src/bitlinear.cpp:606-659,690-741). */
+int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const int8_t* w_i8_dev,
+                       float weight_scale, int M, int K, int N, int bits, int rms_mode,
+                       const float* magnitude_dev, const float* bias_dev, float* y_dev,
+                       void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* ---- grouped variant ------------------------------------------------------------------- */
+
+/* Borrowed descriptor of one linear; field-for-field the reference's GpuLinearView
+ * (OXN/nsos/include/gpu_linear_view.h:8-26).  Only the packed mode (packed != NULL,
+ * weight == NULL, activation_bits in [2,8]) is implemented; others -> TBL_ERR_UNSUPPORTED. */
+typedef struct tbl_linear_view {
+    const float* weight;
+    const uint32_t* packed;
+    const float* magnitude;
+    const float* bias;
+    int inputs;
+    int outputs;
+    int activation_bits;
+    int rms_input;
+    float weight_scale;
+} tbl_linear_view;
+
+#define TBL_MAX_GROUPS 32
+
+/* Bytes of scratch for tbl_grouped_forward with `groups` views of at most max_inputs inputs. */
+size_t tbl_grouped_workspace_bytes(int groups, int max_inputs);
+
+/* `groups` independent linears sharing ONE input row (QKV, Mamba x/z/B/C/dt): views is a
+ * HOST array; view g reads input_dev[0..inputs) and writes output_dev[g*output_stride ..].
+ * All views must share inputs, activation_bits and rms_input so the row is quantised once.
+ * Replaces: launch_grouped_decode_projections (OXN/nsos/src/cuda/moe_kernels.cu:779-784) and
+ * GpuProjectionGroup::forward (OXN/nsos/src/gpu_projection_group.cpp:12-52). */
+int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const float* input_dev,
+                        float* output_dev, int output_stride, int rms_mode,
+                        void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch for tbl_moe_forward. */
+size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row);
+
+/* MoE expert FFN: out[r,:] = sum_e routing[r,e] * down_e(relu(up_e(x_r))^2), experts summed in
+ * index order, experts with routing weight 0 skipped (their weights are never read).
+ * views_host holds 2*experts views: [0,E) the up linears (dim -> hidden_dim), [E,2E) the down
+ * linears (hidden_dim -> dim).  routing_dev fp32 [rows,experts].  At most max_routes_per_row
+ * non-zero routing weights per row (else the device status reports TBL_DEV_ROUTE_OVERFLOW).
+ * Replaces: launch_moe_sparse_decode (OXN/nsos/src/cuda/moe_kernels.cu:786-795) and the CPU
+ * composition in JambaBlock::forward_moe (OXN/nsos/src/jamba.cpp:3865-3972). */
+int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev, const float* x_dev,
+                    int rows, int dim, int hidden_dim, int experts, int max_routes_per_row,
+                    int rms_mode, int tie_mode, float* out_dev,
+                    void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* ---- device status ---------------------------------------------------------------------- */
+#define TBL_DEV_OK 0
+#define TBL_DEV_WAIT_TIMEOUT 1     /* a bounded mbarrier / TMA wait gave up                */
+#define TBL_DEV_ROUTE_OVERFLOW 2   /* a row had more routes than max_routes_per_row        */
+
+/* Synchronises `stream`, returns the sticky device status word of the current device and
+ * clears it.  Negative on a CUDA error. */
+int tbl_device_status(void* stream);
+
+/* Number of kernels this library has launched in this process (all streams). */
+uint64_t tbl_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TERNARY_B200_H */

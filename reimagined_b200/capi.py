@@ -1,0 +1,84 @@
+"""ctypes bindings of every symbol declared in include/ternary_b200.h.
+
+Pointers are passed as integers (``tensor.data_ptr()`` for device memory, ``array.ctypes.data`` for
+host memory); nothing here copies, allocates or falls back to a CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libternary_b200.so")
+
+
+class TernaryB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().tbl_status_string(status).decode()
+        super().__init__(f"{where}: status {status} ({msg})")
+
+
+class LinearView(C.Structure):
+    """Field-for-field tbl_linear_view (the reference's GpuLinearView)."""
+
+    _fields_ = [("weight", C.c_void_p), ("packed", C.c_void_p), ("magnitude", C.c_void_p),
+                ("bias", C.c_void_p), ("inputs", C.c_int), ("outputs", C.c_int),
+                ("activation_bits", C.c_int), ("rms_input", C.c_int), ("weight_scale", C.c_float)]
+
+
+_vp = C.c_void_p
+_SIGNATURES = {
+    # name: (restype, argtypes)
+    "tbl_status_string": (C.c_char_p, [C.c_int]),
+    "tbl_abi_version": (C.c_int, []),
+    "tbl_packed_words": (C.c_int64, [C.c_int, C.c_int]),
+    "tbl_pack_weights": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
+    "tbl_unpack_weights_i8": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
+    "tbl_validate_packed": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_float, _vp, _vp]),
+    "tbl_expand_weights_i8": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
+    "tbl_quantize_rows": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
+    "tbl_gemv_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "tbl_gemv": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp,
+                           C.c_size_t, _vp]),
+    "tbl_gemm": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
+    "tbl_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "tbl_linear_forward": (C.c_int, [_vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                     _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "tbl_grouped_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "tbl_grouped_forward": (C.c_int, [C.POINTER(LinearView), C.c_int, _vp, _vp, C.c_int, C.c_int, _vp,
+                                      C.c_size_t, _vp]),
+    "tbl_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tbl_moe_forward": (C.c_int, [C.POINTER(LinearView), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int,
+                                  C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_size_t, _vp]),
+    "tbl_device_status": (C.c_int, [_vp]),
+    "tbl_launch_count": (C.c_uint64, []),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libternary_b200.so (once).  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m reimagined_b200.build` "
+                "(the ternary linear path has no CPU or PyTorch fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise TernaryB200Error(status, where)

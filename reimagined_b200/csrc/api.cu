@@ -1,0 +1,413 @@
+// extern "C" entry points: validation, workspace carving and kernel selection.  No allocation,
+// no synchronisation (except tbl_device_status), no exceptions across the boundary.
+#include <atomic>
+#include <climits>
+#include <cmath>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+
+static std::atomic<uint64_t> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? TBL_OK : TBL_ERR_CUDA; }
+
+// Shape rules shared by every device entry point; they are the reference's own
+// (bitnet_gemm_158bit_gpu: positive sizes, K % 16 == 0, K <= INT_MAX/254, M*N <= INT_MAX,
+// finite positive scale, bits in [2,8]).
+int check_problem(int M, int K, int N, float weight_scale, int bits) {
+    if (M <= 0 || K <= 0 || N <= 0) return TBL_ERR_INVALID_ARG;
+    if (bits < 2 || bits > 8) return TBL_ERR_BITS;
+    if (K > INT_MAX / 254) return TBL_ERR_OVERFLOW;
+    if (!std::isfinite(weight_scale) || weight_scale <= 0.0f) return TBL_ERR_SCALE;
+    if (K % 16 != 0) return TBL_ERR_SHAPE;
+    if (static_cast<int64_t>(M) * N > INT_MAX) return TBL_ERR_SHAPE;
+    return TBL_OK;
+}
+
+struct Workspace {
+    int8_t* q;
+    int8_t* qp;
+    float* act_scales;
+    int32_t* q_sums;
+    float* inv_norm;
+    size_t bytes;
+};
+
+Workspace carve(void* base, int M, int K) {
+    Workspace w;
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    const size_t mk = round_up(static_cast<size_t>(M) * K, 256);
+    w.q = reinterpret_cast<int8_t*>(p + off); off += mk;
+    w.qp = reinterpret_cast<int8_t*>(p + off); off += mk;
+    const size_t vec = round_up(static_cast<size_t>(M) * 4, 256);
+    w.act_scales = reinterpret_cast<float*>(p + off); off += vec;
+    w.q_sums = reinterpret_cast<int32_t*>(p + off); off += vec;
+    w.inv_norm = reinterpret_cast<float*>(p + off); off += vec;
+    w.bytes = off;
+    return w;
+}
+
+// GEMV on already-quantised activations for any M (the tensor-core kernel walks M in tiles of 64).
+int run_gemv(const int8_t* q, const int8_t* qp, const float* act_scales, const int32_t* q_sums,
+             const uint32_t* words, float weight_scale, const float* magnitude, const float* bias, int M,
+             int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream) {
+    if (M <= 4 && gemv_small_supported(M, K, N) && aligned16(words) && aligned16(q)) {
+        GemvSmallArgs a{};
+        a.q = q; a.act_scales = act_scales; a.words = words; a.magnitude = magnitude; a.bias = bias;
+        a.y = y; a.acc_debug = acc_debug; a.weight_scale = weight_scale; a.q_max = 127.0f;
+        a.M = M; a.K = K; a.N = N; a.rms_mode = TBL_RMS_NONE;
+        return cuda_status(launch_gemv_small(a, stream));
+    }
+    if (qp && gemv_mma_supported(K) && aligned16(words)) {
+        MmaProblem pr{};
+        pr.words = words; pr.qp = qp; pr.act_scales = act_scales; pr.q_sums = q_sums;
+        pr.magnitude = magnitude; pr.bias = bias; pr.y = y; pr.acc_debug = acc_debug;
+        pr.weight_scale = weight_scale; pr.rows = M; pr.N = N; pr.K = K; pr.ldy = N;
+        return cuda_status(launch_gemv_mma(&pr, 1, stream));
+    }
+    return cuda_status(launch_gemv_generic(q, act_scales, words, weight_scale, magnitude, bias, M, K, N, y,
+                                           acc_debug, 0, nullptr, nullptr, stream));
+}
+
+}  // namespace
+}  // namespace tbl
+
+using namespace tbl;
+
+extern "C" {
+
+const char* tbl_status_string(int status) {
+    switch (status) {
+        case TBL_OK: return "ok";
+        case TBL_ERR_INVALID_ARG: return "invalid argument (null pointer, non-positive size or bad flag)";
+        case TBL_ERR_SHAPE: return "unsupported shape (K must be a multiple of 16, M*N <= INT_MAX, M within the kernel's range)";
+        case TBL_ERR_OVERFLOW: return "K too large: int32 accumulation could overflow";
+        case TBL_ERR_SCALE: return "weight_scale must be finite and positive";
+        case TBL_ERR_BITS: return "activation bits must be in [2,8]";
+        case TBL_ERR_ALIGNMENT: return "device pointer must be 16-byte aligned";
+        case TBL_ERR_WORKSPACE: return "workspace too small";
+        case TBL_ERR_CODE: return "packed words contain the reserved code 0b11";
+        case TBL_ERR_CUDA: return "CUDA runtime error";
+        case TBL_ERR_UNSUPPORTED: return "descriptor mode not implemented";
+        default: return "unknown status";
+    }
+}
+
+int tbl_abi_version(void) { return 1; }
+
+uint64_t tbl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int tbl_device_status(void* stream) {
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    int status = 0;
+    if (read_and_clear_device_status(&status) != 0) return TBL_ERR_CUDA;
+    return status;
+}
+
+int tbl_expand_weights_i8(const uint32_t* words_dev, int N, int K, int8_t* w_i8_dev, void* stream) {
+    if (!words_dev || !w_i8_dev || N <= 0 || K <= 0) return TBL_ERR_INVALID_ARG;
+    if (!aligned16(words_dev) || !aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
+    return cuda_status(launch_expand_i8(words_dev, N, K, w_i8_dev, static_cast<cudaStream_t>(stream)));
+}
+
+int tbl_quantize_rows(const float* x_dev, const int32_t* row_index_dev, int M, int K, int bits, int rms_mode,
+                      int tie_mode, int8_t* q_dev, float* act_scales_dev, int32_t* q_sums_dev, void* stream) {
+    if (!x_dev || !q_dev || !act_scales_dev || M <= 0 || K <= 0) return TBL_ERR_INVALID_ARG;
+    if (bits < 2 || bits > 8) return TBL_ERR_BITS;
+    if (rms_mode != TBL_RMS_NONE && rms_mode != TBL_RMS_FAST) {
+        // the reference-order factor needs one float of scratch per row; this entry point has no
+        // workspace argument, so only the layer-level calls offer that mode
+        return TBL_ERR_INVALID_ARG;
+    }
+    if (tie_mode != TBL_TIE_EVEN && tie_mode != TBL_TIE_AWAY) return TBL_ERR_INVALID_ARG;
+    return cuda_status(launch_quantize_rows(x_dev, row_index_dev, M, K, bits, rms_mode, tie_mode, q_dev,
+                                            nullptr, act_scales_dev, q_sums_dev, nullptr, nullptr,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
+size_t tbl_gemv_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0) return 0;
+    return round_up(static_cast<size_t>(M) * K, 256) + round_up(static_cast<size_t>(M) * 4, 256);
+}
+
+int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* words_dev, float weight_scale,
+             const float* magnitude_dev, const float* bias_dev, int M, int K, int N, float* y_dev,
+             int32_t* acc_debug_dev, void* workspace_dev, size_t workspace_bytes, void* stream) {
+    if (!q_dev || !act_scales_dev || !words_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+    const int rc = check_problem(M, K, N, weight_scale, 8);
+    if (rc != TBL_OK) return rc;
+    if (M > 64) return TBL_ERR_SHAPE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int8_t* qp = nullptr;
+    int32_t* q_sums = nullptr;
+    const bool small = M <= 4 && gemv_small_supported(M, K, N) && aligned16(words_dev) && aligned16(q_dev);
+    if (!small && gemv_mma_supported(K) && aligned16(words_dev) && aligned16(q_dev)) {
+        if (!workspace_dev || workspace_bytes < tbl_gemv_workspace_bytes(M, K)) return TBL_ERR_WORKSPACE;
+        if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
+        qp = static_cast<int8_t*>(workspace_dev);
+        q_sums = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace_dev) +
+                                            round_up(static_cast<size_t>(M) * K, 256));
+        const cudaError_t e = launch_permute_q(q_dev, M, K, qp, q_sums, st);
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+    }
+    return run_gemv(q_dev, qp, act_scales_dev, q_sums, words_dev, weight_scale, magnitude_dev, bias_dev, M, K,
+                    N, y_dev, acc_debug_dev, st);
+}
+
+int tbl_gemm(const int8_t* q_dev, const float* act_scales_dev, const int8_t* w_i8_dev, float weight_scale,
+             const float* magnitude_dev, const float* bias_dev, int M, int K, int N, float* y_dev,
+             int32_t* acc_debug_dev, void* stream) {
+    if (!q_dev || !act_scales_dev || !w_i8_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+    const int rc = check_problem(M, K, N, weight_scale, 8);
+    if (rc != TBL_OK) return rc;
+    if (!aligned16(q_dev) || !aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
+    return cuda_status(launch_gemm_tcgen05(q_dev, act_scales_dev, w_i8_dev, weight_scale, magnitude_dev,
+                                           bias_dev, M, K, N, y_dev, acc_debug_dev,
+                                           static_cast<cudaStream_t>(stream)));
+}
+
+size_t tbl_linear_workspace_bytes(int M, int K, int N) {
+    (void)N;
+    if (M <= 0 || K <= 0) return 0;
+    return carve(nullptr, M, K).bytes;
+}
+
+int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const int8_t* w_i8_dev,
+                       float weight_scale, int M, int K, int N, int bits, int rms_mode,
+                       const float* magnitude_dev, const float* bias_dev, float* y_dev, void* workspace_dev,
+                       size_t workspace_bytes, void* stream) {
+    if (!x_dev || !words_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+    const int rc = check_problem(M, K, N, weight_scale, bits);
+    if (rc != TBL_OK) return rc;
+    if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
+    if (!aligned16(x_dev)) return TBL_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // M <= 4: one kernel, the quantiser runs in the GEMV's prologue
+    if (M <= 4 && rms_mode != TBL_RMS_REFERENCE_ORDER && aligned16(words_dev) &&
+        gemv_small_supported(M, K, N)) {
+        GemvSmallArgs a{};
+        a.x = x_dev; a.words = words_dev; a.magnitude = magnitude_dev; a.bias = bias_dev; a.y = y_dev;
+        a.weight_scale = weight_scale; a.q_max = qmax_for_bits(bits);
+        a.M = M; a.K = K; a.N = N; a.rms_mode = rms_mode;
+        return cuda_status(launch_gemv_small(a, st));
+    }
+
+    if (!workspace_dev || workspace_bytes < tbl_linear_workspace_bytes(M, K, N)) return TBL_ERR_WORKSPACE;
+    if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
+    const Workspace w = carve(workspace_dev, M, K);
+    const bool use_gemm = w_i8_dev != nullptr && M > 64;
+    const bool want_qp = !use_gemm && gemv_mma_supported(K);
+    cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, w.q,
+                                         want_qp ? w.qp : nullptr, w.act_scales, w.q_sums, w.inv_norm, nullptr, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    if (use_gemm) {
+        if (!aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
+        return cuda_status(launch_gemm_tcgen05(w.q, w.act_scales, w_i8_dev, weight_scale, magnitude_dev,
+                                               bias_dev, M, K, N, y_dev, nullptr, st));
+    }
+    return run_gemv(w.q, want_qp ? w.qp : nullptr, w.act_scales, w.q_sums, words_dev, weight_scale,
+                    magnitude_dev, bias_dev, M, K, N, y_dev, nullptr, st);
+}
+
+}  // extern "C"
+
+// ---- grouped variant ---------------------------------------------------------------------------
+
+namespace {
+
+int check_view(const tbl_linear_view& v) {
+    if (v.weight != nullptr || v.packed == nullptr) return TBL_ERR_UNSUPPORTED;
+    if (v.activation_bits == 0) return TBL_ERR_UNSUPPORTED;
+    const int rc = check_problem(1, v.inputs, v.outputs, v.weight_scale, v.activation_bits);
+    if (rc != TBL_OK) return rc;
+    if (!aligned16(v.packed)) return TBL_ERR_ALIGNMENT;
+    return TBL_OK;
+}
+
+struct MoeWorkspace {
+    MoeLists lists;
+    int8_t* q1;          // [capacity, dim]   quantised expert inputs (interleaved or row-major)
+    int8_t* q2;          // [capacity, hidden]
+    float* scales1; int32_t* sums1; float* inv1;
+    float* scales2; int32_t* sums2; float* inv2;
+    float* hidden;       // [capacity, hidden] fp32
+    float* contrib;      // [capacity, dim] fp32
+    size_t bytes;
+};
+
+MoeWorkspace carve_moe(void* base, int rows, int dim, int hidden_dim, int experts, int capacity) {
+    MoeWorkspace w;
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { uint8_t* r = p + off; off += round_up(bytes, 256); return r; };
+    w.lists.counts = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * experts));
+    w.lists.offsets = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * experts));
+    w.lists.total = reinterpret_cast<int32_t*>(take(sizeof(int32_t)));
+    w.lists.slot_row = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * capacity));
+    w.lists.slot_of = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * static_cast<size_t>(rows) * experts));
+    w.q1 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * dim));
+    w.q2 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * hidden_dim));
+    w.scales1 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
+    w.sums1 = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * capacity));
+    w.inv1 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
+    w.scales2 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
+    w.sums2 = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * capacity));
+    w.inv2 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
+    w.hidden = reinterpret_cast<float*>(take(sizeof(float) * static_cast<size_t>(capacity) * hidden_dim));
+    w.contrib = reinterpret_cast<float*>(take(sizeof(float) * static_cast<size_t>(capacity) * dim));
+    w.bytes = off;
+    return w;
+}
+
+// One grouped linear stage of the MoE: problem e multiplies the rows of expert e's slot range.
+int run_expert_stage(const tbl_linear_view* views, int experts, const int8_t* q, const float* scales,
+                     const int32_t* sums, const MoeLists& lists, int capacity, float* y, int squared_relu,
+                     cudaStream_t st) {
+    const int K = views[0].inputs, N = views[0].outputs;
+    if (gemv_mma_supported(K)) {
+        MmaProblem pr[TBL_MAX_GROUPS];
+        for (int e = 0; e < experts; ++e) {
+            pr[e] = MmaProblem{};
+            pr[e].words = views[e].packed; pr[e].qp = q; pr[e].act_scales = scales; pr[e].q_sums = sums;
+            pr[e].magnitude = views[e].magnitude; pr[e].bias = views[e].bias; pr[e].y = y;
+            pr[e].rows_dev = lists.counts + e; pr[e].offset_dev = lists.offsets + e;
+            pr[e].weight_scale = views[e].weight_scale; pr[e].rows = capacity;
+            pr[e].N = N; pr[e].K = K; pr[e].ldy = N; pr[e].squared_relu = squared_relu;
+        }
+        return cuda_status(launch_gemv_mma(pr, experts, st));
+    }
+    for (int e = 0; e < experts; ++e) {
+        const cudaError_t err = launch_gemv_generic(q, scales, views[e].packed, views[e].weight_scale,
+                                                    views[e].magnitude, views[e].bias, capacity, K, N, y,
+                                                    nullptr, squared_relu, lists.counts + e,
+                                                    lists.offsets + e, st);
+        if (err != cudaSuccess) return TBL_ERR_CUDA;
+    }
+    return TBL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t tbl_grouped_workspace_bytes(int groups, int max_inputs) {
+    if (groups <= 0 || max_inputs <= 0) return 0;
+    return carve(nullptr, 1, max_inputs).bytes;
+}
+
+int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const float* input_dev,
+                        float* output_dev, int output_stride, int rms_mode, void* workspace_dev,
+                        size_t workspace_bytes, void* stream) {
+    if (!views_host || !input_dev || !output_dev || groups <= 0 || groups > TBL_MAX_GROUPS ||
+        output_stride <= 0)
+        return TBL_ERR_INVALID_ARG;
+    if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
+    const int K = views_host[0].inputs;
+    for (int g = 0; g < groups; ++g) {
+        const int rc = check_view(views_host[g]);
+        if (rc != TBL_OK) return rc;
+        // one shared input row is quantised once, so the views must agree on how
+        if (views_host[g].inputs != K || views_host[g].activation_bits != views_host[0].activation_bits ||
+            (views_host[g].rms_input != 0) != (views_host[0].rms_input != 0))
+            return TBL_ERR_UNSUPPORTED;
+        if (views_host[g].outputs > output_stride) return TBL_ERR_SHAPE;
+    }
+    if (!workspace_dev || workspace_bytes < tbl_grouped_workspace_bytes(groups, K)) return TBL_ERR_WORKSPACE;
+    if (!aligned16(workspace_dev) || !aligned16(input_dev)) return TBL_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const Workspace w = carve(workspace_dev, 1, K);
+    const int mode = views_host[0].rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
+    const bool mma = gemv_mma_supported(K);
+    cudaError_t e = launch_quantize_rows(input_dev, nullptr, 1, K, views_host[0].activation_bits, mode,
+                                         TBL_TIE_EVEN, w.q, mma ? w.qp : nullptr, w.act_scales, w.q_sums,
+                                         w.inv_norm, nullptr, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    if (mma) {
+        MmaProblem pr[TBL_MAX_GROUPS];
+        for (int g = 0; g < groups; ++g) {
+            pr[g] = MmaProblem{};
+            pr[g].words = views_host[g].packed; pr[g].qp = w.qp; pr[g].act_scales = w.act_scales;
+            pr[g].q_sums = w.q_sums; pr[g].magnitude = views_host[g].magnitude; pr[g].bias = views_host[g].bias;
+            pr[g].y = output_dev + static_cast<size_t>(g) * output_stride;
+            pr[g].weight_scale = views_host[g].weight_scale; pr[g].rows = 1;
+            pr[g].N = views_host[g].outputs; pr[g].K = K; pr[g].ldy = views_host[g].outputs;
+        }
+        return cuda_status(launch_gemv_mma(pr, groups, st));
+    }
+    for (int g = 0; g < groups; ++g) {
+        e = launch_gemv_generic(w.q, w.act_scales, views_host[g].packed, views_host[g].weight_scale,
+                                views_host[g].magnitude, views_host[g].bias, 1, K, views_host[g].outputs,
+                                output_dev + static_cast<size_t>(g) * output_stride, nullptr, 0, nullptr,
+                                nullptr, st);
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+    }
+    return TBL_OK;
+}
+
+size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row) {
+    if (rows <= 0 || dim <= 0 || hidden_dim <= 0 || experts <= 0 || max_routes_per_row <= 0) return 0;
+    if (max_routes_per_row > experts) max_routes_per_row = experts;
+    return carve_moe(nullptr, rows, dim, hidden_dim, experts, rows * max_routes_per_row).bytes;
+}
+
+int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev, const float* x_dev, int rows,
+                    int dim, int hidden_dim, int experts, int max_routes_per_row, int rms_mode, int tie_mode,
+                    float* out_dev, void* workspace_dev, size_t workspace_bytes, void* stream) {
+    if (!views_host || !routing_dev || !x_dev || !out_dev || rows <= 0 || dim <= 0 || hidden_dim <= 0 ||
+        experts <= 0 || experts > TBL_MAX_GROUPS || max_routes_per_row <= 0)
+        return TBL_ERR_INVALID_ARG;
+    if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
+    if (tie_mode != TBL_TIE_EVEN && tie_mode != TBL_TIE_AWAY) return TBL_ERR_INVALID_ARG;
+    if (max_routes_per_row > experts) max_routes_per_row = experts;
+    if (static_cast<int64_t>(rows) * max_routes_per_row > INT_MAX / 2) return TBL_ERR_SHAPE;
+    for (int e = 0; e < 2 * experts; ++e) {
+        const int rc = check_view(views_host[e]);
+        if (rc != TBL_OK) return rc;
+        const tbl_linear_view& v = views_host[e];
+        const int want_in = e < experts ? dim : hidden_dim, want_out = e < experts ? hidden_dim : dim;
+        if (v.inputs != want_in || v.outputs != want_out) return TBL_ERR_SHAPE;
+        if (v.activation_bits != views_host[0].activation_bits ||
+            (v.rms_input != 0) != (views_host[0].rms_input != 0))
+            return TBL_ERR_UNSUPPORTED;
+    }
+    if (!workspace_dev ||
+        workspace_bytes < tbl_moe_workspace_bytes(rows, dim, hidden_dim, experts, max_routes_per_row))
+        return TBL_ERR_WORKSPACE;
+    if (!aligned16(workspace_dev) || !aligned16(x_dev)) return TBL_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int capacity = rows * max_routes_per_row;
+    const MoeWorkspace w = carve_moe(workspace_dev, rows, dim, hidden_dim, experts, capacity);
+    const int bits = views_host[0].activation_bits;
+    const int mode = views_host[0].rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
+    int* status = device_status_ptr();
+    if (!status) return TBL_ERR_CUDA;
+
+    cudaError_t e = launch_moe_route(routing_dev, rows, experts, capacity, w.lists, status, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    // expert inputs: gather routed rows, [RMSNorm], quantise once per slot
+    const bool mma1 = gemv_mma_supported(dim), mma2 = gemv_mma_supported(hidden_dim);
+    e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, mma1 ? nullptr : w.q1,
+                             mma1 ? w.q1 : nullptr, w.scales1, w.sums1, w.inv1, w.lists.total, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    int rc = run_expert_stage(views_host, experts, w.q1, w.scales1, w.sums1, w.lists, capacity, w.hidden, 1, st);
+    if (rc != TBL_OK) return rc;
+    e = launch_quantize_rows(w.hidden, nullptr, capacity, hidden_dim, bits, mode, tie_mode, mma2 ? nullptr : w.q2,
+                             mma2 ? w.q2 : nullptr, w.scales2, w.sums2, w.inv2, w.lists.total, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    rc = run_expert_stage(views_host + experts, experts, w.q2, w.scales2, w.sums2, w.lists, capacity, w.contrib,
+                          0, st);
+    if (rc != TBL_OK) return rc;
+    return cuda_status(launch_moe_merge(routing_dev, w.contrib, w.lists.slot_of, rows, experts, dim, out_dev, st));
+}
+
+}  // extern "C"

@@ -1,0 +1,97 @@
+// Internal launcher declarations shared by the translation units of libternary_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ternary_b200.h"
+
+namespace tbl {
+
+// ---- interleaved activation order used by the tensor-core GEMV -------------------------------
+// Inside every 256-element block of a row, the sixteen 16-element groups (chunk t = 0..3 of 64
+// elements, quarter i = 0..3) are stored at group position i*4 + t, and each group is 4x4
+// byte-transposed.  Offset (in bytes) of the group that starts at element j (j % 16 == 0):
+__host__ __device__ __forceinline__ int qp_offset16(int j) {
+    const int b = j >> 8, r = j & 255;
+    const int t = r >> 6, i = (r >> 4) & 3;
+    return (b << 8) + (i << 6) + (t << 4);
+}
+
+// quantize.cu
+// active_rows (device, may be null): rows >= *active_rows are skipped.
+cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
+                                 int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
+                                 int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
+                                 cudaStream_t stream);
+cudaError_t launch_expand_i8(const uint32_t* words, int N, int K, int8_t* out, cudaStream_t stream);
+
+// gemv_stream.cu — M <= 4, CUDA-core dp4a, weights streamed by per-warp TMA rings.
+struct GemvSmallArgs {
+    const float* x;          // fp32 [M,K] when fused, else null
+    const int8_t* q;         // int8 [M,K] row-major when not fused, else null
+    const float* act_scales; // fp32 [M] when not fused
+    const uint32_t* words;   // canonical packed [N, K/16]
+    const float* magnitude;  // [N] or null
+    const float* bias;       // [N] or null
+    float* y;                // fp32 [M,N]
+    int32_t* acc_debug;      // int32 [M,N] or null
+    int8_t* q_out;           // fused only: int8 [M,K] codes written by CTA 0, or null
+    float* scales_out;       // fused only: fp32 [M] written by CTA 0, or null
+    float weight_scale;
+    float q_max;
+    int M, K, N;
+    int rms_mode;            // fused only: TBL_RMS_NONE or TBL_RMS_FAST
+};
+bool gemv_small_supported(int M, int K, int N);
+cudaError_t launch_gemv_small(const GemvSmallArgs& a, cudaStream_t stream);
+
+// gemv_generic.cu — any K % 16 == 0, any M: one warp per output row (correctness fallback).
+// rows_dev / offset_dev (device, may be null): the row count and first row come from device memory
+// (rows of q, act_scales and y are then taken relative to *offset_dev; M is the upper bound).
+cudaError_t launch_gemv_generic(const int8_t* q, const float* act_scales, const uint32_t* words,
+                                float weight_scale, const float* magnitude, const float* bias,
+                                int M, int K, int N, float* y, int32_t* acc_debug, int squared_relu,
+                                const int32_t* rows_dev, const int32_t* offset_dev, cudaStream_t stream);
+
+// gemv_mma.cu — 1 <= M <= 64 per pass, int8 mma.sync tensor cores, grouped problem table.
+struct MmaProblem {
+    const uint32_t* words;    // canonical packed [N, K/16]
+    const int8_t* qp;         // interleaved int8 activations [rows, K]
+    const float* act_scales;  // [rows]
+    const int32_t* q_sums;    // [rows]
+    const float* magnitude;
+    const float* bias;
+    float* y;                 // fp32 [rows, ldy]
+    int32_t* acc_debug;       // int32 [rows, ldy] or null
+    const int32_t* rows_dev;  // device row count (overrides rows when non-null)
+    const int32_t* offset_dev;// device index of this problem's first row in qp/act_scales/q_sums/y
+    float weight_scale;
+    int rows;                 // host-known row count (upper bound when rows_dev is set)
+    int N, K, ldy;
+    int squared_relu;
+    int cta_begin;            // first CTA index of this problem (filled by the launcher)
+};
+bool gemv_mma_supported(int K);
+cudaError_t launch_gemv_mma(MmaProblem* problems, int count, cudaStream_t stream);
+cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t* q_sums, cudaStream_t stream);
+
+// gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
+cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8,
+                                float weight_scale, const float* magnitude, const float* bias,
+                                int M, int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream);
+
+// moe.cu — routing lists and the final merge.
+struct MoeLists {
+    int32_t* counts;    // [E] rows routed to each expert
+    int32_t* offsets;   // [E] first slot of each expert
+    int32_t* total;     // [1] slots in use
+    int32_t* slot_row;  // [capacity] source row of each slot
+    int32_t* slot_of;   // [rows,E] slot of (row, expert) or -1
+};
+cudaError_t launch_moe_route(const float* routing, int rows, int experts, int capacity, MoeLists lists,
+                             int* status, cudaStream_t stream);
+cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,
+                             int experts, int dim, float* out, cudaStream_t stream);
+
+}  // namespace tbl

@@ -1,0 +1,99 @@
+// MoE helpers around the grouped ternary kernels: device-side routing lists (which rows go to
+// which expert, without a host round trip) and the final weighted merge in expert order.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+namespace {
+
+constexpr int kRouteThreads = 256;
+
+// One CTA walks the experts in index order and, inside an expert, the rows in row order, handing
+// out consecutive slots: slots of expert e are [offsets[e], offsets[e] + counts[e]).
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const float* __restrict__ routing, int rows, int experts, int capacity, MoeLists L,
+                 int* status) {
+    __shared__ int warp_totals[kRouteThreads / 32];
+    __shared__ int base;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int e = 0; e < experts; ++e) {
+        const int start = base;
+        for (int r0 = 0; r0 < rows; r0 += kRouteThreads) {
+            const int r = r0 + threadIdx.x;
+            const bool hit = r < rows && routing[static_cast<size_t>(r) * experts + e] != 0.0f;
+            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+            const int before = __popc(ballot & ((1u << lane) - 1));
+            if (lane == 0) warp_totals[warp] = __popc(ballot);
+            __syncthreads();
+            int prefix = 0, total = 0;
+            for (int w = 0; w < kRouteThreads / 32; ++w) {
+                if (w < warp) prefix += warp_totals[w];
+                total += warp_totals[w];
+            }
+            const int chunk_base = base;
+            if (r < rows) {
+                int slot = -1;
+                if (hit) {
+                    slot = chunk_base + prefix + before;
+                    if (slot < capacity) {
+                        L.slot_row[slot] = r;
+                    } else {
+                        slot = -1;
+                        atomicOr(status, TBL_DEV_ROUTE_OVERFLOW);
+                    }
+                }
+                L.slot_of[static_cast<size_t>(r) * experts + e] = slot;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) base = chunk_base + total;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            const int end = min(base, capacity);
+            const int begin = min(start, capacity);
+            L.offsets[e] = begin;
+            L.counts[e] = end - begin;
+        }
+    }
+    if (threadIdx.x == 0) *L.total = min(base, capacity);
+}
+
+// out[r,n] = sum over experts in index order of contrib[slot(r,e), n] * routing[r,e], each term and
+// each addition separately rounded (the CPU composition accumulates expert by expert).
+__global__ void __launch_bounds__(256)
+moe_merge_kernel(const float* __restrict__ routing, const float* __restrict__ contrib,
+                 const int32_t* __restrict__ slot_of, int experts, int dim, float* __restrict__ out) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (n >= dim) return;
+    float sum = 0.0f;
+    for (int e = 0; e < experts; ++e) {
+        const float w = routing[static_cast<size_t>(r) * experts + e];
+        if (w != 0.0f) {
+            const int slot = slot_of[static_cast<size_t>(r) * experts + e];
+            if (slot >= 0) sum = __fadd_rn(sum, __fmul_rn(contrib[static_cast<size_t>(slot) * dim + n], w));
+        }
+    }
+    out[static_cast<size_t>(r) * dim + n] = sum;
+}
+
+}  // namespace
+
+cudaError_t launch_moe_route(const float* routing, int rows, int experts, int capacity, MoeLists lists,
+                             int* status, cudaStream_t stream) {
+    moe_route_kernel<<<1, kRouteThreads, 0, stream>>>(routing, rows, experts, capacity, lists, status);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,
+                             int experts, int dim, float* out, cudaStream_t stream) {
+    const dim3 grid((dim + 255) / 256, rows);
+    moe_merge_kernel<<<grid, 256, 0, stream>>>(routing, contrib, slot_of, experts, dim, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace tbl

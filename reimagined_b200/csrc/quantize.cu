@@ -1,0 +1,280 @@
+// Per-row absmax int8 activation quantiser (optionally preceded by the input RMSNorm), and the
+// 2-bit -> int8 weight expansion that feeds the tensor-core GEMM.  Both are pure HBM/L2
+// streaming kernels.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+
+__device__ int g_device_status = 0;
+
+int* device_status_ptr() {
+    static int* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        cached[dev] = static_cast<int*>(p);
+    }
+    return cached[dev];
+}
+
+int read_and_clear_device_status(int* out) {
+    int status = 0;
+    if (cudaMemcpyFromSymbol(&status, g_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (status != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
+    *out = status;
+    return 0;
+}
+
+namespace {
+
+constexpr int kQuantThreads = 256;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Block-wide reductions over kQuantThreads threads; every thread gets the result.
+__device__ float block_max(float v, float* scratch) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = scratch[0];
+#pragma unroll
+    for (int w = 1; w < kQuantThreads / 32; ++w) r = fmaxf(r, scratch[w]);
+    __syncthreads();
+    return r;
+}
+__device__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kQuantThreads / 32; ++w) r += scratch[w];
+    __syncthreads();
+    return r;
+}
+
+// Reference-order RMS factor: one thread per row walks the row left to right with a
+// separately rounded multiply and add per element, exactly like the CPU loop it mirrors
+// (sum_sq += v*v; inv = 1/sqrt(sum_sq/K + eps)).  Latency-bound by design; rows run in parallel.
+__global__ void rms_reference_order_kernel(const float* __restrict__ x,
+                                           const int32_t* __restrict__ row_index, int M, int K,
+                                           float eps, float* __restrict__ inv_norm,
+                                           const int32_t* __restrict__ active_rows) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= M) return;
+    if (active_rows && row >= *active_rows) return;
+    const int src = row_index ? row_index[row] : row;
+    const float* p = x + static_cast<size_t>(src) * K;
+    float sum_sq = 0.0f;
+    for (int j = 0; j < K; ++j) {
+        const float v = p[j];
+        sum_sq = __fadd_rn(sum_sq, __fmul_rn(v, v));
+    }
+    const float mean = __fdiv_rn(sum_sq, static_cast<float>(K > 1 ? K : 1));
+    inv_norm[row] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+// One CTA per output row.  VEC16: K % 16 == 0 and 16-byte aligned rows -> 128-bit loads and
+// stores, optional second output in the tensor-core GEMV's interleaved order (qp).
+template <bool VEC16>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index, int K,
+                     float q_max, int rms_mode, bool tie_away, const float* __restrict__ inv_norm_in,
+                     int8_t* __restrict__ q, int8_t* __restrict__ qp, float* __restrict__ act_scales,
+                     int32_t* __restrict__ q_sums, const int32_t* __restrict__ active_rows) {
+    __shared__ float scratch[kQuantThreads / 32];
+    __shared__ int sum_scratch[kQuantThreads / 32];
+    const int row = blockIdx.x;
+    if (active_rows && row >= *active_rows) return;
+    const int src = row_index ? row_index[row] : row;
+    const float* xr = x + static_cast<size_t>(src) * K;
+
+    float inv = 1.0f;
+    if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
+        inv = inv_norm_in[row];
+    } else if (rms_mode == TBL_RMS_FAST) {
+        float ss = 0.0f;
+        if (VEC16) {
+            for (int j = threadIdx.x * 4; j < K; j += kQuantThreads * 4) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        } else {
+            for (int j = threadIdx.x; j < K; j += kQuantThreads) ss += xr[j] * xr[j];
+        }
+        ss = block_sum(ss, scratch);
+        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), 1e-6f)));
+    }
+    const bool normed = rms_mode != TBL_RMS_NONE;
+
+    float mx = 0.0f;
+    if (VEC16) {
+        for (int j = threadIdx.x * 4; j < K; j += kQuantThreads * 4) {
+            float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
+            if (normed) {
+                v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+            }
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    } else {
+        for (int j = threadIdx.x; j < K; j += kQuantThreads) {
+            float v = xr[j];
+            if (normed) v = __fmul_rn(v, inv);
+            mx = fmaxf(mx, fabsf(v));
+        }
+    }
+    mx = block_max(mx, scratch);
+    const float denom = __fadd_rn(mx, 1e-8f);
+    const float scale = __fdiv_rn(q_max, denom);
+    if (threadIdx.x == 0) act_scales[row] = __fdiv_rn(denom, q_max);
+
+    int local_sum = 0;
+    if (VEC16) {
+        // each thread turns 16 consecutive elements into one 128-bit store
+        for (int j = threadIdx.x * 16; j < K; j += kQuantThreads * 16) {
+            uint32_t words[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float4 v = __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e));
+                if (normed) {
+                    v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                    v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                }
+                const int a = static_cast<int>(round_tie(__fmul_rn(v.x, scale), tie_away));
+                const int b = static_cast<int>(round_tie(__fmul_rn(v.y, scale), tie_away));
+                const int c = static_cast<int>(round_tie(__fmul_rn(v.z, scale), tie_away));
+                const int d = static_cast<int>(round_tie(__fmul_rn(v.w, scale), tie_away));
+                local_sum += a + b + c + d;
+                words[e] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+            }
+            const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
+            if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
+            if (qp) {
+                *reinterpret_cast<uint4*>(qp + static_cast<size_t>(row) * K + qp_offset16(j)) =
+                    transpose4x4_bytes(natural);
+            }
+        }
+    } else {
+        // general K: the reference's AVX2 quantiser rounds the 8-wide body half-to-even and the
+        // K % 8 tail with std::round
+        const int body = tie_away ? 0 : (K / 8) * 8;
+        for (int j = threadIdx.x; j < K; j += kQuantThreads) {
+            float v = xr[j];
+            if (normed) v = __fmul_rn(v, inv);
+            const float r = round_tie(__fmul_rn(v, scale), j >= body);
+            const int a = static_cast<int>(fminf(127.0f, fmaxf(-127.0f, r)));
+            local_sum += a;
+            if (q) q[static_cast<size_t>(row) * K + j] = static_cast<int8_t>(a);
+        }
+    }
+    if (q_sums) {
+        local_sum = warp_sum_i(local_sum);
+        if ((threadIdx.x & 31) == 0) sum_scratch[threadIdx.x >> 5] = local_sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int s = 0;
+            for (int w = 0; w < kQuantThreads / 32; ++w) s += sum_scratch[w];
+            q_sums[row] = s;
+        }
+    }
+}
+
+// Each thread expands one 128-bit load (64 weights of one row) into four 128-bit stores.
+__global__ void expand_i8_kernel(const uint4* __restrict__ words, int64_t n_vec, int8_t* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+        const uint4 v = __ldg(words + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint4* dst = reinterpret_cast<uint4*>(out + i * 64);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // weights 4e..4e+3 of this word: 2-bit codes -> bytes, minus 1 per byte
+                const uint32_t b = (w[x] >> (8 * e)) & 0xffu;
+                const uint32_t spread = (b & 0x03u) | ((b & 0x0cu) << 6) | ((b & 0x30u) << 12) | ((b & 0xc0u) << 18);
+                o[e] = __vsub4(spread, 0x01010101u);
+            }
+            dst[x] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// scalar tail for N*K not a multiple of 64
+__global__ void expand_i8_tail_kernel(const uint32_t* __restrict__ words, int64_t first, int64_t total,
+                                      int8_t* __restrict__ out) {
+    const int64_t i = first + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    out[i] = static_cast<int8_t>(static_cast<int>((words[i >> 4] >> ((i & 15) << 1)) & 3u) - 1);
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
+                                 int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
+                                 int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
+                                 cudaStream_t stream) {
+    if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
+        rms_reference_order_kernel<<<(M + 63) / 64, 64, 0, stream>>>(x, row_index, M, K, 1e-6f,
+                                                                     inv_norm_scratch, active_rows);
+        note_launch();
+    }
+    const bool vec = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     (!q || (reinterpret_cast<uintptr_t>(q) & 15) == 0) &&
+                     (!qp || (reinterpret_cast<uintptr_t>(qp) & 15) == 0);
+    const float q_max = qmax_for_bits(bits);
+    if (vec) {
+        quantize_rows_kernel<true><<<M, kQuantThreads, 0, stream>>>(
+            x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, qp,
+            act_scales, q_sums, active_rows);
+    } else {
+        quantize_rows_kernel<false><<<M, kQuantThreads, 0, stream>>>(
+            x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, nullptr,
+            act_scales, q_sums, active_rows);
+    }
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expand_i8(const uint32_t* words, int N, int K, int8_t* out, cudaStream_t stream) {
+    const int64_t total = static_cast<int64_t>(N) * K;
+    const int64_t n_vec = total / 64;
+    if (n_vec > 0) {
+        const int threads = 256;
+        int64_t blocks = (n_vec + threads - 1) / threads;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        expand_i8_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(
+            reinterpret_cast<const uint4*>(words), n_vec, out);
+        note_launch();
+    }
+    const int64_t done = n_vec * 64;
+    if (done < total) {
+        expand_i8_tail_kernel<<<1, 64, 0, stream>>>(words, done, total, out);
+        note_launch();
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace tbl

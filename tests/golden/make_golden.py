@@ -1,0 +1,85 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own C++ (oracle/_ref/libnsos_ref.so,
+built by oracle/Makefile from the reference checkout) on seeded inputs.
+
+    python tests/golden/make_golden.py
+
+Only runs where the reference checkout is available; the produced fixtures are committed and are
+what the CPU-only and GPU tests compare against on machines without the reference.
+Inputs come from numpy's PCG64 (seeded); each fixture stores a SHA-256 of its inputs so a change
+of generator would be noticed, plus the inputs themselves when they are small.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def sha(*arrays):
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def make_inputs(seed, N, K, M, affine):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    mag = (1.0 + 0.25 * rng.standard_normal(N)).astype(np.float32) if affine else None
+    bias = (0.1 * rng.standard_normal(N)).astype(np.float32) if affine else None
+    return w, x, mag, bias
+
+
+# name, seed, N, K, M, exact_linear, affine, bits, store_inputs
+LINEAR_CASES = [
+    ("c1_exact_768", 0, 768, 768, 1, True, False, 8, False),
+    ("c1_default_768", 0, 768, 768, 1, False, True, 8, False),
+    ("small_33x48_m3", 11, 33, 48, 3, True, False, 8, True),
+    ("small_17x1024_m5", 12, 17, 1024, 5, True, False, 8, True),
+    ("tail_64x52_m2", 13, 64, 52, 2, True, False, 8, True),
+    ("affine_32x64_m8", 14, 32, 64, 8, False, True, 8, True),
+    ("bits4_48x256_m4", 15, 48, 256, 4, True, False, 4, True),
+    ("bits2_48x256_m4", 16, 48, 256, 4, True, False, 2, True),
+    ("mid_96x512_m24", 17, 96, 512, 24, False, True, 8, True),
+    ("gemm_160x256_m130", 18, 160, 256, 130, True, False, 8, True),
+]
+
+
+def main():
+    R = oracle.ref()
+    for name, seed, N, K, M, exact, affine, bits, store in LINEAR_CASES:
+        w, x, mag, bias = make_inputs(seed, N, K, M, affine)
+        words, scale = R.pack(w)
+        y = R.linear_forward(w, x, exact_linear=exact, magnitude=mag, bias=bias, bits=bits)
+        rec = dict(seed=seed, N=N, K=K, M=M, exact_linear=exact, affine=affine, bits=bits,
+                   input_sha=sha(w, x), words=words, weight_scale=np.float32(scale), y=y)
+        if store:
+            rec.update(w=w, x=x)
+        if affine:
+            rec.update(magnitude=mag, bias=bias)
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), **rec)
+        print(name, "scale", scale, "y[0,:3]", y[0, :3])
+
+    # MoE expert FFN (default-mode experts: RMS input norm, magnitude 1, no bias), top-2 of 4
+    rng = np.random.default_rng(21)
+    rows, D, H, E, top_k = 6, 64, 128, 4, 2
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    up = (rng.standard_normal((E, H, D)) * 0.02).astype(np.float32)
+    down = (rng.standard_normal((E, D, H)) * 0.02).astype(np.float32)
+    logits = rng.standard_normal((rows, E)).astype(np.float32)
+    routing = oracle.port().router_topk(logits, top_k)
+    out = R.moe_forward(x, routing, up, down)
+    np.savez_compressed(os.path.join(OUT, "moe_6x64x128_e4.npz"), x=x, up=up, down=down, routing=routing,
+                        out=out, top_k=top_k)
+    print("moe out[0,:3]", out[0, :3])
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+"""CPU-only checks of the product library: it loads, exports every declared symbol, its host-side
+packer is bit-identical to the oracle and the golden vectors, and validation rejects bad calls
+before anything is launched."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, golden_cases, load_golden
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ternary_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tbl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(tbl):
+    from reimagined_b200 import capi
+    names = declared_symbols()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(tbl, n), f"{n} declared in include/ternary_b200.h but not exported"
+    assert set(names) == set(capi.EXPORTED_SYMBOLS), "capi.py bindings out of sync with the header"
+    assert tbl.tbl_abi_version() == 1
+    assert tbl.tbl_status_string(0) == b"ok"
+
+
+def host_pack(tbl, w):
+    N, K = w.shape
+    n = tbl.tbl_packed_words(N, K)
+    words = np.zeros(n, np.uint32)
+    scale = np.zeros(1, np.float32)
+    rc = tbl.tbl_pack_weights(w.ctypes.data, N, K, words.ctypes.data, scale.ctypes.data)
+    assert rc == 0
+    return words, scale[0]
+
+
+@pytest.mark.parametrize("path", [p for p in golden_cases() if "moe_" not in p],
+                         ids=lambda p: p.split("/")[-1][:-4])
+def test_host_packer_matches_golden(tbl, path):
+    g = load_golden(path)
+    words, scale = host_pack(tbl, np.ascontiguousarray(g["w"]))
+    assert np.array_equal(words, g["words"])
+    assert np.float32(scale).view(np.uint32) == np.float32(g["weight_scale"]).view(np.uint32)
+
+
+@pytest.mark.parametrize("N,K", [(1, 16), (3, 5), (17, 33), (64, 768), (5, 1)])
+def test_host_packer_matches_oracle_and_roundtrips(tbl, port, N, K):
+    rng = np.random.default_rng(N * 1000 + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    words, scale = host_pack(tbl, w)
+    owords, oscale, t, _ = port.pack_weights(w)
+    assert np.array_equal(words, owords)
+    assert np.float32(scale).view(np.uint32) == oscale.view(np.uint32)
+    back = np.zeros((N, K), np.int8)
+    assert tbl.tbl_unpack_weights_i8(words.ctypes.data, N, K, back.ctypes.data) == 0
+    assert np.array_equal(back, t)
+    assert set(np.unique(back)).issubset({-1, 0, 1})
+    assert tbl.tbl_validate_packed(words.ctypes.data, words.size, N, K, float(scale), None, None) == 0
+
+
+def test_packer_all_zero_and_constant(tbl, port):
+    w = np.zeros((4, 16), np.float32)
+    words, scale = host_pack(tbl, w)
+    assert scale == np.float32(1e-8) and np.all(words == 0x55555555)  # every code is 1 (zero weight)
+    w[:] = 0.3
+    words, scale = host_pack(tbl, w)
+    assert np.all(words == 0xAAAAAAAA)  # every weight rounds to +1
+    assert np.array_equal(words, port.pack_weights(w)[0])
+
+
+def test_validate_packed_rejects(tbl):
+    from reimagined_b200 import capi as A
+    C3 = -8
+    words = np.full(4, 0x55555555, np.uint32)
+    ok = lambda *a: tbl.tbl_validate_packed(*a)
+    assert ok(words.ctypes.data, 4, 4, 16, 0.5, None, None) == 0
+    assert ok(words.ctypes.data, 3, 4, 16, 0.5, None, None) == -2          # wrong word count
+    assert ok(words.ctypes.data, 4, 4, 16, 0.0, None, None) == -4          # scale must be > 0
+    assert ok(words.ctypes.data, 4, 4, 16, float("nan"), None, None) == -4
+    bad = words.copy(); bad[2] |= 0x3 << 10
+    assert ok(bad.ctypes.data, 4, 4, 16, 0.5, None, None) == C3            # reserved code 0b11
+    mag = np.array([1, 2, np.inf, 4], np.float32)
+    assert ok(words.ctypes.data, 4, 4, 16, 0.5, mag.ctypes.data, None) == -1
+    assert ok(None, 4, 4, 16, 0.5, None, None) == -1
+
+
+def test_device_entry_points_validate_before_launching(tbl):
+    """Bad arguments are refused with a status and nothing is enqueued (no GPU needed).
+    The non-null 'pointers' are dummies that validation never dereferences."""
+    P = 0x1000  # 16-byte aligned dummy
+    before = tbl.tbl_launch_count()
+    lf = tbl.tbl_linear_forward
+    assert lf(P, P, None, 0.5, 1, 24, 8, 8, 0, None, None, P, None, 0, None) == -2     # K % 16
+    assert lf(P, P, None, 0.5, 0, 32, 8, 8, 0, None, None, P, None, 0, None) == -1     # M <= 0
+    assert lf(P, P, None, -1.0, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -4    # scale
+    assert lf(P, P, None, 0.5, 1, 32, 8, 9, 0, None, None, P, None, 0, None) == -5     # bits
+    assert lf(P, P, None, 0.5, 1, 32, 8, 1, 0, None, None, P, None, 0, None) == -5
+    assert lf(P, P, None, 0.5, 1, 8454672, 8, 8, 0, None, None, P, None, 0, None) == -3  # K > INT_MAX/254
+    assert lf(P, P, None, 0.5, 65536, 32, 65536, 8, 0, None, None, P, None, 0, None) == -2  # M*N > INT_MAX
+    assert lf(None, P, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -1
+    assert lf(P + 4, P, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -6  # alignment
+    assert lf(P, P, None, 0.5, 8, 32, 8, 8, 0, None, None, P, None, 0, None) == -7      # needs workspace
+    assert tbl.tbl_gemv(P, P, P, 0.5, None, None, 65, 32, 8, P, None, None, 0, None) == -2  # M > 64
+    assert tbl.tbl_quantize_rows(P, None, 1, 32, 8, 2, 0, P, P, None, None) == -1
+    from reimagined_b200 import capi
+    v = capi.LinearView(P, None, None, None, 32, 8, 8, 0, 0.5)   # fp32-weight view: not implemented
+    arr = (capi.LinearView * 1)(v)
+    assert tbl.tbl_grouped_forward(arr, 1, P, P, 8, 0, P, 1 << 20, None) == -10
+    assert tbl.tbl_launch_count() == before
+    assert tbl.tbl_linear_workspace_bytes(8, 1024, 64) >= 2 * 8 * 1024
