@@ -33,6 +33,8 @@ def device_status():
 def quantize_rows(x, bits=8, rms_mode=0, tie_mode=0, row_index=None):
     L = capi.lib()
     M, K = x.shape
+    if row_index is not None:
+        M = row_index.numel()
     q = torch.empty((M, K), dtype=torch.int8, device="cuda")
     sc = torch.empty(M, dtype=torch.float32, device="cuda")
     sums = torch.empty(M, dtype=torch.int32, device="cuda")
