@@ -83,7 +83,19 @@ int tbl_unpack_weights_i8(const uint32_t* words_host, int N, int K, int8_t* t_ho
 int tbl_validate_packed(const uint32_t* words_host, int64_t n_words, int N, int K,
                         float weight_scale, const float* magnitude_host, const float* bias_host);
 
-/* ---- device: weight expansion for the tensor-core GEMM ------------------------------- */
+/* ---- device: weight layouts derived from the canonical words ------------------------------ */
+
+/* Bytes of the strip-major copy of an [N,K] matrix (K % 256 == 0; rows padded to a multiple of 16). */
+size_t tbl_strip_bytes(int N, int K);
+
+/* Re-orders canonical words (device) into the strip-major layout the decode GEMV streams:
+ * strips of 16 rows, each a contiguous run of K/256 blocks of 1 KB whose 16-byte chunks are in
+ * warp-lane order (rows g and g+8 of lane 4g+t).  A permutation of the canonical 16-byte chunks
+ * plus zero-weight padding rows; done once per matrix at load time.  Needs K % 256 == 0.
+ * Replaces: the H2D upload of the packed words in BitLinear::forward
+ * (OXN/nsos/src/bitlinear.cpp:632-643), which is where the reference fixes its device layout. */
+int tbl_relayout_strips(const uint32_t* words_dev, int N, int K, void* strips_dev, void* stream);
+
 
 /* Expands canonical words (device) into int8 {-1,0,+1} [N,K] row-major (device), the K-major
  * operand the tcgen05 GEMM reads through TMA.  Mirrors the unpacked copy the reference keeps
@@ -109,13 +121,15 @@ int tbl_quantize_rows(const float* x_dev, const int32_t* row_index_dev, int M, i
 size_t tbl_gemv_workspace_bytes(int M, int K);
 
 /* Decode GEMV, 1 <= M <= 64: y[M,N] = epilogue(q[M,K] x ternary[N,K]^T).
+ * Weights: strips_dev (tbl_relayout_strips, the fast tensor-core stream) and/or words_dev
+ * (canonical; used when strips_dev is NULL or K % 256 != 0).  At least one must be given.
  * acc_debug (device int32 [M,N], may be NULL) receives the raw accumulators.
  * Replaces: launch_bitnet_gemv_scaled (OXN/nsos/src/cuda/kernels.cu:1027-1066,1110-1130) and,
  * for 1 < M <= 64, launch_bitnet_gemm + launch_bitnet_apply_act_scales_kernel
  * (OXN/nsos/src/cuda/kernels.cu:966-1022, OXN/nsos/src/cuda/bitnet_kernels.cu:140-149). */
 int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* words_dev,
-             float weight_scale, const float* magnitude_dev, const float* bias_dev,
-             int M, int K, int N, float* y_dev, int32_t* acc_debug_dev,
+             const void* strips_dev, float weight_scale, const float* magnitude_dev,
+             const float* bias_dev, int M, int K, int N, float* y_dev, int32_t* acc_debug_dev,
              void* workspace_dev, size_t workspace_bytes, void* stream);
 
 /* Prefill GEMM on tcgen05 int8 tensor cores (any M >= 1, intended for M >= 128):
@@ -133,21 +147,23 @@ int tbl_gemm(const int8_t* q_dev, const float* act_scales_dev, const int8_t* w_i
 size_t tbl_linear_workspace_bytes(int M, int K, int N);
 
 /* x fp32 [M,K] (device) -> y fp32 [M,N] (device): [RMSNorm] -> quantise -> ternary GEMV
- * (M <= 64, packed words) or tcgen05 GEMM (M > 64 when w_i8_dev != NULL) -> two-scale
- * epilogue [* magnitude] [+ bias].  w_i8_dev may be NULL: then every M runs on the packed words.
+ * (M <= 64, 2-bit weights) or tcgen05 GEMM (M > 64 when w_i8_dev != NULL) -> two-scale
+ * epilogue [* magnitude] [+ bias].  strips_dev / w_i8_dev may be NULL: then the call runs on what
+ * it is given (canonical words alone serve every M, at lower speed).
  * Replaces: bitnet_gemm_158bit_gpu (OXN/nsos/include/bitnet_gpu_dispatch.h:46-51,
  * OXN/nsos/src/bitnet_gpu_dispatch.cpp:65-174) and the packed branch of BitLinear::forward
  * (OXN/nsos/src/bitlinear.cpp:606-659,690-741). */
-int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const int8_t* w_i8_dev,
-                       float weight_scale, int M, int K, int N, int bits, int rms_mode,
+int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void* strips_dev,
+                       const int8_t* w_i8_dev, float weight_scale, int M, int K, int N, int bits, int rms_mode,
                        const float* magnitude_dev, const float* bias_dev, float* y_dev,
                        void* workspace_dev, size_t workspace_bytes, void* stream);
 
 /* ---- grouped variant ------------------------------------------------------------------- */
 
-/* Borrowed descriptor of one linear; field-for-field the reference's GpuLinearView
- * (OXN/nsos/include/gpu_linear_view.h:8-26).  Only the packed mode (packed != NULL,
- * weight == NULL, activation_bits in [2,8]) is implemented; others -> TBL_ERR_UNSUPPORTED. */
+/* Borrowed descriptor of one linear; the first nine fields are field-for-field the reference's
+ * GpuLinearView (OXN/nsos/include/gpu_linear_view.h:8-26); `strips` is this library's addition
+ * (strip-major copy of `packed`, or NULL).  Only the packed mode (packed != NULL, weight == NULL,
+ * activation_bits in [2,8]) is implemented; others -> TBL_ERR_UNSUPPORTED. */
 typedef struct tbl_linear_view {
     const float* weight;
     const uint32_t* packed;
@@ -158,6 +174,7 @@ typedef struct tbl_linear_view {
     int activation_bits;
     int rms_input;
     float weight_scale;
+    const void* strips;
 } tbl_linear_view;
 
 #define TBL_MAX_GROUPS 32

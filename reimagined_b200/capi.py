@@ -26,7 +26,8 @@ class LinearView(C.Structure):
 
     _fields_ = [("weight", C.c_void_p), ("packed", C.c_void_p), ("magnitude", C.c_void_p),
                 ("bias", C.c_void_p), ("inputs", C.c_int), ("outputs", C.c_int),
-                ("activation_bits", C.c_int), ("rms_input", C.c_int), ("weight_scale", C.c_float)]
+                ("activation_bits", C.c_int), ("rms_input", C.c_int), ("weight_scale", C.c_float),
+                ("strips", C.c_void_p)]
 
 
 _vp = C.c_void_p
@@ -38,14 +39,16 @@ _SIGNATURES = {
     "tbl_pack_weights": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
     "tbl_unpack_weights_i8": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "tbl_validate_packed": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_float, _vp, _vp]),
+    "tbl_strip_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "tbl_relayout_strips": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
     "tbl_expand_weights_i8": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp]),
     "tbl_quantize_rows": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "tbl_gemv_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
-    "tbl_gemv": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp,
+    "tbl_gemv": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp,
                            C.c_size_t, _vp]),
     "tbl_gemm": (C.c_int, [_vp, _vp, _vp, C.c_float, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
     "tbl_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
-    "tbl_linear_forward": (C.c_int, [_vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+    "tbl_linear_forward": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                      _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "tbl_grouped_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "tbl_grouped_forward": (C.c_int, [C.POINTER(LinearView), C.c_int, _vp, _vp, C.c_int, C.c_int, _vp,

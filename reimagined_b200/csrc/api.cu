@@ -57,21 +57,22 @@ Workspace carve(void* base, int M, int K) {
 
 // GEMV on already-quantised activations for any M (the tensor-core kernel walks M in tiles of 64).
 int run_gemv(const int8_t* q, const int8_t* qp, const float* act_scales, const int32_t* q_sums,
-             const uint32_t* words, float weight_scale, const float* magnitude, const float* bias, int M,
-             int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream) {
+             const uint32_t* words, const void* strips, float weight_scale, const float* magnitude,
+             const float* bias, int M, int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream) {
+    if (qp && strips && gemv_strip_supported(K)) {
+        StripProblem pr{};
+        pr.strips = static_cast<const uint8_t*>(strips); pr.qp = qp; pr.act_scales = act_scales;
+        pr.q_sums = q_sums; pr.magnitude = magnitude; pr.bias = bias; pr.y = y; pr.acc_debug = acc_debug;
+        pr.weight_scale = weight_scale; pr.rows = M; pr.N = N; pr.K = K; pr.ldy = N;
+        return cuda_status(launch_gemv_strip(&pr, 1, stream));
+    }
+    if (!words || !q) return TBL_ERR_INVALID_ARG;
     if (M <= 4 && gemv_small_supported(M, K, N) && aligned16(words) && aligned16(q)) {
         GemvSmallArgs a{};
         a.q = q; a.act_scales = act_scales; a.words = words; a.magnitude = magnitude; a.bias = bias;
         a.y = y; a.acc_debug = acc_debug; a.weight_scale = weight_scale; a.q_max = 127.0f;
         a.M = M; a.K = K; a.N = N; a.rms_mode = TBL_RMS_NONE;
         return cuda_status(launch_gemv_small(a, stream));
-    }
-    if (qp && gemv_mma_supported(K) && aligned16(words)) {
-        MmaProblem pr{};
-        pr.words = words; pr.qp = qp; pr.act_scales = act_scales; pr.q_sums = q_sums;
-        pr.magnitude = magnitude; pr.bias = bias; pr.y = y; pr.acc_debug = acc_debug;
-        pr.weight_scale = weight_scale; pr.rows = M; pr.N = N; pr.K = K; pr.ldy = N;
-        return cuda_status(launch_gemv_mma(&pr, 1, stream));
     }
     return cuda_status(launch_gemv_generic(q, act_scales, words, weight_scale, magnitude, bias, M, K, N, y,
                                            acc_debug, 0, nullptr, nullptr, stream));
@@ -113,6 +114,18 @@ int tbl_device_status(void* stream) {
     return status;
 }
 
+size_t tbl_strip_bytes(int N, int K) {
+    if (N <= 0 || K <= 0 || K % 256 != 0) return 0;
+    return static_cast<size_t>((N + 15) / 16) * 16 * (K / 4);
+}
+
+int tbl_relayout_strips(const uint32_t* words_dev, int N, int K, void* strips_dev, void* stream) {
+    if (!words_dev || !strips_dev || N <= 0 || K <= 0) return TBL_ERR_INVALID_ARG;
+    if (!gemv_strip_supported(K)) return TBL_ERR_SHAPE;
+    if (!aligned16(words_dev) || !aligned16(strips_dev)) return TBL_ERR_ALIGNMENT;
+    return cuda_status(launch_relayout_strips(words_dev, N, K, strips_dev, static_cast<cudaStream_t>(stream)));
+}
+
 int tbl_expand_weights_i8(const uint32_t* words_dev, int N, int K, int8_t* w_i8_dev, void* stream) {
     if (!words_dev || !w_i8_dev || N <= 0 || K <= 0) return TBL_ERR_INVALID_ARG;
     if (!aligned16(words_dev) || !aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
@@ -131,7 +144,7 @@ int tbl_quantize_rows(const float* x_dev, const int32_t* row_index_dev, int M, i
     if (tie_mode != TBL_TIE_EVEN && tie_mode != TBL_TIE_AWAY) return TBL_ERR_INVALID_ARG;
     return cuda_status(launch_quantize_rows(x_dev, row_index_dev, M, K, bits, rms_mode, tie_mode, q_dev,
                                             nullptr, act_scales_dev, q_sums_dev, nullptr, nullptr,
-                                            static_cast<cudaStream_t>(stream)));
+                                            QuantSegments{}, static_cast<cudaStream_t>(stream)));
 }
 
 size_t tbl_gemv_workspace_bytes(int M, int K) {
@@ -139,18 +152,21 @@ size_t tbl_gemv_workspace_bytes(int M, int K) {
     return round_up(static_cast<size_t>(M) * K, 256) + round_up(static_cast<size_t>(M) * 4, 256);
 }
 
-int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* words_dev, float weight_scale,
-             const float* magnitude_dev, const float* bias_dev, int M, int K, int N, float* y_dev,
-             int32_t* acc_debug_dev, void* workspace_dev, size_t workspace_bytes, void* stream) {
-    if (!q_dev || !act_scales_dev || !words_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* words_dev, const void* strips_dev,
+             float weight_scale, const float* magnitude_dev, const float* bias_dev, int M, int K, int N,
+             float* y_dev, int32_t* acc_debug_dev, void* workspace_dev, size_t workspace_bytes, void* stream) {
+    if (!q_dev || !act_scales_dev || (!words_dev && !strips_dev) || !y_dev) return TBL_ERR_INVALID_ARG;
     const int rc = check_problem(M, K, N, weight_scale, 8);
     if (rc != TBL_OK) return rc;
     if (M > 64) return TBL_ERR_SHAPE;
+    if (!aligned16(q_dev) || (words_dev && !aligned16(words_dev)) || (strips_dev && !aligned16(strips_dev)))
+        return TBL_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int8_t* qp = nullptr;
     int32_t* q_sums = nullptr;
-    const bool small = M <= 4 && gemv_small_supported(M, K, N) && aligned16(words_dev) && aligned16(q_dev);
-    if (!small && gemv_mma_supported(K) && aligned16(words_dev) && aligned16(q_dev)) {
+    const bool strip = strips_dev != nullptr && gemv_strip_supported(K);
+    if (!strip && !words_dev) return TBL_ERR_SHAPE;
+    if (strip) {
         if (!workspace_dev || workspace_bytes < tbl_gemv_workspace_bytes(M, K)) return TBL_ERR_WORKSPACE;
         if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
         qp = static_cast<int8_t*>(workspace_dev);
@@ -159,8 +175,8 @@ int tbl_gemv(const int8_t* q_dev, const float* act_scales_dev, const uint32_t* w
         const cudaError_t e = launch_permute_q(q_dev, M, K, qp, q_sums, st);
         if (e != cudaSuccess) return TBL_ERR_CUDA;
     }
-    return run_gemv(q_dev, qp, act_scales_dev, q_sums, words_dev, weight_scale, magnitude_dev, bias_dev, M, K,
-                    N, y_dev, acc_debug_dev, st);
+    return run_gemv(q_dev, qp, act_scales_dev, q_sums, words_dev, strip ? strips_dev : nullptr, weight_scale,
+                    magnitude_dev, bias_dev, M, K, N, y_dev, acc_debug_dev, st);
 }
 
 int tbl_gemm(const int8_t* q_dev, const float* act_scales_dev, const int8_t* w_i8_dev, float weight_scale,
@@ -181,20 +197,24 @@ size_t tbl_linear_workspace_bytes(int M, int K, int N) {
     return carve(nullptr, M, K).bytes;
 }
 
-int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const int8_t* w_i8_dev,
-                       float weight_scale, int M, int K, int N, int bits, int rms_mode,
+int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void* strips_dev,
+                       const int8_t* w_i8_dev, float weight_scale, int M, int K, int N, int bits, int rms_mode,
                        const float* magnitude_dev, const float* bias_dev, float* y_dev, void* workspace_dev,
                        size_t workspace_bytes, void* stream) {
-    if (!x_dev || !words_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+    if (!x_dev || !y_dev) return TBL_ERR_INVALID_ARG;
     const int rc = check_problem(M, K, N, weight_scale, bits);
     if (rc != TBL_OK) return rc;
     if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
-    if (!aligned16(x_dev)) return TBL_ERR_ALIGNMENT;
+    if (!aligned16(x_dev) || (words_dev && !aligned16(words_dev)) || (strips_dev && !aligned16(strips_dev)) ||
+        (w_i8_dev && !aligned16(w_i8_dev)))
+        return TBL_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool use_gemm = w_i8_dev != nullptr && M > 64;
+    const bool strip = !use_gemm && strips_dev != nullptr && gemv_strip_supported(K);
+    if (!use_gemm && !strip && !words_dev) return TBL_ERR_INVALID_ARG;
 
-    // M <= 4: one kernel, the quantiser runs in the GEMV's prologue
-    if (M <= 4 && rms_mode != TBL_RMS_REFERENCE_ORDER && aligned16(words_dev) &&
-        gemv_small_supported(M, K, N)) {
+    // canonical words only, M <= 4: one kernel, the quantiser runs in the GEMV's prologue
+    if (!use_gemm && !strip && M <= 4 && rms_mode != TBL_RMS_REFERENCE_ORDER && gemv_small_supported(M, K, N)) {
         GemvSmallArgs a{};
         a.x = x_dev; a.words = words_dev; a.magnitude = magnitude_dev; a.bias = bias_dev; a.y = y_dev;
         a.weight_scale = weight_scale; a.q_max = qmax_for_bits(bits);
@@ -205,18 +225,16 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const int8
     if (!workspace_dev || workspace_bytes < tbl_linear_workspace_bytes(M, K, N)) return TBL_ERR_WORKSPACE;
     if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
     const Workspace w = carve(workspace_dev, M, K);
-    const bool use_gemm = w_i8_dev != nullptr && M > 64;
-    const bool want_qp = !use_gemm && gemv_mma_supported(K);
-    cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, w.q,
-                                         want_qp ? w.qp : nullptr, w.act_scales, w.q_sums, w.inv_norm, nullptr, st);
+    // the strip GEMV reads only the interleaved copy; the other paths read the row-major codes
+    cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, strip ? nullptr : w.q,
+                                         strip ? w.qp : nullptr, w.act_scales, w.q_sums, w.inv_norm, nullptr,
+                                         QuantSegments{}, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
-    if (use_gemm) {
-        if (!aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
+    if (use_gemm)
         return cuda_status(launch_gemm_tcgen05(w.q, w.act_scales, w_i8_dev, weight_scale, magnitude_dev,
                                                bias_dev, M, K, N, y_dev, nullptr, st));
-    }
-    return run_gemv(w.q, want_qp ? w.qp : nullptr, w.act_scales, w.q_sums, words_dev, weight_scale,
-                    magnitude_dev, bias_dev, M, K, N, y_dev, nullptr, st);
+    return run_gemv(strip ? nullptr : w.q, strip ? w.qp : nullptr, w.act_scales, w.q_sums, words_dev,
+                    strip ? strips_dev : nullptr, weight_scale, magnitude_dev, bias_dev, M, K, N, y_dev, nullptr, st);
 }
 
 }  // extern "C"
@@ -270,21 +288,22 @@ MoeWorkspace carve_moe(void* base, int rows, int dim, int hidden_dim, int expert
 }
 
 // One grouped linear stage of the MoE: problem e multiplies the rows of expert e's slot range.
-int run_expert_stage(const tbl_linear_view* views, int experts, const int8_t* q, const float* scales,
+int run_expert_stage(const tbl_linear_view* views, int experts, const int8_t* q, bool strip, const float* scales,
                      const int32_t* sums, const MoeLists& lists, int capacity, float* y, int squared_relu,
                      cudaStream_t st) {
     const int K = views[0].inputs, N = views[0].outputs;
-    if (gemv_mma_supported(K)) {
-        MmaProblem pr[TBL_MAX_GROUPS];
+    if (strip) {
+        StripProblem pr[TBL_MAX_GROUPS];
         for (int e = 0; e < experts; ++e) {
-            pr[e] = MmaProblem{};
-            pr[e].words = views[e].packed; pr[e].qp = q; pr[e].act_scales = scales; pr[e].q_sums = sums;
+            pr[e] = StripProblem{};
+            pr[e].strips = static_cast<const uint8_t*>(views[e].strips); pr[e].qp = q;
+            pr[e].act_scales = scales; pr[e].q_sums = sums;
             pr[e].magnitude = views[e].magnitude; pr[e].bias = views[e].bias; pr[e].y = y;
             pr[e].rows_dev = lists.counts + e; pr[e].offset_dev = lists.offsets + e;
             pr[e].weight_scale = views[e].weight_scale; pr[e].rows = capacity;
             pr[e].N = N; pr[e].K = K; pr[e].ldy = N; pr[e].squared_relu = squared_relu;
         }
-        return cuda_status(launch_gemv_mma(pr, experts, st));
+        return cuda_status(launch_gemv_strip(pr, experts, st));
     }
     for (int e = 0; e < experts; ++e) {
         const cudaError_t err = launch_gemv_generic(q, scales, views[e].packed, views[e].weight_scale,
@@ -294,6 +313,12 @@ int run_expert_stage(const tbl_linear_view* views, int experts, const int8_t* q,
         if (err != cudaSuccess) return TBL_ERR_CUDA;
     }
     return TBL_OK;
+}
+
+bool all_have_strips(const tbl_linear_view* views, int count) {
+    for (int i = 0; i < count; ++i)
+        if (!views[i].strips || !aligned16(views[i].strips)) return false;
+    return gemv_strip_supported(views[0].inputs);
 }
 
 }  // namespace
@@ -327,22 +352,23 @@ int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const flo
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const Workspace w = carve(workspace_dev, 1, K);
     const int mode = views_host[0].rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
-    const bool mma = gemv_mma_supported(K);
+    const bool mma = all_have_strips(views_host, groups);
     cudaError_t e = launch_quantize_rows(input_dev, nullptr, 1, K, views_host[0].activation_bits, mode,
                                          TBL_TIE_EVEN, w.q, mma ? w.qp : nullptr, w.act_scales, w.q_sums,
-                                         w.inv_norm, nullptr, st);
+                                         w.inv_norm, nullptr, QuantSegments{}, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
     if (mma) {
-        MmaProblem pr[TBL_MAX_GROUPS];
+        StripProblem pr[TBL_MAX_GROUPS];
         for (int g = 0; g < groups; ++g) {
-            pr[g] = MmaProblem{};
-            pr[g].words = views_host[g].packed; pr[g].qp = w.qp; pr[g].act_scales = w.act_scales;
+            pr[g] = StripProblem{};
+            pr[g].strips = static_cast<const uint8_t*>(views_host[g].strips); pr[g].qp = w.qp;
+            pr[g].act_scales = w.act_scales;
             pr[g].q_sums = w.q_sums; pr[g].magnitude = views_host[g].magnitude; pr[g].bias = views_host[g].bias;
             pr[g].y = output_dev + static_cast<size_t>(g) * output_stride;
             pr[g].weight_scale = views_host[g].weight_scale; pr[g].rows = 1;
             pr[g].N = views_host[g].outputs; pr[g].K = K; pr[g].ldy = views_host[g].outputs;
         }
-        return cuda_status(launch_gemv_mma(pr, groups, st));
+        return cuda_status(launch_gemv_strip(pr, groups, st));
     }
     for (int g = 0; g < groups; ++g) {
         e = launch_gemv_generic(w.q, w.act_scales, views_host[g].packed, views_host[g].weight_scale,
@@ -395,17 +421,20 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
     cudaError_t e = launch_moe_route(routing_dev, rows, experts, capacity, w.lists, status, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
     // expert inputs: gather routed rows, [RMSNorm], quantise once per slot
-    const bool mma1 = gemv_mma_supported(dim), mma2 = gemv_mma_supported(hidden_dim);
+    const bool mma1 = all_have_strips(views_host, experts);
+    const bool mma2 = all_have_strips(views_host + experts, experts);
+    const QuantSegments seg{w.lists.offsets, w.lists.counts, experts};
     e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, mma1 ? nullptr : w.q1,
-                             mma1 ? w.q1 : nullptr, w.scales1, w.sums1, w.inv1, w.lists.total, st);
+                             mma1 ? w.q1 : nullptr, w.scales1, w.sums1, w.inv1, w.lists.total, seg, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
-    int rc = run_expert_stage(views_host, experts, w.q1, w.scales1, w.sums1, w.lists, capacity, w.hidden, 1, st);
+    int rc = run_expert_stage(views_host, experts, w.q1, mma1, w.scales1, w.sums1, w.lists, capacity, w.hidden,
+                              1, st);
     if (rc != TBL_OK) return rc;
     e = launch_quantize_rows(w.hidden, nullptr, capacity, hidden_dim, bits, mode, tie_mode, mma2 ? nullptr : w.q2,
-                             mma2 ? w.q2 : nullptr, w.scales2, w.sums2, w.inv2, w.lists.total, st);
+                             mma2 ? w.q2 : nullptr, w.scales2, w.sums2, w.inv2, w.lists.total, seg, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
-    rc = run_expert_stage(views_host + experts, experts, w.q2, w.scales2, w.sums2, w.lists, capacity, w.contrib,
-                          0, st);
+    rc = run_expert_stage(views_host + experts, experts, w.q2, mma2, w.scales2, w.sums2, w.lists, capacity,
+                          w.contrib, 0, st);
     if (rc != TBL_OK) return rc;
     return cuda_status(launch_moe_merge(routing_dev, w.contrib, w.lists.slot_of, rows, experts, dim, out_dev, st));
 }

@@ -1,6 +1,335 @@
+// Prefill GEMM: y[M,N] = epilogue(q[M,K] (int8) x w[N,K]^T (int8 ternary)) on the 5th-generation
+// tensor cores.  tcgen05.mma kind::i8 (s8 x s8 -> s32), both operands K-major in shared memory in
+// the 128-byte-swizzled canonical layout written by TMA, accumulators in tensor memory (TMEM).
+//
+// One persistent CTA per SM, six warps:
+//   warp 0    TMA producer: per k-block one box of q [128 rows x 128 B] and one of w [BN x 128 B]
+//   warp 1    MMA issuer (one lane): 4 x tcgen05.mma (K = 32 each) per k-block, tcgen05.commit
+//             releases the stage; also owns the TMEM allocation (512 columns = 2 accumulators)
+//   warps 2-5 epilogue: tcgen05.ld the 128 x BN s32 tile (one TMEM lane quarter per warp), apply
+//             float(acc) * (act_scale*weight_scale) [* magnitude] [+ bias], stage 32x32 fp32 blocks
+//             in swizzled shared memory and write them with TMA stores (clipped at the edges)
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// Every wait is bounded: on a timeout the role records the status word and falls through to
+// the common exit, where TMEM is released.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
+
 namespace tbl {
-cudaError_t launch_gemm_tcgen05(const int8_t*, const float*, const int8_t*, float, const float*, const float*,
-                                int, int, int, float*, int32_t*, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+constexpr int BM = 128;          // activation rows per tile (UMMA M)
+constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
+constexpr int kStages = 4;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kNumSm = 148;
+
+struct GemmParams {
+    const float* act_scales;
+    const float* magnitude;
+    const float* bias;
+    float* y;
+    int32_t* acc_debug;
+    float weight_scale;
+    int M, K, N;
+    int tiles_m, tiles_n;
+    int use_tma_store;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
 }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_u32(src))
+                 : "memory");
+}
+
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    // K-major, 128-byte swizzle: 8-row groups are 1024 B apart (SBO = 64 x 16 B); LBO unused (1);
+    // descriptor version 1; layout type 2 = SWIZZLE_128B
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment is required by the 128-byte swizzle pattern
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kABytes = BM * BK;
+    constexpr int kBBytes = BN * BK;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    uint8_t* epi_stage = smem + kStages * kStageBytes;                 // 4 warps x 4 KB
+    uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + kEpiWarps * 4096);
+    uint64_t* empty = full + kStages;
+    uint64_t* tmem_full = empty + kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kblocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], kEpiWarps); }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages) {
+                        alive = mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1, p.status);
+                        if (!alive) break;
+                    }
+                    uint8_t* a_dst = smem + s * kStageBytes;
+                    uint8_t* b_dst = a_dst + kABytes;
+                    mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full[s]);
+                    tma_load_2d(b_dst, &map_b, kb * BK, tn * BN, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // kind::i8 instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = BN, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(BM >> 4) << 24);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) {
+                    alive = mbar_wait_bounded(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status);
+                    if (!alive) break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    alive = mbar_wait_bounded(&full[s], (it / kStages) & 1, p.status);
+                    if (!alive) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 32; ++kk) {
+                        umma_i8(d_tmem, smem_desc_sw128(a_addr + kk * 32), smem_desc_sw128(b_addr + kk * 32), idesc,
+                                (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);   // stage reusable once these MMAs have read it
+                }
+                if (alive) umma_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are this warp's
+        uint8_t* stage = epi_stage + (warp - 2) * 4096;
+        int local = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int buf = local & 1;
+            alive = mbar_wait_bounded(&tmem_full[buf], (local >> 1) & 1, p.status);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            tc_fence_after();
+            const int m = tm * BM + quarter * 32 + lane;
+            const float comb = m < p.M ? __fmul_rn(__ldg(p.act_scales + m), p.weight_scale) : 0.0f;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = tn * BN + c * 32;
+                if (n0 >= p.N) break;
+                uint32_t r[32];
+                tmem_ld32(t_row + c * 32, r);
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int n = n0 + i;
+                    v[i] = n < p.N ? epilogue(static_cast<int>(r[i]), comb, p.magnitude, p.bias, n) : 0.0f;
+                }
+                if (p.acc_debug && m < p.M) {
+                    for (int i = 0; i < 32; ++i)
+                        if (n0 + i < p.N) p.acc_debug[static_cast<size_t>(m) * p.N + n0 + i] = static_cast<int>(r[i]);
+                }
+                if (p.use_tma_store) {
+                    // the previous block's store must have finished reading the staging buffer
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+                    // row = lane; 16-byte chunk j of the 128-byte row goes to chunk j ^ (row & 7)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = f;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_y, n0, tm * BM + quarter * 32, stage);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (m < p.M) {
+                    for (int i = 0; i < 32; ++i)
+                        if (n0 + i < p.N) p.y[static_cast<size_t>(m) * p.N + n0 + i] = v[i];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    // common exit: all roles meet, then the allocating warp releases TMEM
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D tensor map over a row-major [rows, cols] array with `elem` bytes per element.
+bool make_map(CUtensorMap* map, CUtensorMapDataType type, int elem, const void* base, uint64_t rows,
+              uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const GemmParams& p,
+                      cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<BN>;
+    const size_t smem = 1024 + kStages * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = tiles < kNumSm ? tiles : kNumSm;
+    kernel<<<grid, kThreads, smem, stream>>>(ma, mb, my, p);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8, float weight_scale,
+                                const float* magnitude, const float* bias, int M, int K, int N, float* y,
+                                int32_t* acc_debug, cudaStream_t stream) {
+    GemmParams p{};
+    p.act_scales = act_scales; p.magnitude = magnitude; p.bias = bias; p.y = y; p.acc_debug = acc_debug;
+    p.weight_scale = weight_scale; p.M = M; p.K = K; p.N = N;
+    p.status = device_status_ptr();
+    if (!p.status) return cudaErrorUnknown;
+    const int bn = N > 128 ? 256 : 128;
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = (N + bn - 1) / bn;
+    // TMA stores need a 16-byte row pitch and base
+    p.use_tma_store = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    CUtensorMap ma, mb, my;
+    if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, M, K, BK, BM)) return cudaErrorUnknown;
+    if (!make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_i8, N, K, BK, bn)) return cudaErrorUnknown;
+    if (p.use_tma_store) {
+        if (!make_map(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, M, N, 32, 32)) return cudaErrorUnknown;
+    } else {
+        my = ma;  // unused
+    }
+    return bn == 256 ? launch_bn<256>(ma, mb, my, p, stream) : launch_bn<128>(ma, mb, my, p, stream);
+}
+
+}  // namespace tbl

@@ -1,0 +1,335 @@
+// Decode GEMV / small-M GEMM (1 <= M <= 64 activation rows per pass) on the strip-major device
+// layout of the 2-bit weights: HBM-bound streaming with int8 tensor-core MMAs ("swap-AB").
+//
+// Layout ("strips", produced once per matrix by relayout_strips): rows are grouped in strips of 16;
+// a strip is stored as K/256 blocks of 1 KB; block b holds, for lane = 4g+t of a warp, the 16-byte
+// chunk (64 weights, k = 256b + 64t ..) of row g at byte lane*16 and of row g+8 at 512 + lane*16.
+// A strip is therefore one contiguous run of 4K bytes that a warp consumes front to back, and the
+// two 128-bit shared loads of a lane are its m16n8k32 A-fragment source (rows g / g+8) with no
+// bank conflicts.  A stage of the ring holds KS weights of up to 8 strips (one bulk copy per
+// strip, 4 KB at KS = 1024) plus the matching slab of activations (one bulk copy).
+//
+// Widening: for 2-bit position j, (word & (0x03030303 << 2j)) is the unsigned byte vector
+// 4^j * code of weights {j,4+j,8+j,12+j} of that word.  With one accumulator set per j the four
+// partial sums are exact multiples of 4^j and are recombined with shifts (SCALED variant, one AND
+// per A register); the NT = 8 variant shifts instead to keep a single accumulator set.  The
+// constant "-1" of the code is removed in the epilogue by subtracting sum_k q[m,k].
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+namespace {
+
+constexpr int kMaxStages = 4;
+constexpr int kStripWarps = 8;
+constexpr int kNumSm = 148;
+
+struct StripParams {
+    StripProblem prob[TBL_MAX_GROUPS];
+    int count;
+    int total_strips;
+    int ks;       // k per stage, multiple of 256
+    int stages;
+    int* status;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, bool SCALED>
+__global__ void __launch_bounds__((kStripWarps + 1) * 32, 1)
+gemv_strip_kernel(const __grid_constant__ StripParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int MPAD = 8 * NT;
+    constexpr int NJ = SCALED ? 4 : 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk_stage = P.ks >> 8;
+    const int wstage = kStripWarps * nblk_stage * 1024;           // weight bytes of a stage
+    const int stage_bytes = wstage + nblk_stage * MPAD * 256;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kMaxStages;
+    uint8_t* stage_base = smem + 128;
+    const int nstages = P.stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kStripWarps);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    // contiguous, balanced share of the global strip list
+    const int s_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_strips / gridDim.x);
+    const int s_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_strips / gridDim.x);
+    const bool producer = warp == kStripWarps;
+    const int g = lane >> 2, t = lane & 3;
+
+    int it = 0;
+    bool alive = true;
+    int pi = 0;
+    for (int s = s_begin; s < s_end && alive;) {
+        while (pi + 1 < P.count && s >= P.prob[pi + 1].strip_begin) ++pi;
+        const StripProblem& pr = P.prob[pi];
+        const int K = pr.K, N = pr.N;
+        const int nstrips = (N + 15) >> 4;
+        const int local = s - pr.strip_begin;
+        const int cnt = min(kStripWarps, min(s_end - s, nstrips - local));
+        s += cnt;
+        int rows = pr.rows;
+        if (pr.rows_dev) rows = min(rows, __ldg(pr.rows_dev));
+        if (rows <= 0) continue;
+        const int row0 = pr.offset_dev ? __ldg(pr.offset_dev) : 0;
+        const int nblk = K >> 8;
+        const int ksteps = (nblk + nblk_stage - 1) / nblk_stage;
+        const int mtiles = (rows + MPAD - 1) / MPAD;   // > 1 only in the NT = 8 variant
+        const uint8_t* wsrc = pr.strips + (static_cast<size_t>(local) * nblk << 10);
+        const int8_t* qsrc = pr.qp + static_cast<size_t>(row0) * K;
+
+        for (int mt = 0; mt < mtiles && alive; ++mt) {
+            const int R = min(MPAD, rows - mt * MPAD);
+            const int8_t* qtile = qsrc + static_cast<size_t>(mt) * MPAD * K;
+
+            if (producer) {
+                for (int ksi = 0; ksi < ksteps; ++ksi, ++it) {
+                    const int st = it % nstages;
+                    if (it >= nstages) {
+                        alive = mbar_wait_bounded(&empty[st], ((it / nstages) - 1) & 1, P.status);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                    }
+                    const int b0 = ksi * nblk_stage;
+                    const int nb = min(nblk_stage, nblk - b0);
+                    uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes;
+                    if (lane == 0)
+                        mbar_arrive_expect_tx(&full[st], static_cast<uint32_t>(cnt) * nb * 1024 +
+                                                             static_cast<uint32_t>(nb) * R * 256);
+                    __syncwarp();
+                    if (lane < cnt)
+                        bulk_g2s(wst + lane * nblk_stage * 1024,
+                                 wsrc + ((static_cast<size_t>(lane) * nblk + b0) << 10), nb * 1024, &full[st]);
+                    if (lane == kStripWarps)
+                        bulk_g2s(wst + wstage, qtile + static_cast<size_t>(b0) * R * 256, nb * R * 256,
+                                 &full[st]);
+                }
+                continue;
+            }
+
+            // ---------------- consumer warps ----------------
+            const bool active = warp < cnt;
+            int acc[NJ][NT][4];
+#pragma unroll
+            for (int j = 0; j < NJ; ++j)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) acc[j][nt][0] = acc[j][nt][1] = acc[j][nt][2] = acc[j][nt][3] = 0;
+
+            for (int ksi = 0; ksi < ksteps; ++ksi, ++it) {
+                const int st = it % nstages;
+                alive = mbar_wait_bounded(&full[st], (it / nstages) & 1, P.status);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                if (active) {
+                    const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
+                    const uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes +
+                                         warp * nblk_stage * 1024 + lane * 16;
+                    const uint8_t* ast = stage_base + static_cast<size_t>(st) * stage_bytes + wstage;
+                    for (int b = 0; b < nb; ++b) {
+                        const uint4 lo = *reinterpret_cast<const uint4*>(wst + b * 1024);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(wst + b * 1024 + 512);
+                        const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
+                        const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
+                        const uint8_t* ablk = ast + static_cast<size_t>(b) * R * 256;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const int m = nt * 8 + g;
+                            uint4 B[4];
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                B[x] = make_uint4(0, 0, 0, 0);
+                                if (m < R)
+                                    B[x] = *reinterpret_cast<const uint4*>(ablk + m * 256 +
+                                                                           (((x ^ (m & 1)) << 2) + t) * 16);
+                            }
+                            const uint32_t bw[4][4] = {{B[0].x, B[0].y, B[0].z, B[0].w},
+                                                       {B[1].x, B[1].y, B[1].z, B[1].w},
+                                                       {B[2].x, B[2].y, B[2].z, B[2].w},
+                                                       {B[3].x, B[3].y, B[3].z, B[3].w}};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (SCALED) {
+                                    const uint32_t mk = 0x03030303u << (2 * j);
+                                    mma_u8s8(acc[j][nt], lw[0] & mk, hw[0] & mk, lw[1] & mk, hw[1] & mk,
+                                             bw[0][j], bw[1][j]);
+                                    mma_u8s8(acc[j][nt], lw[2] & mk, hw[2] & mk, lw[3] & mk, hw[3] & mk,
+                                             bw[2][j], bw[3][j]);
+                                } else {
+                                    const uint32_t mk = 0x03030303u;
+                                    mma_u8s8(acc[0][nt], (lw[0] >> (2 * j)) & mk, (hw[0] >> (2 * j)) & mk,
+                                             (lw[1] >> (2 * j)) & mk, (hw[1] >> (2 * j)) & mk, bw[0][j], bw[1][j]);
+                                    mma_u8s8(acc[0][nt], (lw[2] >> (2 * j)) & mk, (hw[2] >> (2 * j)) & mk,
+                                             (lw[3] >> (2 * j)) & mk, (hw[3] >> (2 * j)) & mk, bw[2][j], bw[3][j]);
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
+            }
+            if (!alive) break;
+
+            if (active) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int n = (local + warp) * 16 + g + 8 * h;
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int m = nt * 8 + 2 * t + c;
+                            if (n < N && m < R) {
+                                const int e = 2 * h + c;
+                                int total;
+                                if (SCALED)
+                                    total = acc[0][nt][e] + (acc[NJ > 1 ? 1 : 0][nt][e] >> 2) +
+                                            (acc[NJ > 2 ? 2 : 0][nt][e] >> 4) + (acc[NJ > 3 ? 3 : 0][nt][e] >> 6);
+                                else
+                                    total = acc[0][nt][e];
+                                const int gm = row0 + mt * MPAD + m;
+                                total -= __ldg(pr.q_sums + gm);
+                                if (pr.acc_debug) pr.acc_debug[static_cast<size_t>(gm) * pr.ldy + n] = total;
+                                float v = epilogue(total, __fmul_rn(__ldg(pr.act_scales + gm), pr.weight_scale),
+                                                   pr.magnitude, pr.bias, n);
+                                if (pr.squared_relu) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
+                                pr.y[static_cast<size_t>(gm) * pr.ldy + n] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// canonical [N, K/16] words -> strip layout; one thread per 16-byte chunk of the output.
+__global__ void __launch_bounds__(256)
+relayout_strips_kernel(const uint4* __restrict__ words, int N, int K, uint4* __restrict__ strips, int64_t chunks) {
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (o >= chunks) return;
+    const int cpr = K >> 6;               // chunks per row
+    const int64_t cps = static_cast<int64_t>(cpr) * 16;   // chunks per strip
+    const int s = static_cast<int>(o / cps);
+    const int in = static_cast<int>(o % cps);
+    const int b = in >> 6, within = in & 63;
+    const int h = within >> 5, ln = within & 31;
+    const int row = s * 16 + h * 8 + (ln >> 2);
+    const int c = 4 * b + (ln & 3);
+    uint4 v = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // code 1 = weight 0
+    if (row < N) v = __ldg(words + static_cast<size_t>(row) * cpr + c);
+    strips[o] = v;
+}
+
+// q row-major [M,K] -> tile-exact interleaved order + per-row sums; one CTA per row.
+__global__ void __launch_bounds__(256) permute_q_kernel(const int8_t* __restrict__ q, int M, int K,
+                                                        int8_t* __restrict__ qp, int32_t* __restrict__ q_sums) {
+    __shared__ int partial[8];
+    const int row = blockIdx.x;
+    const int8_t* src = q + static_cast<size_t>(row) * K;
+    int sum = 0;
+    for (int j = threadIdx.x * 16; j < K; j += 256 * 16) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + j));
+        sum = dp4a_ss(static_cast<int>(v.x), 0x01010101, sum);
+        sum = dp4a_ss(static_cast<int>(v.y), 0x01010101, sum);
+        sum = dp4a_ss(static_cast<int>(v.z), 0x01010101, sum);
+        sum = dp4a_ss(static_cast<int>(v.w), 0x01010101, sum);
+        *reinterpret_cast<uint4*>(qp + qp_offset(row, M, K, j)) = transpose4x4_bytes(v);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int w = 0; w < 8; ++w) s += partial[w];
+        q_sums[row] = s;
+    }
+}
+
+template <int NT, bool SCALED>
+cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStream_t stream) {
+    auto kernel = gemv_strip_kernel<NT, SCALED>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, (kStripWarps + 1) * 32, smem, stream>>>(P);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemv_strip_supported(int K) { return K > 0 && K % 256 == 0 && K <= 65536; }
+
+cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* strips, cudaStream_t stream) {
+    const int64_t chunks = static_cast<int64_t>((N + 15) / 16) * 16 * (K / 64);
+    const int blocks = static_cast<int>((chunks + 255) / 256);
+    relayout_strips_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(words), N, K,
+                                                       static_cast<uint4*>(strips), chunks);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t* q_sums, cudaStream_t stream) {
+    permute_q_kernel<<<M, 256, 0, stream>>>(q, M, K, qp, q_sums);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t stream) {
+    if (count < 1 || count > TBL_MAX_GROUPS) return cudaErrorInvalidValue;
+    StripParams P{};
+    P.count = count;
+    P.status = device_status_ptr();
+    if (!P.status) return cudaErrorUnknown;
+    int max_rows = 1, total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!gemv_strip_supported(problems[i].K)) return cudaErrorInvalidValue;
+        max_rows = problems[i].rows > max_rows ? problems[i].rows : max_rows;
+        P.prob[i] = problems[i];
+        P.prob[i].strip_begin = total;
+        total += (problems[i].N + 15) / 16;
+    }
+    P.total_strips = total;
+    const int nt = max_rows <= 8 ? 1 : (max_rows <= 16 ? 2 : (max_rows <= 32 ? 4 : 8));
+    // stage depth in k: 1024 keeps each strip copy at 4 KB; shrink for tall activation tiles
+    P.ks = nt <= 2 ? 1024 : 512;
+    const size_t stage_bytes = static_cast<size_t>(kStripWarps) * (P.ks / 256) * 1024 +
+                               static_cast<size_t>(P.ks / 256) * (8 * nt) * 256;
+    P.stages = kMaxStages;
+    while (P.stages > 2 && 128 + P.stages * stage_bytes > 220 * 1024) --P.stages;
+    const size_t smem = 128 + P.stages * stage_bytes;
+    int grid = (total + kStripWarps - 1) / kStripWarps;
+    if (grid > kNumSm) grid = kNumSm;
+    // spread small problems over more SMs (fewer strips per CTA)
+    if (total < kNumSm * kStripWarps) grid = total < kNumSm ? total : kNumSm;
+    switch (nt) {
+        case 1: return launch_variant<1, true>(P, grid, smem, stream);
+        case 2: return launch_variant<2, true>(P, grid, smem, stream);
+        case 4: return launch_variant<4, true>(P, grid, smem, stream);
+        default: return launch_variant<8, false>(P, grid, smem, stream);
+    }
+}
+
+}  // namespace tbl

@@ -8,22 +8,39 @@
 
 namespace tbl {
 
-// ---- interleaved activation order used by the tensor-core GEMV -------------------------------
-// Inside every 256-element block of a row, the sixteen 16-element groups (chunk t = 0..3 of 64
-// elements, quarter i = 0..3) are stored at group position i*4 + t, and each group is 4x4
-// byte-transposed.  Offset (in bytes) of the group that starts at element j (j % 16 == 0):
-__host__ __device__ __forceinline__ int qp_offset16(int j) {
-    const int b = j >> 8, r = j & 255;
+// ---- interleaved activation order read by the strip GEMV ------------------------------------
+// Rows are grouped in tiles of kQpTile; a tile with R rows is stored block-major over K:
+// [k/256][R][256 bytes], so the activations of one k-slab of a tile are contiguous (one bulk copy).
+// Inside a 256-byte row-block the sixteen 16-element groups (chunk t = 0..3 of 64 elements,
+// quarter i = 0..3) sit at group position ((i ^ (m & 1)) * 4 + t) -- the XOR spreads odd and even
+// rows over different shared-memory banks -- and each group is 4x4 byte-transposed so that byte e
+// of word j is element 4e + j (the order the 2-bit extraction pairs weights in).
+// Byte offset of the group starting at element j (j % 16 == 0) of row `row` out of `rows`:
+constexpr int kQpTile = 64;
+__host__ __device__ __forceinline__ size_t qp_offset(int row, int rows, int K, int j) {
+    const int mt = row / kQpTile, m = row % kQpTile;
+    const int remaining = rows - mt * kQpTile;
+    const int R = remaining < kQpTile ? remaining : kQpTile;
+    const int kb = j >> 8, r = j & 255;
     const int t = r >> 6, i = (r >> 4) & 3;
-    return (b << 8) + (i << 6) + (t << 4);
+    return static_cast<size_t>(mt) * kQpTile * K + static_cast<size_t>(kb) * R * 256 + m * 256 +
+           ((((i ^ (m & 1)) << 2) + t) << 4);
 }
 
 // quantize.cu
 // active_rows (device, may be null): rows >= *active_rows are skipped.
+// qp (may be null) receives the interleaved copy; its tiling follows the row's problem: either the
+// whole call is one problem of M rows, or seg_offsets/seg_counts (device, `segs` entries) give the
+// first row and row count of each problem.
+struct QuantSegments {
+    const int32_t* offsets;
+    const int32_t* counts;
+    int segs;
+};
 cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
                                  int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
                                  int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
-                                 cudaStream_t stream);
+                                 QuantSegments segments, cudaStream_t stream);
 cudaError_t launch_expand_i8(const uint32_t* words, int N, int K, int8_t* out, cudaStream_t stream);
 
 // gemv_stream.cu — M <= 4, CUDA-core dp4a, weights streamed by per-warp TMA rings.
@@ -54,10 +71,11 @@ cudaError_t launch_gemv_generic(const int8_t* q, const float* act_scales, const 
                                 int M, int K, int N, float* y, int32_t* acc_debug, int squared_relu,
                                 const int32_t* rows_dev, const int32_t* offset_dev, cudaStream_t stream);
 
-// gemv_mma.cu — 1 <= M <= 64 per pass, int8 mma.sync tensor cores, grouped problem table.
-struct MmaProblem {
-    const uint32_t* words;    // canonical packed [N, K/16]
-    const int8_t* qp;         // interleaved int8 activations [rows, K]
+// gemv_strip.cu -- 1 <= M <= 64 rows per pass, int8 mma.sync tensor cores, strip-major weights,
+// problem table for grouped launches.
+struct StripProblem {
+    const uint8_t* strips;    // strip-major packed weights (launch_relayout_strips)
+    const int8_t* qp;         // interleaved int8 activations
     const float* act_scales;  // [rows]
     const int32_t* q_sums;    // [rows]
     const float* magnitude;
@@ -70,10 +88,11 @@ struct MmaProblem {
     int rows;                 // host-known row count (upper bound when rows_dev is set)
     int N, K, ldy;
     int squared_relu;
-    int cta_begin;            // first CTA index of this problem (filled by the launcher)
+    int strip_begin;          // global index of this problem's first strip (filled by the launcher)
 };
-bool gemv_mma_supported(int K);
-cudaError_t launch_gemv_mma(MmaProblem* problems, int count, cudaStream_t stream);
+bool gemv_strip_supported(int K);
+cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* strips, cudaStream_t stream);
+cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t stream);
 cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t* q_sums, cudaStream_t stream);
 
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.

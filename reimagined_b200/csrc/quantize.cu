@@ -95,19 +95,29 @@ __global__ void rms_reference_order_kernel(const float* __restrict__ x,
 }
 
 // One CTA per output row.  VEC16: K % 16 == 0 and 16-byte aligned rows -> 128-bit loads and
-// stores, optional second output in the tensor-core GEMV's interleaved order (qp).
+// stores, optional second output in the strip GEMV's interleaved order (qp).
 template <bool VEC16>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index, int K,
                      float q_max, int rms_mode, bool tie_away, const float* __restrict__ inv_norm_in,
                      int8_t* __restrict__ q, int8_t* __restrict__ qp, float* __restrict__ act_scales,
-                     int32_t* __restrict__ q_sums, const int32_t* __restrict__ active_rows) {
+                     int32_t* __restrict__ q_sums, const int32_t* __restrict__ active_rows,
+                     int qp_rows, QuantSegments seg) {
     __shared__ float scratch[kQuantThreads / 32];
     __shared__ int sum_scratch[kQuantThreads / 32];
     const int row = blockIdx.x;
     if (active_rows && row >= *active_rows) return;
     const int src = row_index ? row_index[row] : row;
     const float* xr = x + static_cast<size_t>(src) * K;
+    // position of this row inside its problem (for the interleaved copy)
+    int prow = row, prows = qp_rows;
+    size_t pbase = 0;
+    if (VEC16 && qp && seg.offsets) {
+        for (int e = 0; e < seg.segs; ++e) {
+            const int o = seg.offsets[e], c = seg.counts[e];
+            if (row >= o && row < o + c) { prow = row - o; prows = c; pbase = static_cast<size_t>(o) * K; break; }
+        }
+    }
 
     float inv = 1.0f;
     if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
@@ -171,7 +181,7 @@ quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ ro
             const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
             if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
             if (qp) {
-                *reinterpret_cast<uint4*>(qp + static_cast<size_t>(row) * K + qp_offset16(j)) =
+                *reinterpret_cast<uint4*>(qp + pbase + qp_offset(prow, prows, K, j)) =
                     transpose4x4_bytes(natural);
             }
         }
@@ -235,7 +245,7 @@ __global__ void expand_i8_tail_kernel(const uint32_t* __restrict__ words, int64_
 cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
                                  int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
                                  int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
-                                 cudaStream_t stream) {
+                                 QuantSegments segments, cudaStream_t stream) {
     if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
         rms_reference_order_kernel<<<(M + 63) / 64, 64, 0, stream>>>(x, row_index, M, K, 1e-6f,
                                                                      inv_norm_scratch, active_rows);
@@ -248,11 +258,11 @@ cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M
     if (vec) {
         quantize_rows_kernel<true><<<M, kQuantThreads, 0, stream>>>(
             x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, qp,
-            act_scales, q_sums, active_rows);
+            act_scales, q_sums, active_rows, M, segments);
     } else {
         quantize_rows_kernel<false><<<M, kQuantThreads, 0, stream>>>(
             x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, nullptr,
-            act_scales, q_sums, active_rows);
+            act_scales, q_sums, active_rows, M, segments);
     }
     note_launch();
     return cudaGetLastError();

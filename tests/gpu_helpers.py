@@ -43,14 +43,23 @@ def quantize_rows(x, bits=8, rms_mode=0, tie_mode=0, row_index=None):
     return q, sc, sums
 
 
-def gemv(q, sc, words, weight_scale, N, magnitude=None, bias=None, want_acc=True):
+def relayout_strips(words, N, K):
+    L = capi.lib()
+    nbytes = L.tbl_strip_bytes(N, K)
+    assert nbytes > 0
+    out = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.check(L.tbl_relayout_strips(ptr(words), N, K, ptr(out), stream_ptr()), "tbl_relayout_strips")
+    return out
+
+
+def gemv(q, sc, words, weight_scale, N, magnitude=None, bias=None, want_acc=True, strips=None):
     L = capi.lib()
     M, K = q.shape
     y = torch.empty((M, N), dtype=torch.float32, device="cuda")
     acc = torch.empty((M, N), dtype=torch.int32, device="cuda") if want_acc else None
     nbytes = L.tbl_gemv_workspace_bytes(M, K)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
-    capi.check(L.tbl_gemv(ptr(q), ptr(sc), ptr(words), float(weight_scale), ptr(magnitude), ptr(bias), M, K, N,
+    capi.check(L.tbl_gemv(ptr(q), ptr(sc), ptr(words), ptr(strips), float(weight_scale), ptr(magnitude), ptr(bias), M, K, N,
                           ptr(y), ptr(acc), ptr(ws), nbytes, stream_ptr()), "tbl_gemv")
     return y, acc
 
@@ -73,21 +82,23 @@ def gemm(q, sc, w_i8, weight_scale, magnitude=None, bias=None, want_acc=True):
     return y, acc
 
 
-def linear_forward(x, words, weight_scale, N, w_i8=None, bits=8, rms_mode=0, magnitude=None, bias=None):
+def linear_forward(x, words, weight_scale, N, w_i8=None, bits=8, rms_mode=0, magnitude=None, bias=None,
+                   strips=None):
     L = capi.lib()
     M, K = x.shape
     y = torch.empty((M, N), dtype=torch.float32, device="cuda")
     nbytes = L.tbl_linear_workspace_bytes(M, K, N)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
-    capi.check(L.tbl_linear_forward(ptr(x), ptr(words), ptr(w_i8), float(weight_scale), M, K, N, bits, rms_mode,
+    capi.check(L.tbl_linear_forward(ptr(x), ptr(words), ptr(strips), ptr(w_i8), float(weight_scale), M, K, N, bits, rms_mode,
                                     ptr(magnitude), ptr(bias), ptr(y), ptr(ws), nbytes, stream_ptr()),
                "tbl_linear_forward")
     return y
 
 
-def make_view(words_t, inputs, outputs, weight_scale, bits=8, rms_input=0, magnitude=None, bias=None):
+def make_view(words_t, inputs, outputs, weight_scale, bits=8, rms_input=0, magnitude=None, bias=None,
+              strips=None):
     return capi.LinearView(None, ptr(words_t), ptr(magnitude) or None, ptr(bias) or None, inputs, outputs, bits,
-                           rms_input, float(weight_scale))
+                           rms_input, float(weight_scale), ptr(strips) or None)
 
 
 def grouped_forward(views, x_row, output_stride, rms_mode=0):

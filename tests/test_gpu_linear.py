@@ -104,10 +104,10 @@ def test_gemv_on_codes_int32_exact(cuda, port, tbl, N, K, M):
 
 
 @pytest.mark.parametrize("N,K", [(768, 768), (1536, 768), (32000, 768), (100, 1024), (130, 2048), (16, 768),
-                                 (2048, 5632), (64, 16384), (47, 256)])
-@pytest.mark.parametrize("M", [5, 8, 16, 17, 33, 64])
-def test_gemv_tensor_path_mid_m(cuda, port, tbl, N, K, M):
-    """5 <= M <= 64 on the packed words (mma.sync path): accumulators and outputs bit-exact."""
+                                 (2048, 5632), (64, 16384), (47, 256), (3000, 512)])
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 8, 16, 17, 33, 64])
+def test_gemv_strip_tensor_path(cuda, port, tbl, N, K, M):
+    """1 <= M <= 64 on the strip-major weights (mma.sync path): accumulators and outputs bit-exact."""
     import gpu_helpers as H
     if N * K * M > 3e9:
         pytest.skip("oracle too slow at this size")
@@ -118,12 +118,47 @@ def test_gemv_tensor_path_mid_m(cuda, port, tbl, N, K, M):
     oy, *_ = port.linear_forward(x, words, scale, N, magnitude=mag, bias=bias)
     dm = None if mag is None else H.dev(mag)
     db = None if bias is None else H.dev(bias)
-    y, acc = H.gemv(H.dev(oq), H.dev(osc), H.words_dev(words), scale, N, dm, db)
+    dwords = H.words_dev(words)
+    strips = H.relayout_strips(dwords, N, K)
+    y, acc = H.gemv(H.dev(oq), H.dev(osc), None, scale, N, dm, db, strips=strips)
     assert np.array_equal(acc.cpu().numpy(), oacc)
     assert bits_equal(y.cpu().numpy(), oy)
-    y2 = H.linear_forward(H.dev(x), H.words_dev(words), scale, N, magnitude=dm, bias=db)
+    y2 = H.linear_forward(H.dev(x), None, scale, N, magnitude=dm, bias=db, strips=strips)
     assert bits_equal(y2.cpu().numpy(), oy)
     assert H.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K,M", [(100, 1024, 9), (33, 48, 12), (768, 768, 64), (17, 80, 5)])
+def test_gemv_canonical_words_any_m(cuda, port, tbl, N, K, M):
+    """Canonical words only (no strip copy): the generic kernel serves M > 4 and odd K."""
+    import gpu_helpers as H
+    w, x, mag, bias = make_case(N + K + M, N, K, M, affine=True)
+    words, scale, t, _ = port.pack_weights(w)
+    oq, osc = port.quantize_rows(x)
+    oy, *_ = port.linear_forward(x, words, scale, N, magnitude=mag, bias=bias)
+    y, acc = H.gemv(H.dev(oq), H.dev(osc), H.words_dev(words), scale, N, H.dev(mag), H.dev(bias))
+    assert np.array_equal(acc.cpu().numpy(), oq.astype(np.int32) @ t.astype(np.int32).T)
+    assert bits_equal(y.cpu().numpy(), oy)
+
+
+def test_strip_relayout_is_a_permutation(cuda, port, tbl):
+    """Every canonical 16-byte chunk appears exactly once in the strip copy; padding rows are zero weights."""
+    import gpu_helpers as H
+    N, K = 40, 512
+    words = np.arange(N * K // 16, dtype=np.uint32)  # distinct words (not valid codes: layout test only)
+    strips = H.relayout_strips(H.words_dev(words), N, K).cpu().numpy().view(np.uint32).reshape(-1, 4)
+    canon = words.reshape(-1, 4)
+    pad = (strips == 0x55555555).all(axis=1)
+    assert pad.sum() == (48 - N) * (K // 64)
+    got = strips[~pad]
+    order = np.lexsort(got.T[::-1])
+    assert np.array_equal(got[order], canon[np.lexsort(canon.T[::-1])])
+    # block 0 of strip 0: lane 4g+t holds chunk t of row g, then rows g+8 at +512 bytes
+    cpr = K // 64
+    for g in range(8):
+        for t_ in range(4):
+            assert np.array_equal(strips[4 * g + t_], canon[g * cpr + t_])
+            assert np.array_equal(strips[32 + 4 * g + t_], canon[(g + 8) * cpr + t_])
 
 
 @pytest.mark.parametrize("M", [65, 100, 200])
@@ -134,7 +169,11 @@ def test_packed_path_for_large_m_without_int8_copy(cuda, port, tbl, M):
     w, x, mag, bias = make_case(M, N, K, M, affine=True)
     words, scale, *_ = port.pack_weights(w)
     oy, *_ = port.linear_forward(x, words, scale, N, magnitude=mag, bias=bias)
-    y = H.linear_forward(H.dev(x), H.words_dev(words), scale, N, magnitude=H.dev(mag), bias=H.dev(bias))
+    dwords = H.words_dev(words)
+    y = H.linear_forward(H.dev(x), dwords, scale, N, magnitude=H.dev(mag), bias=H.dev(bias))
+    assert bits_equal(y.cpu().numpy(), oy)
+    y = H.linear_forward(H.dev(x), None, scale, N, magnitude=H.dev(mag), bias=H.dev(bias),
+                         strips=H.relayout_strips(dwords, N, K))
     assert bits_equal(y.cpu().numpy(), oy)
 
 
@@ -153,6 +192,11 @@ def test_linear_forward_matches_reference_golden(cuda, tbl, path):
     y = H.linear_forward(H.dev(g["x"]), words, float(g["weight_scale"]), N, w_i8=w_i8, bits=int(g["bits"]),
                          rms_mode=0 if exact else 2, magnitude=mag, bias=bias).cpu().numpy()
     assert bits_equal(y, g["y"]), f"max diff {np.abs(y - g['y']).max()}"
+    if K % 256 == 0:
+        ys = H.linear_forward(H.dev(g["x"]), None, float(g["weight_scale"]), N, bits=int(g["bits"]),
+                              rms_mode=0 if exact else 2, magnitude=mag, bias=bias,
+                              strips=H.relayout_strips(words, N, K)).cpu().numpy()
+        assert bits_equal(ys, g["y"]), f"strip path max diff {np.abs(ys - g['y']).max()}"
     if not exact:
         yf = H.linear_forward(H.dev(g["x"]), words, float(g["weight_scale"]), N, w_i8=w_i8, bits=int(g["bits"]),
                               rms_mode=1, magnitude=mag, bias=bias).cpu().numpy()
@@ -198,8 +242,9 @@ def test_roundtrip_properties_at_scale(cuda, port, tbl):
     words, scale, t, _ = port.pack_weights(w)
     dw = H.words_dev(words)
     oq, osc = port.quantize_rows(x)
-    y1, acc = H.gemv(H.dev(oq), H.dev(osc), dw, scale, N)
-    y2, _ = H.gemv(H.dev(oq), H.dev(osc), dw, 2 * float(scale), N)
+    strips = H.relayout_strips(dw, N, K)
+    y1, acc = H.gemv(H.dev(oq), H.dev(osc), None, scale, N, strips=strips)
+    y2, _ = H.gemv(H.dev(oq), H.dev(osc), None, 2 * float(scale), N, strips=strips)
     assert bits_equal(y2.cpu().numpy(), 2 * y1.cpu().numpy())  # scaling by 2 is exact in fp32
     rows = np.random.default_rng(0).choice(N, 64, replace=False)
     oacc = oq.astype(np.int32) @ t[rows].astype(np.int32).T

@@ -94,20 +94,20 @@ def test_device_entry_points_validate_before_launching(tbl):
     P = 0x1000  # 16-byte aligned dummy
     before = tbl.tbl_launch_count()
     lf = tbl.tbl_linear_forward
-    assert lf(P, P, None, 0.5, 1, 24, 8, 8, 0, None, None, P, None, 0, None) == -2     # K % 16
-    assert lf(P, P, None, 0.5, 0, 32, 8, 8, 0, None, None, P, None, 0, None) == -1     # M <= 0
-    assert lf(P, P, None, -1.0, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -4    # scale
-    assert lf(P, P, None, 0.5, 1, 32, 8, 9, 0, None, None, P, None, 0, None) == -5     # bits
-    assert lf(P, P, None, 0.5, 1, 32, 8, 1, 0, None, None, P, None, 0, None) == -5
-    assert lf(P, P, None, 0.5, 1, 8454672, 8, 8, 0, None, None, P, None, 0, None) == -3  # K > INT_MAX/254
-    assert lf(P, P, None, 0.5, 65536, 32, 65536, 8, 0, None, None, P, None, 0, None) == -2  # M*N > INT_MAX
-    assert lf(None, P, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -1
-    assert lf(P + 4, P, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -6  # alignment
-    assert lf(P, P, None, 0.5, 8, 32, 8, 8, 0, None, None, P, None, 0, None) == -7      # needs workspace
-    assert tbl.tbl_gemv(P, P, P, 0.5, None, None, 65, 32, 8, P, None, None, 0, None) == -2  # M > 64
+    assert lf(P, P, None, None, 0.5, 1, 24, 8, 8, 0, None, None, P, None, 0, None) == -2     # K % 16
+    assert lf(P, P, None, None, 0.5, 0, 32, 8, 8, 0, None, None, P, None, 0, None) == -1     # M <= 0
+    assert lf(P, P, None, None, -1.0, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -4    # scale
+    assert lf(P, P, None, None, 0.5, 1, 32, 8, 9, 0, None, None, P, None, 0, None) == -5     # bits
+    assert lf(P, P, None, None, 0.5, 1, 32, 8, 1, 0, None, None, P, None, 0, None) == -5
+    assert lf(P, P, None, None, 0.5, 1, 8454672, 8, 8, 0, None, None, P, None, 0, None) == -3  # K > INT_MAX/254
+    assert lf(P, P, None, None, 0.5, 65536, 32, 65536, 8, 0, None, None, P, None, 0, None) == -2  # M*N > INT_MAX
+    assert lf(None, P, None, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -1
+    assert lf(P + 4, P, None, None, 0.5, 1, 32, 8, 8, 0, None, None, P, None, 0, None) == -6  # alignment
+    assert lf(P, P, None, None, 0.5, 8, 32, 8, 8, 0, None, None, P, None, 0, None) == -7      # needs workspace
+    assert tbl.tbl_gemv(P, P, P, None, 0.5, None, None, 65, 32, 8, P, None, None, 0, None) == -2  # M > 64
     assert tbl.tbl_quantize_rows(P, None, 1, 32, 8, 2, 0, P, P, None, None) == -1
     from reimagined_b200 import capi
-    v = capi.LinearView(P, None, None, None, 32, 8, 8, 0, 0.5)   # fp32-weight view: not implemented
+    v = capi.LinearView(P, None, None, None, 32, 8, 8, 0, 0.5, None)   # fp32-weight view: not implemented
     arr = (capi.LinearView * 1)(v)
     assert tbl.tbl_grouped_forward(arr, 1, P, P, 8, 0, P, 1 << 20, None) == -10
     assert tbl.tbl_launch_count() == before
