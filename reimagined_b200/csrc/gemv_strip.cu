@@ -21,7 +21,7 @@ namespace tbl {
 namespace {
 
 constexpr int kMaxStages = 4;
-constexpr int kStripWarps = 8;
+constexpr int kStripSlots = 8;     // strips processed concurrently by a CTA
 constexpr int kNumSm = 148;
 
 struct StripParams {
@@ -41,25 +41,30 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, bool SCALED>
-__global__ void __launch_bounds__((kStripWarps + 1) * 32, 1)
+// WPS warps share one strip: warp `part` of a strip takes the 1 KB blocks b with b % WPS == part and
+// the partial sums meet in shared memory before the epilogue (more warps in flight per SM).
+template <int NT, bool SCALED, int WPS>
+__global__ void __launch_bounds__((kStripSlots * WPS + 1) * 32, 1)
 gemv_strip_kernel(const __grid_constant__ StripParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MPAD = 8 * NT;
     constexpr int NJ = SCALED ? 4 : 1;
+    constexpr int kConsumers = kStripSlots * WPS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblk_stage = P.ks >> 8;
-    const int wstage = kStripWarps * nblk_stage * 1024;           // weight bytes of a stage
+    const int wstage = kStripSlots * nblk_stage * 1024;           // weight bytes of a stage
     const int stage_bytes = wstage + nblk_stage * MPAD * 256;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
-    uint8_t* stage_base = smem + 128;
+    int* reduce_buf = reinterpret_cast<int*>(smem + 128);        // [slot][WPS-1][32 lanes][4*NT]
+    constexpr int kReduceBytes = WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
+    uint8_t* stage_base = smem + 128 + kReduceBytes;
     const int nstages = P.stages;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kStripWarps);
+            mbar_init(&empty[s], kConsumers);
         }
         fence_mbar_init();
         fence_proxy_async();
@@ -69,7 +74,8 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     // contiguous, balanced share of the global strip list
     const int s_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_strips / gridDim.x);
     const int s_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_strips / gridDim.x);
-    const bool producer = warp == kStripWarps;
+    const bool producer = warp == kConsumers;
+    const int slot = warp / WPS, part = warp % WPS;
     const int g = lane >> 2, t = lane & 3;
 
     int it = 0;
@@ -81,7 +87,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         const int K = pr.K, N = pr.N;
         const int nstrips = (N + 15) >> 4;
         const int local = s - pr.strip_begin;
-        const int cnt = min(kStripWarps, min(s_end - s, nstrips - local));
+        const int cnt = min(kStripSlots, min(s_end - s, nstrips - local));
         s += cnt;
         int rows = pr.rows;
         if (pr.rows_dev) rows = min(rows, __ldg(pr.rows_dev));
@@ -115,7 +121,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                     if (lane < cnt)
                         bulk_g2s(wst + lane * nblk_stage * 1024,
                                  wsrc + ((static_cast<size_t>(lane) * nblk + b0) << 10), nb * 1024, &full[st]);
-                    if (lane == kStripWarps)
+                    if (lane == kStripSlots)
                         bulk_g2s(wst + wstage, qtile + static_cast<size_t>(b0) * R * 256, nb * R * 256,
                                  &full[st]);
                 }
@@ -123,7 +129,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
             }
 
             // ---------------- consumer warps ----------------
-            const bool active = warp < cnt;
+            const bool active = slot < cnt;
             int acc[NJ][NT][4];
 #pragma unroll
             for (int j = 0; j < NJ; ++j)
@@ -138,9 +144,11 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 if (active) {
                     const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
                     const uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes +
-                                         warp * nblk_stage * 1024 + lane * 16;
+                                         slot * nblk_stage * 1024 + lane * 16;
                     const uint8_t* ast = stage_base + static_cast<size_t>(st) * stage_bytes + wstage;
-                    for (int b = 0; b < nb; ++b) {
+                    // blocks of this stage are global blocks ksi*nblk_stage + b; this warp takes its residue class
+                    const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
+                    for (int b = first; b < nb; b += WPS) {
                         const uint4 lo = *reinterpret_cast<const uint4*>(wst + b * 1024);
                         const uint4 hi = *reinterpret_cast<const uint4*>(wst + b * 1024 + 512);
                         const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
@@ -186,22 +194,52 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
             if (!alive) break;
 
             if (active) {
+                // exact recombination of the scaled partial sums, then the cross-warp reduction
+                int tot[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (SCALED)
+                            tot[nt][e] = acc[0][nt][e] + (acc[NJ > 1 ? 1 : 0][nt][e] >> 2) +
+                                         (acc[NJ > 2 ? 2 : 0][nt][e] >> 4) + (acc[NJ > 3 ? 3 : 0][nt][e] >> 6);
+                        else
+                            tot[nt][e] = acc[0][nt][e];
+                    }
+                if (WPS > 1) {
+                    int* mine = reduce_buf + ((slot * (WPS - 1) + (part - 1)) * 32 + lane) * 4 * NT;
+                    if (part > 0) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                            *reinterpret_cast<int4*>(mine + 4 * nt) = make_int4(tot[nt][0], tot[nt][1], tot[nt][2], tot[nt][3]);
+                    }
+                    asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPS) : "memory");
+                    if (part == 0) {
+#pragma unroll
+                        for (int w = 0; w < WPS - 1; ++w) {
+                            const int* other = reduce_buf + ((slot * (WPS - 1) + w) * 32 + lane) * 4 * NT;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const int4 v = *reinterpret_cast<const int4*>(other + 4 * nt);
+                                tot[nt][0] += v.x; tot[nt][1] += v.y; tot[nt][2] += v.z; tot[nt][3] += v.w;
+                            }
+                        }
+                    }
+                    // the buffer is reused by the next pass: readers must be done before writers return
+                    asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPS) : "memory");
+                }
+                if (part == 0) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const int n = (local + warp) * 16 + g + 8 * h;
+                        const int n = (local + slot) * 16 + g + 8 * h;
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
                             const int m = nt * 8 + 2 * t + c;
                             if (n < N && m < R) {
                                 const int e = 2 * h + c;
-                                int total;
-                                if (SCALED)
-                                    total = acc[0][nt][e] + (acc[NJ > 1 ? 1 : 0][nt][e] >> 2) +
-                                            (acc[NJ > 2 ? 2 : 0][nt][e] >> 4) + (acc[NJ > 3 ? 3 : 0][nt][e] >> 6);
-                                else
-                                    total = acc[0][nt][e];
+                                int total = tot[nt][e];
                                 const int gm = row0 + mt * MPAD + m;
                                 total -= __ldg(pr.q_sums + gm);
                                 if (pr.acc_debug) pr.acc_debug[static_cast<size_t>(gm) * pr.ldy + n] = total;
@@ -212,6 +250,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                             }
                         }
                     }
+                }
                 }
             }
         }
@@ -262,9 +301,10 @@ __global__ void __launch_bounds__(256) permute_q_kernel(const int8_t* __restrict
     }
 }
 
-template <int NT, bool SCALED>
+template <int NT, bool SCALED, int WPS>
 cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStream_t stream) {
-    auto kernel = gemv_strip_kernel<NT, SCALED>;
+    auto kernel = gemv_strip_kernel<NT, SCALED, WPS>;
+    smem += WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -273,7 +313,7 @@ cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStre
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, (kStripWarps + 1) * 32, smem, stream>>>(P);
+    kernel<<<grid, (kStripSlots * WPS + 1) * 32, smem, stream>>>(P);
     note_launch();
     return cudaGetLastError();
 }
@@ -315,20 +355,20 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const int nt = max_rows <= 8 ? 1 : (max_rows <= 16 ? 2 : (max_rows <= 32 ? 4 : 8));
     // stage depth in k: 1024 keeps each strip copy at 4 KB; shrink for tall activation tiles
     P.ks = nt <= 2 ? 1024 : 512;
-    const size_t stage_bytes = static_cast<size_t>(kStripWarps) * (P.ks / 256) * 1024 +
+    const size_t stage_bytes = static_cast<size_t>(kStripSlots) * (P.ks / 256) * 1024 +
                                static_cast<size_t>(P.ks / 256) * (8 * nt) * 256;
     P.stages = kMaxStages;
-    while (P.stages > 2 && 128 + P.stages * stage_bytes > 220 * 1024) --P.stages;
+    while (P.stages > 2 && 128 + P.stages * stage_bytes > 200 * 1024) --P.stages;
     const size_t smem = 128 + P.stages * stage_bytes;
-    int grid = (total + kStripWarps - 1) / kStripWarps;
+    int grid = (total + kStripSlots - 1) / kStripSlots;
     if (grid > kNumSm) grid = kNumSm;
     // spread small problems over more SMs (fewer strips per CTA)
-    if (total < kNumSm * kStripWarps) grid = total < kNumSm ? total : kNumSm;
+    if (total < kNumSm * kStripSlots) grid = total < kNumSm ? total : kNumSm;
     switch (nt) {
-        case 1: return launch_variant<1, true>(P, grid, smem, stream);
-        case 2: return launch_variant<2, true>(P, grid, smem, stream);
-        case 4: return launch_variant<4, true>(P, grid, smem, stream);
-        default: return launch_variant<8, false>(P, grid, smem, stream);
+        case 1: return launch_variant<1, true, 2>(P, grid, smem, stream);
+        case 2: return launch_variant<2, true, 2>(P, grid, smem, stream);
+        case 4: return launch_variant<4, true, 1>(P, grid, smem, stream);
+        default: return launch_variant<8, false, 1>(P, grid, smem, stream);
     }
 }
 

@@ -210,6 +210,117 @@ quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ ro
     }
 }
 
+// Register-resident variant for K % 16 == 0 and K <= 16 * G * blockDim (G <= 2, so K <= 32768): every thread keeps its
+// G groups of 16 elements in registers, so the row is read from memory exactly once and the kernel
+// is a single load -> reduce -> quantise -> store chain (what matters at decode batch sizes, where
+// one row per CTA is pure latency).
+template <int G>
+__global__ void __launch_bounds__(1024)
+quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index, int K,
+                         float q_max, int rms_mode, bool tie_away, const float* __restrict__ inv_norm_in,
+                         int8_t* __restrict__ q, int8_t* __restrict__ qp, float* __restrict__ act_scales,
+                         int32_t* __restrict__ q_sums, const int32_t* __restrict__ active_rows,
+                         int qp_rows, QuantSegments seg) {
+    __shared__ float scratch[32];
+    __shared__ int sum_scratch[32];
+    const int row = blockIdx.x;
+    if (active_rows && row >= *active_rows) return;
+    const int src = row_index ? row_index[row] : row;
+    const float* xr = x + static_cast<size_t>(src) * K;
+    const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int prow = row, prows = qp_rows;
+    size_t pbase = 0;
+    if (qp && seg.offsets) {
+        for (int e = 0; e < seg.segs; ++e) {
+            const int o = seg.offsets[e], c = seg.counts[e];
+            if (row >= o && row < o + c) { prow = row - o; prows = c; pbase = static_cast<size_t>(o) * K; break; }
+        }
+    }
+
+    float4 v[G][4];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int j = (threadIdx.x + i * blockDim.x) * 16;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            v[i][e] = j < K ? __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    auto reduce = [&](float val, bool is_max) -> float {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, val, o);
+            val = is_max ? fmaxf(val, other) : val + other;
+        }
+        __syncthreads();
+        if (lane == 0) scratch[warp] = val;
+        __syncthreads();
+        float r = scratch[0];
+        for (int w = 1; w < nwarps; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+        return r;
+    };
+
+    float inv = 1.0f;
+    if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
+        inv = inv_norm_in[row];
+    } else if (rms_mode == TBL_RMS_FAST) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < G; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                ss += v[i][e].x * v[i][e].x + v[i][e].y * v[i][e].y + v[i][e].z * v[i][e].z + v[i][e].w * v[i][e].w;
+        ss = reduce(ss, false);
+        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), 1e-6f)));
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < G; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (rms_mode != TBL_RMS_NONE) {
+                v[i][e].x = __fmul_rn(v[i][e].x, inv); v[i][e].y = __fmul_rn(v[i][e].y, inv);
+                v[i][e].z = __fmul_rn(v[i][e].z, inv); v[i][e].w = __fmul_rn(v[i][e].w, inv);
+            }
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[i][e].x), fabsf(v[i][e].y)), fmaxf(fabsf(v[i][e].z), fabsf(v[i][e].w))));
+        }
+    mx = reduce(mx, true);
+    const float denom = __fadd_rn(mx, 1e-8f);
+    const float scale = __fdiv_rn(q_max, denom);
+    if (threadIdx.x == 0) act_scales[row] = __fdiv_rn(denom, q_max);
+
+    int local_sum = 0;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int j = (threadIdx.x + i * blockDim.x) * 16;
+        if (j < K) {
+            uint32_t words[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int a = static_cast<int>(round_tie(__fmul_rn(v[i][e].x, scale), tie_away));
+                const int b = static_cast<int>(round_tie(__fmul_rn(v[i][e].y, scale), tie_away));
+                const int c = static_cast<int>(round_tie(__fmul_rn(v[i][e].z, scale), tie_away));
+                const int d = static_cast<int>(round_tie(__fmul_rn(v[i][e].w, scale), tie_away));
+                local_sum += a + b + c + d;
+                words[e] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+            }
+            const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
+            if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
+            if (qp) *reinterpret_cast<uint4*>(qp + pbase + qp_offset(prow, prows, K, j)) = transpose4x4_bytes(natural);
+        }
+    }
+    if (q_sums) {
+        local_sum = warp_sum_i(local_sum);
+        if (lane == 0) sum_scratch[warp] = local_sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < nwarps; ++w) t += sum_scratch[w];
+            q_sums[row] = t;
+        }
+    }
+}
+
 // Each thread expands one 128-bit load (64 weights of one row) into four 128-bit stores.
 __global__ void expand_i8_kernel(const uint4* __restrict__ words, int64_t n_vec, int8_t* __restrict__ out) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -255,13 +366,26 @@ cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M
                      (!q || (reinterpret_cast<uintptr_t>(q) & 15) == 0) &&
                      (!qp || (reinterpret_cast<uintptr_t>(qp) & 15) == 0);
     const float q_max = qmax_for_bits(bits);
-    if (vec) {
+    const bool away = tie_mode == TBL_TIE_AWAY;
+    if (vec && K <= 32768) {
+        const int groups = K / 16;
+        int threads = ((groups + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        const int g = (groups + threads - 1) / threads;
+#define TBL_LAUNCH_REG(G)                                                                                  \
+    quantize_rows_reg_kernel<G><<<M, threads, 0, stream>>>(x, row_index, K, q_max, rms_mode, away,         \
+                                                           inv_norm_scratch, q, qp, act_scales, q_sums,    \
+                                                           active_rows, M, segments)
+        if (g <= 1) TBL_LAUNCH_REG(1);
+        else TBL_LAUNCH_REG(2);
+#undef TBL_LAUNCH_REG
+    } else if (vec) {
         quantize_rows_kernel<true><<<M, kQuantThreads, 0, stream>>>(
-            x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, qp,
+            x, row_index, K, q_max, rms_mode, away, inv_norm_scratch, q, qp,
             act_scales, q_sums, active_rows, M, segments);
     } else {
         quantize_rows_kernel<false><<<M, kQuantThreads, 0, stream>>>(
-            x, row_index, K, q_max, rms_mode, tie_mode == TBL_TIE_AWAY, inv_norm_scratch, q, nullptr,
+            x, row_index, K, q_max, rms_mode, away, inv_norm_scratch, q, nullptr,
             act_scales, q_sums, active_rows, M, segments);
     }
     note_launch();
