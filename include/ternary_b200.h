@@ -215,6 +215,13 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
  * clears it.  Negative on a CUDA error. */
 int tbl_device_status(void* stream);
 
+/* Profiling aid: while set (non-NULL cudaEvent_t handles), every launch of the decode GEMV kernel
+ * records `start_event` just before and `stop_event` just after it on its stream, so a harness can
+ * time that kernel alone with cudaEventElapsedTime.  Pass NULLs to switch it off.  Process-wide.
+ * Replaces: the per-kernel timing the reference's benchmarks take around launch_bitnet_gemv_scaled
+ * (OXN/nsos/benchmarks/bench_decode_gemv.cpp:75-90). */
+void tbl_set_kernel_events(void* start_event, void* stop_event);
+
 /* Number of kernels this library has launched in this process (all streams). */
 uint64_t tbl_launch_count(void);
 

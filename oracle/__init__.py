@@ -183,6 +183,7 @@ class _Ref:
         L.ref_layer_create.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_int]
         L.ref_layer_forward.argtypes = [C.c_void_p, _f32p, C.c_int, _f32p]
         L.ref_layer_forward_mt.argtypes = [C.POINTER(C.c_void_p), C.c_int, _f32p, C.c_int, _f32p]
+        L.ref_layers_forward_parallel.argtypes = [C.POINTER(C.c_void_p), C.c_int, _f32p, C.c_int, C.POINTER(_f32p)]
         L.ref_layer_destroy.argtypes = [C.c_void_p]
         L.ref_moe_forward.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p,
                                       _f32p, _f32p, C.c_int, _f32p]
@@ -227,6 +228,14 @@ class _Ref:
     def layer_forward_mt(self, handles, x, y):
         arr = (C.c_void_p * len(handles))(*handles)
         rc = self.lib.ref_layer_forward_mt(arr, len(handles), _ptr(x, _f32p), x.shape[0], _ptr(y, _f32p))
+        if rc != 0:
+            raise RuntimeError("reference BitLinear::forward raised")
+
+    def layers_forward_parallel(self, handles, x, ys):
+        """Each handle (one per host thread) runs forward on the same x; ys[p] is its [M,N_p] output."""
+        arr = (C.c_void_p * len(handles))(*handles)
+        outs = (_f32p * len(handles))(*[_ptr(y, _f32p) for y in ys])
+        rc = self.lib.ref_layers_forward_parallel(arr, len(handles), _ptr(x, _f32p), x.shape[0], outs)
         if rc != 0:
             raise RuntimeError("reference BitLinear::forward raised")
 

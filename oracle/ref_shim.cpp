@@ -123,6 +123,22 @@ int ref_layer_forward_mt(void* const* handles, int threads, const float* x, int 
     return failed ? -1 : 0;
 }
 
+// `count` independent layers (e.g. column shards of one wide layer, one per host thread) each run
+// BitLinear::forward on the same x [M,K]; y_out[p] receives layer p's [M, N_p] result.
+int ref_layers_forward_parallel(void* const* handles, int count, const float* x, int M, float* const* y_out) {
+    int failed = 0;
+#pragma omp parallel for num_threads(count) schedule(static)
+    for (int p = 0; p < count; ++p) {
+        try {
+            run_forward(*static_cast<BitLinear*>(handles[p]), x, M, y_out[p]);
+        } catch (...) {
+#pragma omp atomic write
+            failed = 1;
+        }
+    }
+    return failed ? -1 : 0;
+}
+
 void ref_layer_destroy(void* handle) { delete static_cast<BitLinear*>(handle); }
 
 // MoE expert FFN built from public pieces exactly as the CPU branch of

@@ -57,6 +57,7 @@ _SIGNATURES = {
     "tbl_moe_forward": (C.c_int, [C.POINTER(LinearView), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_size_t, _vp]),
     "tbl_device_status": (C.c_int, [_vp]),
+    "tbl_set_kernel_events": (None, [_vp, _vp]),
     "tbl_launch_count": (C.c_uint64, []),
 }
 

@@ -106,6 +106,10 @@ int tbl_abi_version(void) { return 1; }
 
 uint64_t tbl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+void tbl_set_kernel_events(void* start_event, void* stop_event) {
+    set_gemv_events(static_cast<cudaEvent_t>(start_event), static_cast<cudaEvent_t>(stop_event));
+}
+
 int tbl_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return TBL_ERR_CUDA;

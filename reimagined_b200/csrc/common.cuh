@@ -81,6 +81,14 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
+// 128-bit load from a 32-bit shared-space address (keeps the access an LDS with 32-bit address
+// arithmetic instead of a generic load the compiler cannot always prove to be shared).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 // d = c + dot4(signed bytes of a, unsigned bytes of b)
 __device__ __forceinline__ int dp4a_su(int a, uint32_t b, int c) {
     int d;

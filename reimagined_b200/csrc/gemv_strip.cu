@@ -1,13 +1,15 @@
 // Decode GEMV / small-M GEMM (1 <= M <= 64 activation rows per pass) on the strip-major device
 // layout of the 2-bit weights: HBM-bound streaming with int8 tensor-core MMAs ("swap-AB").
 //
-// Layout ("strips", produced once per matrix by relayout_strips): rows are grouped in strips of 16;
-// a strip is stored as K/256 blocks of 1 KB; block b holds, for lane = 4g+t of a warp, the 16-byte
-// chunk (64 weights, k = 256b + 64t ..) of row g at byte lane*16 and of row g+8 at 512 + lane*16.
-// A strip is therefore one contiguous run of 4K bytes that a warp consumes front to back, and the
-// two 128-bit shared loads of a lane are its m16n8k32 A-fragment source (rows g / g+8) with no
-// bank conflicts.  A stage of the ring holds KS weights of up to 8 strips (one bulk copy per
-// strip, 4 KB at KS = 1024) plus the matching slab of activations (one bulk copy).
+// Layout ("strips", produced once per matrix by relayout_strips): rows are grouped in strips of 16
+// and K in blocks of 256; block (strip s, block b) is 1 KB and holds, for lane = 4g+t of a warp, the
+// 16-byte chunk (64 weights, k = 256b + 64t ..) of row g at byte lane*16 and of row g+8 at
+// 512 + lane*16 -- the two 128-bit shared loads of a lane are its m16n8k32 A-fragment source
+// (rows g / g+8) with no bank conflicts.  Blocks are ordered slab-major: a slab is 4 consecutive
+// k-blocks (1024 weights of K) of EVERY strip, [slab][strip][block in slab].  CTAs own runs of
+// adjacent strips and walk the slabs in step, so at any moment the whole GPU is reading one
+// contiguous window of memory (DRAM pages are swept once, front to back) and a CTA's stage is a
+// single contiguous bulk copy (strips x 4 KB) plus the matching slab of activations.
 //
 // Widening: for 2-bit position j, (word & (0x03030303 << 2j)) is the unsigned byte vector
 // 4^j * code of weights {j,4+j,8+j,12+j} of that word.  With one accumulator set per j the four
@@ -20,7 +22,7 @@
 namespace tbl {
 namespace {
 
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kStripSlots = 8;     // strips processed concurrently by a CTA
 constexpr int kNumSm = 148;
 
@@ -30,6 +32,8 @@ struct StripParams {
     int total_strips;
     int ks;       // k per stage, multiple of 256
     int stages;
+    int slots;    // strips per pass (<= kStripSlots): sized to the CTA's share so no stage space idles
+    int act_rows; // activation rows held per stage (<= 8*NT)
     int* status;
 };
 
@@ -52,13 +56,14 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     constexpr int kConsumers = kStripSlots * WPS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblk_stage = P.ks >> 8;
-    const int wstage = kStripSlots * nblk_stage * 1024;           // weight bytes of a stage
-    const int stage_bytes = wstage + nblk_stage * MPAD * 256;
+    const int wstage = P.slots * nblk_stage * 1024;               // weight bytes of a stage
+    const int stage_bytes = wstage + nblk_stage * P.act_rows * 256;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
     int* reduce_buf = reinterpret_cast<int*>(smem + 128);        // [slot][WPS-1][32 lanes][4*NT]
     constexpr int kReduceBytes = WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
     uint8_t* stage_base = smem + 128 + kReduceBytes;
+    const uint32_t stage_base_addr = smem_u32(stage_base);
     const int nstages = P.stages;
 
     if (threadIdx.x == 0) {
@@ -77,6 +82,11 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     const bool producer = warp == kConsumers;
     const int slot = warp / WPS, part = warp % WPS;
     const int g = lane >> 2, t = lane & 3;
+    // byte offset, inside a 256-byte activation row block, of the 16-byte group (quarter x, chunk t)
+    // of activation row g (row nt*8+g adds nt*2048; the XOR term is the same since 8 is even)
+    int aoff[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) aoff[x] = g * 256 + ((((x ^ (g & 1)) << 2) + t) << 4);
 
     int it = 0;
     bool alive = true;
@@ -87,7 +97,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         const int K = pr.K, N = pr.N;
         const int nstrips = (N + 15) >> 4;
         const int local = s - pr.strip_begin;
-        const int cnt = min(kStripSlots, min(s_end - s, nstrips - local));
+        const int cnt = min(P.slots, min(s_end - s, nstrips - local));
         s += cnt;
         int rows = pr.rows;
         if (pr.rows_dev) rows = min(rows, __ldg(pr.rows_dev));
@@ -96,7 +106,6 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         const int nblk = K >> 8;
         const int ksteps = (nblk + nblk_stage - 1) / nblk_stage;
         const int mtiles = (rows + MPAD - 1) / MPAD;   // > 1 only in the NT = 8 variant
-        const uint8_t* wsrc = pr.strips + (static_cast<size_t>(local) * nblk << 10);
         const int8_t* qsrc = pr.qp + static_cast<size_t>(row0) * K;
 
         for (int mt = 0; mt < mtiles && alive; ++mt) {
@@ -118,9 +127,18 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                         mbar_arrive_expect_tx(&full[st], static_cast<uint32_t>(cnt) * nb * 1024 +
                                                              static_cast<uint32_t>(nb) * R * 256);
                     __syncwarp();
-                    if (lane < cnt)
-                        bulk_g2s(wst + lane * nblk_stage * 1024,
-                                 wsrc + ((static_cast<size_t>(lane) * nblk + b0) << 10), nb * 1024, &full[st]);
+                    // slab-major source: slab t starts at block 4*t*nstrips and gives each strip bs blocks
+                    const int slab = b0 >> 2, bin = b0 & 3;
+                    const int bs = min(4, nblk - 4 * slab);
+                    const uint8_t* slab_src = pr.strips + ((static_cast<size_t>(4) * slab * nstrips +
+                                                            static_cast<size_t>(local) * bs) << 10);
+                    if (nb == bs) {
+                        // the stage is the whole slab of cnt adjacent strips: one contiguous copy
+                        if (lane == 0) bulk_g2s(wst, slab_src, cnt * nb * 1024, &full[st]);
+                    } else if (lane < cnt) {
+                        bulk_g2s(wst + lane * nb * 1024, slab_src + ((static_cast<size_t>(lane) * bs + bin) << 10),
+                                 nb * 1024, &full[st]);
+                    }
                     if (lane == kStripSlots)
                         bulk_g2s(wst + wstage, qtile + static_cast<size_t>(b0) * R * 256, nb * R * 256,
                                  &full[st]);
@@ -143,28 +161,26 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 if (!alive) break;
                 if (active) {
                     const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
-                    const uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes +
-                                         slot * nblk_stage * 1024 + lane * 16;
-                    const uint8_t* ast = stage_base + static_cast<size_t>(st) * stage_bytes + wstage;
+                    const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
+                    const uint32_t wst = stage_addr + slot * nb * 1024 + lane * 16;
+                    const uint32_t ast = stage_addr + wstage;
                     // blocks of this stage are global blocks ksi*nblk_stage + b; this warp takes its residue class
                     const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
+#pragma unroll 2
                     for (int b = first; b < nb; b += WPS) {
-                        const uint4 lo = *reinterpret_cast<const uint4*>(wst + b * 1024);
-                        const uint4 hi = *reinterpret_cast<const uint4*>(wst + b * 1024 + 512);
+                        const uint4 lo = lds128(wst + b * 1024);
+                        const uint4 hi = lds128(wst + b * 1024 + 512);
                         const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
                         const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
-                        const uint8_t* ablk = ast + static_cast<size_t>(b) * R * 256;
+                        // rows m >= R of the slab are stale shared memory: their accumulator columns are
+                        // never stored, so the loads need no predicate
+                        const uint32_t ablk = ast + b * R * 256;
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
-                            const int m = nt * 8 + g;
                             uint4 B[4];
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) {
-                                B[x] = make_uint4(0, 0, 0, 0);
-                                if (m < R)
-                                    B[x] = *reinterpret_cast<const uint4*>(ablk + m * 256 +
-                                                                           (((x ^ (m & 1)) << 2) + t) * 16);
-                            }
+                            for (int x = 0; x < 4; ++x)
+                                B[x] = lds128(ablk + nt * 2048 + aoff[x]);
                             const uint32_t bw[4][4] = {{B[0].x, B[0].y, B[0].z, B[0].w},
                                                        {B[1].x, B[1].y, B[1].z, B[1].w},
                                                        {B[2].x, B[2].y, B[2].z, B[2].w},
@@ -257,16 +273,30 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     }
 }
 
-// canonical [N, K/16] words -> strip layout; one thread per 16-byte chunk of the output.
+// canonical [N, K/16] words -> strip layout (slab-major); one thread per 16-byte chunk of the output.
 __global__ void __launch_bounds__(256)
 relayout_strips_kernel(const uint4* __restrict__ words, int N, int K, uint4* __restrict__ strips, int64_t chunks) {
     const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (o >= chunks) return;
-    const int cpr = K >> 6;               // chunks per row
-    const int64_t cps = static_cast<int64_t>(cpr) * 16;   // chunks per strip
-    const int s = static_cast<int>(o / cps);
-    const int in = static_cast<int>(o % cps);
-    const int b = in >> 6, within = in & 63;
+    const int cpr = K >> 6;               // 16-byte chunks per row
+    const int nblk = K >> 8;
+    const int nstrips = (N + 15) >> 4;
+    const int64_t blk = o >> 6;           // 1 KB block index in the output
+    const int within = static_cast<int>(o & 63);
+    const int full_slabs = nblk >> 2;
+    const int64_t boundary = static_cast<int64_t>(full_slabs) * 4 * nstrips;
+    int s, b;
+    if (blk < boundary) {
+        const int64_t slab = blk / (4 * static_cast<int64_t>(nstrips));
+        const int rem = static_cast<int>(blk % (4 * static_cast<int64_t>(nstrips)));
+        s = rem >> 2;
+        b = static_cast<int>(slab) * 4 + (rem & 3);
+    } else {
+        const int r = nblk & 3;           // blocks per strip in the last, partial slab
+        const int rem = static_cast<int>(blk - boundary);
+        s = rem / r;
+        b = full_slabs * 4 + rem % r;
+    }
     const int h = within >> 5, ln = within & 31;
     const int row = s * 16 + h * 8 + (ln >> 2);
     const int c = 4 * b + (ln & 3);
@@ -301,6 +331,8 @@ __global__ void __launch_bounds__(256) permute_q_kernel(const int8_t* __restrict
     }
 }
 
+cudaEvent_t g_event_start = nullptr, g_event_stop = nullptr;
+
 template <int NT, bool SCALED, int WPS>
 cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStream_t stream) {
     auto kernel = gemv_strip_kernel<NT, SCALED, WPS>;
@@ -313,12 +345,19 @@ cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStre
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
+    if (g_event_start) cudaEventRecord(g_event_start, stream);
     kernel<<<grid, (kStripSlots * WPS + 1) * 32, smem, stream>>>(P);
+    if (g_event_stop) cudaEventRecord(g_event_stop, stream);
     note_launch();
     return cudaGetLastError();
 }
 
 }  // namespace
+
+void set_gemv_events(cudaEvent_t start, cudaEvent_t stop) {
+    g_event_start = start;
+    g_event_stop = stop;
+}
 
 bool gemv_strip_supported(int K) { return K > 0 && K % 256 == 0 && K <= 65536; }
 
@@ -355,18 +394,24 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const int nt = max_rows <= 8 ? 1 : (max_rows <= 16 ? 2 : (max_rows <= 32 ? 4 : 8));
     // stage depth in k: 1024 keeps each strip copy at 4 KB; shrink for tall activation tiles
     P.ks = nt <= 2 ? 1024 : 512;
-    const size_t stage_bytes = static_cast<size_t>(kStripSlots) * (P.ks / 256) * 1024 +
-                               static_cast<size_t>(P.ks / 256) * (8 * nt) * 256;
-    P.stages = kMaxStages;
-    while (P.stages > 2 && 128 + P.stages * stage_bytes > 200 * 1024) --P.stages;
-    const size_t smem = 128 + P.stages * stage_bytes;
     int grid = (total + kStripSlots - 1) / kStripSlots;
     if (grid > kNumSm) grid = kNumSm;
     // spread small problems over more SMs (fewer strips per CTA)
     if (total < kNumSm * kStripSlots) grid = total < kNumSm ? total : kNumSm;
+    // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
+    const int share = (total + grid - 1) / grid;
+    const int passes = (share + kStripSlots - 1) / kStripSlots;
+    P.slots = (share + passes - 1) / passes;
+    P.act_rows = max_rows < 8 * nt ? max_rows : 8 * nt;
+    const size_t stage_bytes = static_cast<size_t>(P.slots) * (P.ks / 256) * 1024 +
+                               static_cast<size_t>(P.ks / 256) * P.act_rows * 256;
+    P.stages = kMaxStages;
+    while (P.stages > 2 && 128 + P.stages * stage_bytes > 208 * 1024) --P.stages;
+    // slack after the last stage: lanes of activation rows >= act_rows read (and ignore) stale bytes
+    const size_t smem = 128 + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
     switch (nt) {
         case 1: return launch_variant<1, true, 2>(P, grid, smem, stream);
-        case 2: return launch_variant<2, true, 2>(P, grid, smem, stream);
+        case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);
         case 4: return launch_variant<4, true, 1>(P, grid, smem, stream);
         default: return launch_variant<8, false, 1>(P, grid, smem, stream);
     }

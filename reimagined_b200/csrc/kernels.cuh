@@ -91,6 +91,7 @@ struct StripProblem {
     int strip_begin;          // global index of this problem's first strip (filled by the launcher)
 };
 bool gemv_strip_supported(int K);
+void set_gemv_events(cudaEvent_t start, cudaEvent_t stop);
 cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* strips, cudaStream_t stream);
 cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t stream);
 cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t* q_sums, cudaStream_t stream);

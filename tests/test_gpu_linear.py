@@ -153,12 +153,21 @@ def test_strip_relayout_is_a_permutation(cuda, port, tbl):
     got = strips[~pad]
     order = np.lexsort(got.T[::-1])
     assert np.array_equal(got[order], canon[np.lexsort(canon.T[::-1])])
-    # block 0 of strip 0: lane 4g+t holds chunk t of row g, then rows g+8 at +512 bytes
-    cpr = K // 64
-    for g in range(8):
-        for t_ in range(4):
-            assert np.array_equal(strips[4 * g + t_], canon[g * cpr + t_])
-            assert np.array_equal(strips[32 + 4 * g + t_], canon[(g + 8) * cpr + t_])
+    # 1 KB block (strip s, k-block b) sits at slab-major position 4*(b//4)*S + s*4 + b%4 (K = 512: one
+    # half slab of 2 blocks per strip): lane 4g+t holds chunk 4b+t of row 16s+g, rows +8 at +512 bytes
+    cpr, S = K // 64, 3
+    for s_ in range(S):
+        for b in range(2):
+            base = (s_ * 2 + b) * 64
+            for g in range(8):
+                for t_ in range(4):
+                    for h in range(2):
+                        row = 16 * s_ + 8 * h + g
+                        got_chunk = strips[base + 32 * h + 4 * g + t_]
+                        if row < N:
+                            assert np.array_equal(got_chunk, canon[row * cpr + 4 * b + t_])
+                        else:
+                            assert (got_chunk == 0x55555555).all()
 
 
 @pytest.mark.parametrize("M", [65, 100, 200])
