@@ -158,6 +158,33 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
                        const float* magnitude_dev, const float* bias_dev, float* y_dev,
                        void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* Largest scratch tbl_linear_forward_noalloc can serve: tbl_linear_workspace_bytes(M,K,N) must not
+ * exceed this (e.g. M*K <= 1 MiB of int8 codes: 64 rows of K = 16384, or 1365 rows of K = 768). */
+#define TBL_NOALLOC_SCRATCH_BYTES (2u * 1024u * 1024u + 64u * 1024u)
+
+/* tbl_linear_forward for callers that have no way to obtain device scratch memory: code running
+ * inside a latency-critical decode loop where cudaMalloc is forbidden, plugins handed only their
+ * input and output buffers by a host runtime that owns the allocator, and bindings (cgo/JNI/ctypes)
+ * whose side of the boundary cannot manage device lifetimes.  Same arithmetic and same results as
+ * tbl_linear_forward; the quantiser's scratch (int8 codes, scales, row sums) lives in a fixed array
+ * inside the library image instead of a caller workspace.
+ *   - The array is TBL_NOALLOC_SCRATCH_BYTES large and is part of every device's copy of the library
+ *     from load until exit; shapes whose scratch would not fit are refused with TBL_ERR_WORKSPACE
+ *     and nothing is launched.
+ *   - The first call on each device looks the array's device address up (with that device current);
+ *     make that first call before any stream capture begins.
+ *   - No cudaMalloc/cudaFree or other allocating call is made, on any call.
+ *   - Every call uses the same array and leaves its last contents there.  Nothing in it has to start
+ *     at zero (each call overwrites all it later reads), but two calls that overlap on the GPU --
+ *     different streams, or one stream fed from several threads without ordering -- race on it: keep
+ *     calls on one stream or order them yourself.
+ * This entry point has no counterpart in the reference (whose dispatch always borrows scratch from
+ * its ExecutionContext). */
+int tbl_linear_forward_noalloc(const float* x_dev, const uint32_t* words_dev, const void* strips_dev,
+                               const int8_t* w_i8_dev, float weight_scale, int M, int K, int N, int bits,
+                               int rms_mode, const float* magnitude_dev, const float* bias_dev,
+                               float* y_dev, void* stream);
+
 /* ---- grouped variant ------------------------------------------------------------------- */
 
 /* Borrowed descriptor of one linear; the first nine fields are field-for-field the reference's

@@ -50,6 +50,8 @@ _SIGNATURES = {
     "tbl_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "tbl_linear_forward": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                      _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "tbl_linear_forward_noalloc": (C.c_int, [_vp, _vp, _vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                             _vp, _vp, _vp, _vp]),
     "tbl_grouped_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "tbl_grouped_forward": (C.c_int, [C.POINTER(LinearView), C.c_int, _vp, _vp, C.c_int, C.c_int, _vp,
                                       C.c_size_t, _vp]),

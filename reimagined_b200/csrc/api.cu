@@ -444,3 +444,39 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
 }
 
 }  // extern "C"
+
+// ---- allocation-free variant of the layer forward --------------------------------------------
+
+// Scratch for tbl_linear_forward_noalloc.  In host code this name is only a stand-in for the
+// symbol: the device address has to be asked for, per device, with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TBL_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_noalloc_scratch on the current device; looked up once per device.
+void* noalloc_scratch_address() {
+    static void* cached[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess) return nullptr;
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+}  // namespace
+
+extern "C" int tbl_linear_forward_noalloc(const float* x_dev, const uint32_t* words_dev, const void* strips_dev,
+                                          const int8_t* w_i8_dev, float weight_scale, int M, int K, int N, int bits,
+                                          int rms_mode, const float* magnitude_dev, const float* bias_dev,
+                                          float* y_dev, void* stream) {
+    if (M <= 0 || K <= 0 || N <= 0) return TBL_ERR_INVALID_ARG;
+    // refuse, before anything is enqueued, what the fixed array cannot hold
+    if (tbl_linear_workspace_bytes(M, K, N) > TBL_NOALLOC_SCRATCH_BYTES) return TBL_ERR_WORKSPACE;
+    void* scratch = noalloc_scratch_address();
+    if (!scratch) return TBL_ERR_CUDA;
+    return tbl_linear_forward(x_dev, words_dev, strips_dev, w_i8_dev, weight_scale, M, K, N, bits, rms_mode,
+                              magnitude_dev, bias_dev, y_dev, scratch, TBL_NOALLOC_SCRATCH_BYTES, stream);
+}
