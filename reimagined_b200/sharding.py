@@ -50,7 +50,8 @@ def gather_columns(y_local, world: int, group=None):
     import torch.distributed as dist
     m, n_local = y_local.shape
     stacked = torch.empty((world, m, n_local), dtype=y_local.dtype, device=y_local.device)
-    dist.all_gather_into_tensor(stacked, y_local.contiguous(), group=group)
+    # list form of all_gather: supported by NCCL and gloo alike; the views alias `stacked`
+    dist.all_gather([stacked[r] for r in range(world)], y_local.contiguous(), group=group)
     return stacked.permute(1, 0, 2).reshape(m, world * n_local).contiguous()
 
 
