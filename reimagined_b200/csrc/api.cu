@@ -226,6 +226,16 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
         return cuda_status(launch_gemv_small(a, st));
     }
 
+    // few rows on the strip layout: one kernel, the quantiser runs in the GEMV's prologue while the
+    // first weight stages are already in flight
+    if (strip && rms_mode != TBL_RMS_REFERENCE_ORDER && M <= gemv_strip_fused_rows(K)) {
+        StripProblem pr{};
+        pr.strips = static_cast<const uint8_t*>(strips_dev); pr.x = x_dev; pr.q_max = qmax_for_bits(bits);
+        pr.rms_fast = rms_mode == TBL_RMS_FAST; pr.magnitude = magnitude_dev; pr.bias = bias_dev; pr.y = y_dev;
+        pr.weight_scale = weight_scale; pr.rows = M; pr.N = N; pr.K = K; pr.ldy = N;
+        return cuda_status(launch_gemv_strip(&pr, 1, st));
+    }
+
     if (!workspace_dev || workspace_bytes < tbl_linear_workspace_bytes(M, K, N)) return TBL_ERR_WORKSPACE;
     if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
     const Workspace w = carve(workspace_dev, M, K);

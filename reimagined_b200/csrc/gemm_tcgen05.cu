@@ -6,10 +6,11 @@
 //   warp 0    TMA producer: per k-block one box of q [128 rows x 128 B] and one of w [BN x 128 B]
 //   warp 1    MMA issuer (one lane): 4 x tcgen05.mma (K = 32 each) per k-block, tcgen05.commit
 //             releases the stage; also owns the TMEM allocation (512 columns = 2 accumulators)
-//   warps 2-5 epilogue: tcgen05.ld the 128 x BN s32 tile (one TMEM lane quarter per warp), apply
+//   warps 2-9 epilogue: tcgen05.ld the 128 x BN s32 tile (a TMEM lane quarter per warp pair), apply
 //             float(acc) * (act_scale*weight_scale) [* magnitude] [+ bias], stage 32x32 fp32 blocks
 //             in swizzled shared memory and write them with TMA stores (clipped at the edges)
-// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1; the next
+// block's tcgen05.ld is issued before the current block is converted and stored.
 // Every wait is bounded: on a timeout the role records the status word and falls through to
 // the common exit, where TMEM is released.
 #include <cuda.h>
@@ -23,7 +24,7 @@ namespace {
 constexpr int BM = 128;          // activation rows per tile (UMMA M)
 constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;        // two warps per TMEM lane quarter, each taking every other 32-column block
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kNumSm = 148;
 
@@ -89,8 +90,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -105,7 +106,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     constexpr int kABytes = BM * BK;
     constexpr int kBBytes = BN * BK;
     constexpr int kStageBytes = kABytes + kBBytes;
-    uint8_t* epi_stage = smem + kStages * kStageBytes;                 // 4 warps x 4 KB
+    uint8_t* epi_stage = smem + kStages * kStageBytes;                 // 8 warps x 4 KB
     uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + kEpiWarps * 4096);
     uint64_t* empty = full + kStages;
     uint64_t* tmem_full = empty + kStages;
@@ -189,6 +190,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------- epilogue warps ----------------
         const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are this warp's
+        const int half = (warp - 2) >> 2;      // which of the two warps of the quarter: blocks half, half+2, ...
         uint8_t* stage = epi_stage + (warp - 2) * 4096;
         int local = 0;
         bool alive = true;
@@ -202,12 +204,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int m = tm * BM + quarter * 32 + lane;
             const float comb = m < p.M ? __fmul_rn(__ldg(p.act_scales + m), p.weight_scale) : 0.0f;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            // blocks of 32 columns this warp owns inside the tile, clipped at N
+            const int nblocks = min(BN / 32, (p.N - tn * BN + 31) / 32);
+            uint32_t r[32], rn[32];
+            if (half < nblocks) tmem_ld32(t_row + half * 32, r);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = half; c < nblocks; c += 2) {
                 const int n0 = tn * BN + c * 32;
-                if (n0 >= p.N) break;
-                uint32_t r[32];
-                tmem_ld32(t_row + c * 32, r);
+                tmem_ld_wait();
+                if (c + 2 < nblocks) tmem_ld32(t_row + (c + 2) * 32, rn);   // in flight while this block is stored
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -238,6 +243,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int i = 0; i < 32; ++i)
                         if (n0 + i < p.N) p.y[static_cast<size_t>(m) * p.N + n0 + i] = v[i];
                 }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = rn[i];
             }
             tc_fence_before();
             __syncwarp();
@@ -316,7 +323,15 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
     p.weight_scale = weight_scale; p.M = M; p.K = K; p.N = N;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
-    const int bn = N > 128 ? 256 : 128;
+    // tile width: 256 unless the narrower tile fills the 148 SMs clearly better (wave quantisation)
+    int bn = N > 128 ? 256 : 128;
+    if (bn == 256) {
+        const long long tm = (M + BM - 1) / BM;
+        const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
+        const double e256 = static_cast<double>(t256) / (((t256 + kNumSm - 1) / kNumSm) * kNumSm);
+        const double e128 = static_cast<double>(t128) / (((t128 + kNumSm - 1) / kNumSm) * kNumSm);
+        if (e128 > 1.15 * e256) bn = 128;
+    }
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     // TMA stores need a 16-byte row pitch and base

@@ -33,7 +33,8 @@ struct StripParams {
     int ks;       // k per stage, multiple of 256
     int stages;
     int slots;    // strips per pass (<= kStripSlots): sized to the CTA's share so no stage space idles
-    int act_rows; // activation rows held per stage (<= 8*NT)
+    int act_rows; // activation rows held per stage (<= 8*NT); 0 when the activations are resident
+    int fused;    // 1: prob[0].x is quantised in the prologue into a resident shared-memory copy
     int* status;
 };
 
@@ -62,8 +63,15 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     uint64_t* empty = full + kMaxStages;
     int* reduce_buf = reinterpret_cast<int*>(smem + 128);        // [slot][WPS-1][32 lanes][4*NT]
     constexpr int kReduceBytes = WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
-    uint8_t* stage_base = smem + 128 + kReduceBytes;
+    // fused mode: [scales 8 f32 | sums 8 i32 | scratch 32 f32] then the resident activations
+    float* s_scale = reinterpret_cast<float*>(smem + 128 + kReduceBytes);
+    int* s_qsum = reinterpret_cast<int*>(s_scale + 8);
+    float* s_red = s_scale + 16;
+    const int fused_bytes = P.fused ? 256 + ((P.prob[0].rows * P.prob[0].K + 127) & ~127) : 0;
+    uint8_t* acts_resident = smem + 128 + kReduceBytes + 256;
+    uint8_t* stage_base = smem + 128 + kReduceBytes + fused_bytes;
     const uint32_t stage_base_addr = smem_u32(stage_base);
+    const uint32_t acts_resident_addr = smem_u32(acts_resident);
     const int nstages = P.stages;
 
     if (threadIdx.x == 0) {
@@ -75,6 +83,79 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         fence_proxy_async();
     }
     __syncthreads();
+
+    if (P.fused && warp < kConsumers) {
+        // ---- fused per-token absmax quantiser (consumer warps only; the producer warp is already
+        // streaming weights).  Same arithmetic as the stand-alone quantiser kernel. ----
+        const StripProblem& pr = P.prob[0];
+        const int K = pr.K, R = pr.rows;
+        constexpr int kT = kConsumers * 32;
+        auto block_reduce = [&](float v, bool is_max) -> float {
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, v, o);
+                v = is_max ? fmaxf(v, other) : v + other;
+            }
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+            if (lane == 0) s_red[warp] = v;
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+            float r = s_red[0];
+            for (int w = 1; w < kConsumers; ++w) r = is_max ? fmaxf(r, s_red[w]) : r + s_red[w];
+            return r;
+        };
+        for (int m = 0; m < R; ++m) {
+            const float* xr = pr.x + static_cast<size_t>(m) * K;
+            float inv = 1.0f;
+            if (pr.rms_fast) {
+                float ss = 0.0f;
+                for (int j = threadIdx.x * 4; j < K; j += kT * 4) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+                ss = block_reduce(ss, false);
+                inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), 1e-6f)));
+            }
+            float mx = 0.0f;
+            for (int j = threadIdx.x * 4; j < K; j += kT * 4) {
+                float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
+                if (pr.rms_fast) {
+                    v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                    v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                }
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+            mx = block_reduce(mx, true);
+            const float denom = __fadd_rn(mx, 1e-8f);
+            const float scale = __fdiv_rn(pr.q_max, denom);
+            int local_sum = 0;
+            for (int j = threadIdx.x * 16; j < K; j += kT * 16) {
+                uint32_t wds[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float4 v = __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e));
+                    if (pr.rms_fast) {
+                        v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                        v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                    }
+                    const int q0 = static_cast<int>(rintf(__fmul_rn(v.x, scale)));
+                    const int q1 = static_cast<int>(rintf(__fmul_rn(v.y, scale)));
+                    const int q2 = static_cast<int>(rintf(__fmul_rn(v.z, scale)));
+                    const int q3 = static_cast<int>(rintf(__fmul_rn(v.w, scale)));
+                    local_sum += q0 + q1 + q2 + q3;
+                    wds[e] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) |
+                             (static_cast<uint32_t>(q3 & 0xff) << 24);
+                }
+                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, j)) =
+                    transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
+            }
+            const float total = block_reduce(static_cast<float>(local_sum), false);  // |sum| <= 127*K < 2^24: exact
+            if (threadIdx.x == 0) {
+                s_scale[m] = __fdiv_rn(denom, pr.q_max);
+                s_qsum[m] = static_cast<int>(total);
+            }
+        }
+        asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+    }
 
     // contiguous, balanced share of the global strip list
     const int s_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_strips / gridDim.x);
@@ -125,7 +206,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                     uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes;
                     if (lane == 0)
                         mbar_arrive_expect_tx(&full[st], static_cast<uint32_t>(cnt) * nb * 1024 +
-                                                             static_cast<uint32_t>(nb) * R * 256);
+                                                             (P.fused ? 0u : static_cast<uint32_t>(nb) * R * 256));
                     __syncwarp();
                     // slab-major source: slab t starts at block 4*t*nstrips and gives each strip bs blocks
                     const int slab = b0 >> 2, bin = b0 & 3;
@@ -139,7 +220,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                         bulk_g2s(wst + lane * nb * 1024, slab_src + ((static_cast<size_t>(lane) * bs + bin) << 10),
                                  nb * 1024, &full[st]);
                     }
-                    if (lane == kStripSlots)
+                    if (lane == kStripSlots && !P.fused)
                         bulk_g2s(wst + wstage, qtile + static_cast<size_t>(b0) * R * 256, nb * R * 256,
                                  &full[st]);
                 }
@@ -163,7 +244,8 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                     const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
                     const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
                     const uint32_t wst = stage_addr + slot * nb * 1024 + lane * 16;
-                    const uint32_t ast = stage_addr + wstage;
+                    // activations: this stage's slab, or the resident copy at the stage's first block
+                    const uint32_t ast = P.fused ? acts_resident_addr + ksi * nblk_stage * R * 256 : stage_addr + wstage;
                     // blocks of this stage are global blocks ksi*nblk_stage + b; this warp takes its residue class
                     const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
 #pragma unroll 2
@@ -257,9 +339,10 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                                 const int e = 2 * h + c;
                                 int total = tot[nt][e];
                                 const int gm = row0 + mt * MPAD + m;
-                                total -= __ldg(pr.q_sums + gm);
+                                total -= P.fused ? s_qsum[m] : __ldg(pr.q_sums + gm);
                                 if (pr.acc_debug) pr.acc_debug[static_cast<size_t>(gm) * pr.ldy + n] = total;
-                                float v = epilogue(total, __fmul_rn(__ldg(pr.act_scales + gm), pr.weight_scale),
+                                const float a_scale = P.fused ? s_scale[m] : __ldg(pr.act_scales + gm);
+                                float v = epilogue(total, __fmul_rn(a_scale, pr.weight_scale),
                                                    pr.magnitude, pr.bias, n);
                                 if (pr.squared_relu) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
                                 pr.y[static_cast<size_t>(gm) * pr.ldy + n] = v;
@@ -359,6 +442,14 @@ void set_gemv_events(cudaEvent_t start, cudaEvent_t stop) {
     g_event_stop = stop;
 }
 
+// The fused prologue keeps rows*K bytes of activations resident next to the ring: allow what leaves
+// the ring deep enough (<= 32 KB), at most 8 rows.
+int gemv_strip_fused_rows(int K) {
+    if (!gemv_strip_supported(K)) return 0;
+    const int rows = 32768 / K;
+    return rows > 8 ? 8 : rows;
+}
+
 bool gemv_strip_supported(int K) { return K > 0 && K % 256 == 0 && K <= 65536; }
 
 cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* strips, cudaStream_t stream) {
@@ -402,13 +493,17 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const int share = (total + grid - 1) / grid;
     const int passes = (share + kStripSlots - 1) / kStripSlots;
     P.slots = (share + passes - 1) / passes;
-    P.act_rows = max_rows < 8 * nt ? max_rows : 8 * nt;
+    P.fused = count == 1 && problems[0].x != nullptr;
+    if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
+        return cudaErrorInvalidValue;
+    P.act_rows = P.fused ? 0 : (max_rows < 8 * nt ? max_rows : 8 * nt);
+    const size_t fused_bytes = P.fused ? 256 + ((static_cast<size_t>(problems[0].rows) * problems[0].K + 127) & ~size_t(127)) : 0;
     const size_t stage_bytes = static_cast<size_t>(P.slots) * (P.ks / 256) * 1024 +
                                static_cast<size_t>(P.ks / 256) * P.act_rows * 256;
     P.stages = kMaxStages;
-    while (P.stages > 2 && 128 + P.stages * stage_bytes > 208 * 1024) --P.stages;
+    while (P.stages > 2 && 128 + fused_bytes + P.stages * stage_bytes > 208 * 1024) --P.stages;
     // slack after the last stage: lanes of activation rows >= act_rows read (and ignore) stale bytes
-    const size_t smem = 128 + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
+    const size_t smem = 128 + fused_bytes + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
     switch (nt) {
         case 1: return launch_variant<1, true, 2>(P, grid, smem, stream);
         case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);

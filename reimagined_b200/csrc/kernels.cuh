@@ -89,7 +89,14 @@ struct StripProblem {
     int N, K, ldy;
     int squared_relu;
     int strip_begin;          // global index of this problem's first strip (filled by the launcher)
+    // fused quantiser (single-problem launches with few rows): when x != null the kernel quantises
+    // x fp32 [rows, K] itself in its prologue and ignores qp / act_scales / q_sums
+    const float* x;
+    float q_max;
+    int rms_fast;             // apply the (parallel-sum) input RMSNorm before quantising
 };
+// rows the strip kernel can quantise in its own prologue for this K (0 = none)
+int gemv_strip_fused_rows(int K);
 bool gemv_strip_supported(int K);
 void set_gemv_events(cudaEvent_t start, cudaEvent_t stop);
 cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* strips, cudaStream_t stream);
