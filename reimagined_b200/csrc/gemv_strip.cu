@@ -63,12 +63,12 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     uint64_t* empty = full + kMaxStages;
     int* reduce_buf = reinterpret_cast<int*>(smem + 128);        // [slot][WPS-1][32 lanes][4*NT]
     constexpr int kReduceBytes = WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
-    // fused mode: [scales 8 f32 | sums 8 i32 | scratch 32 f32] then the resident activations
+    // fused mode: [scales 8 f32 | sums 8 i32 | scratch 16 warps x 8 f32] then the resident activations
     float* s_scale = reinterpret_cast<float*>(smem + 128 + kReduceBytes);
     int* s_qsum = reinterpret_cast<int*>(s_scale + 8);
     float* s_red = s_scale + 16;
-    const int fused_bytes = P.fused ? 256 + ((P.prob[0].rows * P.prob[0].K + 127) & ~127) : 0;
-    uint8_t* acts_resident = smem + 128 + kReduceBytes + 256;
+    const int fused_bytes = P.fused ? 1024 + ((P.prob[0].rows * P.prob[0].K + 127) & ~127) : 0;
+    uint8_t* acts_resident = smem + 128 + kReduceBytes + 1024;
     uint8_t* stage_base = smem + 128 + kReduceBytes + fused_bytes;
     const uint32_t stage_base_addr = smem_u32(stage_base);
     const uint32_t acts_resident_addr = smem_u32(acts_resident);
@@ -86,72 +86,125 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
 
     if (P.fused && warp < kConsumers) {
         // ---- fused per-token absmax quantiser (consumer warps only; the producer warp is already
-        // streaming weights).  Same arithmetic as the stand-alone quantiser kernel. ----
+        // streaming weights).  Same arithmetic as the stand-alone quantiser kernel.  The rows*K <= 16384
+        // inputs are read from memory once, 16 consecutive elements x 2 groups per thread, and stay in
+        // registers between the absmax reduction and the rounding. ----
         const StripProblem& pr = P.prob[0];
         const int K = pr.K, R = pr.rows;
         constexpr int kT = kConsumers * 32;
-        auto block_reduce = [&](float v, bool is_max) -> float {
+        constexpr int kMaxFusedRows = 8;
+        constexpr int kGroups = 16384 / 16 / kT;     // 16-element groups per thread
+        const int total_groups = R * K / 16;
+        float4 xv[kGroups][4];
+        int grow[kGroups];
 #pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                const float other = __shfl_xor_sync(0xffffffffu, v, o);
-                v = is_max ? fmaxf(v, other) : v + other;
-            }
-            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
-            if (lane == 0) s_red[warp] = v;
-            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
-            float r = s_red[0];
-            for (int w = 1; w < kConsumers; ++w) r = is_max ? fmaxf(r, s_red[w]) : r + s_red[w];
-            return r;
-        };
-        for (int m = 0; m < R; ++m) {
-            const float* xr = pr.x + static_cast<size_t>(m) * K;
-            float inv = 1.0f;
-            if (pr.rms_fast) {
-                float ss = 0.0f;
-                for (int j = threadIdx.x * 4; j < K; j += kT * 4) {
-                    const float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                }
-                ss = block_reduce(ss, false);
-                inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), 1e-6f)));
-            }
-            float mx = 0.0f;
-            for (int j = threadIdx.x * 4; j < K; j += kT * 4) {
-                float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
-                if (pr.rms_fast) {
-                    v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
-                    v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
-                }
-                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            }
-            mx = block_reduce(mx, true);
-            const float denom = __fadd_rn(mx, 1e-8f);
-            const float scale = __fdiv_rn(pr.q_max, denom);
-            int local_sum = 0;
-            for (int j = threadIdx.x * 16; j < K; j += kT * 16) {
-                uint32_t wds[4];
+        for (int i = 0; i < kGroups; ++i) {
+            const int G = threadIdx.x + i * kT;
+            grow[i] = -1;
+            if (G < total_groups) {
+                const int e = G * 16;
+                grow[i] = e / K;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float4 v = __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e));
-                    if (pr.rms_fast) {
-                        v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
-                        v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = __ldg(reinterpret_cast<const float4*>(pr.x + e + 4 * q4));
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (threadIdx.x < kMaxFusedRows) s_qsum[threadIdx.x] = 0;
+        // block-wide reduction of one value per row (rows >= R carry the identity)
+        auto reduce_rows = [&](float (&v)[kMaxFusedRows], bool is_max) {
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                if (m < R) {
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[m], o);
+                        v[m] = is_max ? fmaxf(v[m], other) : v[m] + other;
                     }
-                    const int q0 = static_cast<int>(rintf(__fmul_rn(v.x, scale)));
-                    const int q1 = static_cast<int>(rintf(__fmul_rn(v.y, scale)));
-                    const int q2 = static_cast<int>(rintf(__fmul_rn(v.z, scale)));
-                    const int q3 = static_cast<int>(rintf(__fmul_rn(v.w, scale)));
-                    local_sum += q0 + q1 + q2 + q3;
-                    wds[e] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) |
-                             (static_cast<uint32_t>(q3 & 0xff) << 24);
                 }
-                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, j)) =
-                    transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
             }
-            const float total = block_reduce(static_cast<float>(local_sum), false);  // |sum| <= 127*K < 2^24: exact
-            if (threadIdx.x == 0) {
-                s_scale[m] = __fdiv_rn(denom, pr.q_max);
-                s_qsum[m] = static_cast<int>(total);
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m)
+                if (lane == m && m < R) s_red[warp * kMaxFusedRows + m] = v[m];
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                if (m < R) {
+                    float r = s_red[m];
+                    for (int w = 1; w < kConsumers; ++w)
+                        r = is_max ? fmaxf(r, s_red[w * kMaxFusedRows + m]) : r + s_red[w * kMaxFusedRows + m];
+                    v[m] = r;
+                }
+            }
+        };
+        float red[kMaxFusedRows], inv[kMaxFusedRows];
+#pragma unroll
+        for (int m = 0; m < kMaxFusedRows; ++m) { red[m] = 0.0f; inv[m] = 1.0f; }
+        if (pr.rms_fast) {
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    ss += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
+#pragma unroll
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) red[m] += ss;
+            }
+            reduce_rows(red, false);
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                if (m < R) inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(red[m], static_cast<float>(K)), 1e-6f)));
+                red[m] = 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                float f = 1.0f;
+#pragma unroll
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) f = inv[m];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    xv[i][q4].x = __fmul_rn(xv[i][q4].x, f); xv[i][q4].y = __fmul_rn(xv[i][q4].y, f);
+                    xv[i][q4].z = __fmul_rn(xv[i][q4].z, f); xv[i][q4].w = __fmul_rn(xv[i][q4].w, f);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kGroups; ++i) {
+            float mx = 0.0f;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[i][q4].x), fabsf(xv[i][q4].y)), fmaxf(fabsf(xv[i][q4].z), fabsf(xv[i][q4].w))));
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) red[m] = fmaxf(red[m], mx);
+        }
+        reduce_rows(red, true);
+#pragma unroll
+        for (int i = 0; i < kGroups; ++i) {
+            if (grow[i] >= 0) {
+                float mx = 0.0f;
+#pragma unroll
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) mx = red[m];
+                const float denom = __fadd_rn(mx, 1e-8f);
+                const float scale = __fdiv_rn(pr.q_max, denom);
+                uint32_t wds[4];
+                int local_sum = 0;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int q0 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].x, scale)));
+                    const int q1 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].y, scale)));
+                    const int q2 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].z, scale)));
+                    const int q3 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].w, scale)));
+                    local_sum += q0 + q1 + q2 + q3;
+                    wds[q4] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (static_cast<uint32_t>(q3 & 0xff) << 24);
+                }
+                const int e = (threadIdx.x + i * kT) * 16;
+                const int m = grow[i];
+                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) =
+                    transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
+                atomicAdd(&s_qsum[m], local_sum);
+                if (e == m * K) s_scale[m] = __fdiv_rn(denom, pr.q_max);   // one writer per row
             }
         }
         asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
@@ -257,31 +310,35 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                         // rows m >= R of the slab are stale shared memory: their accumulator columns are
                         // never stored, so the loads need no predicate
                         const uint32_t ablk = ast + b * R * 256;
+                        // Word pairs (0,1) and (2,3) of the lane's chunk feed one MMA each per 2-bit position j.
+                        // Loop order keeps consecutive MMAs on different accumulators (sets j when SCALED,
+                        // activation tiles nt otherwise), so none waits on the one issued just before it.
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            uint4 B[4];
+                        for (int xp = 0; xp < 2; ++xp) {
+                            uint32_t bw[NT][2][4];
 #pragma unroll
-                            for (int x = 0; x < 4; ++x)
-                                B[x] = lds128(ablk + nt * 2048 + aoff[x]);
-                            const uint32_t bw[4][4] = {{B[0].x, B[0].y, B[0].z, B[0].w},
-                                                       {B[1].x, B[1].y, B[1].z, B[1].w},
-                                                       {B[2].x, B[2].y, B[2].z, B[2].w},
-                                                       {B[3].x, B[3].y, B[3].z, B[3].w}};
+                            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const uint4 B = lds128(ablk + nt * 2048 + aoff[2 * xp + h]);
+                                    bw[nt][h][0] = B.x; bw[nt][h][1] = B.y; bw[nt][h][2] = B.z; bw[nt][h][3] = B.w;
+                                }
+                            }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
+                                uint32_t a0, a1, a2, a3;
                                 if (SCALED) {
                                     const uint32_t mk = 0x03030303u << (2 * j);
-                                    mma_u8s8(acc[j][nt], lw[0] & mk, hw[0] & mk, lw[1] & mk, hw[1] & mk,
-                                             bw[0][j], bw[1][j]);
-                                    mma_u8s8(acc[j][nt], lw[2] & mk, hw[2] & mk, lw[3] & mk, hw[3] & mk,
-                                             bw[2][j], bw[3][j]);
+                                    a0 = lw[2 * xp] & mk; a1 = hw[2 * xp] & mk;
+                                    a2 = lw[2 * xp + 1] & mk; a3 = hw[2 * xp + 1] & mk;
                                 } else {
                                     const uint32_t mk = 0x03030303u;
-                                    mma_u8s8(acc[0][nt], (lw[0] >> (2 * j)) & mk, (hw[0] >> (2 * j)) & mk,
-                                             (lw[1] >> (2 * j)) & mk, (hw[1] >> (2 * j)) & mk, bw[0][j], bw[1][j]);
-                                    mma_u8s8(acc[0][nt], (lw[2] >> (2 * j)) & mk, (hw[2] >> (2 * j)) & mk,
-                                             (lw[3] >> (2 * j)) & mk, (hw[3] >> (2 * j)) & mk, bw[2][j], bw[3][j]);
+                                    a0 = (lw[2 * xp] >> (2 * j)) & mk; a1 = (hw[2 * xp] >> (2 * j)) & mk;
+                                    a2 = (lw[2 * xp + 1] >> (2 * j)) & mk; a3 = (hw[2 * xp + 1] >> (2 * j)) & mk;
                                 }
+#pragma unroll
+                                for (int nt = 0; nt < NT; ++nt)
+                                    mma_u8s8(acc[SCALED ? j : 0][nt], a0, a1, a2, a3, bw[nt][0][j], bw[nt][1][j]);
                             }
                         }
                     }
@@ -442,11 +499,11 @@ void set_gemv_events(cudaEvent_t start, cudaEvent_t stop) {
     g_event_stop = stop;
 }
 
-// The fused prologue keeps rows*K bytes of activations resident next to the ring: allow what leaves
-// the ring deep enough (<= 32 KB), at most 8 rows.
+// The fused prologue holds rows*K <= 16384 inputs in registers and keeps their int8 codes resident
+// in shared memory next to the ring; at most 8 rows.
 int gemv_strip_fused_rows(int K) {
     if (!gemv_strip_supported(K)) return 0;
-    const int rows = 32768 / K;
+    const int rows = 16384 / K;
     return rows > 8 ? 8 : rows;
 }
 
@@ -497,7 +554,7 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
         return cudaErrorInvalidValue;
     P.act_rows = P.fused ? 0 : (max_rows < 8 * nt ? max_rows : 8 * nt);
-    const size_t fused_bytes = P.fused ? 256 + ((static_cast<size_t>(problems[0].rows) * problems[0].K + 127) & ~size_t(127)) : 0;
+    const size_t fused_bytes = P.fused ? 1024 + ((static_cast<size_t>(problems[0].rows) * problems[0].K + 127) & ~size_t(127)) : 0;
     const size_t stage_bytes = static_cast<size_t>(P.slots) * (P.ks / 256) * 1024 +
                                static_cast<size_t>(P.ks / 256) * P.act_rows * 256;
     P.stages = kMaxStages;
