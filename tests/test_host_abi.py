@@ -112,3 +112,17 @@ def test_device_entry_points_validate_before_launching(tbl):
     assert tbl.tbl_grouped_forward(arr, 1, P, P, 8, 0, P, 1 << 20, None) == -10
     assert tbl.tbl_launch_count() == before
     assert tbl.tbl_linear_workspace_bytes(8, 1024, 64) >= 2 * 8 * 1024
+
+
+def test_header_is_plain_c_and_links(tbl, tmp_path):
+    """A C99 program built with gcc against the header and the shared library runs the host packer."""
+    import subprocess
+    from reimagined_b200 import capi
+    exe = tmp_path / "abi_check"
+    lib_dir = os.path.dirname(capi.LIB_PATH)
+    subprocess.run(["/usr/bin/gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "abi_check.c"), "-o", str(exe),
+                    "-L", lib_dir, "-lternary_b200", "-Wl,-rpath," + lib_dir, "-lm"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, f"abi_check exited {out.returncode}: {out.stdout} {out.stderr}"
+    assert "abi ok" in out.stdout
