@@ -112,6 +112,12 @@ __device__ __forceinline__ float round_tie(float v, bool away) {
     return away ? roundf(v) : rintf(v);
 }
 
+// Programmatic dependent launch (both are no-ops in a kernel that was launched without the attribute).
+// launch_dependents: the next kernel of the stream may be scheduled once every CTA has issued it.
+// wait: blocks until the preceding kernel has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // The reference's epilogue, one separately rounded fp32 operation per step:
 // float(acc) * (act_scale*weight_scale), then * magnitude, then + bias.
 __device__ __forceinline__ float epilogue(int acc, float combined_scale, const float* magnitude,

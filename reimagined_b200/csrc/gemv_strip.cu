@@ -36,6 +36,7 @@ struct StripParams {
     int act_rows; // activation rows held per stage (<= 8*NT); 0 when the activations are resident
     int fused;    // 1: prob[0].x is quantised in the prologue into a resident shared-memory copy
     int* status;
+    long long weight_bytes;   // of all problems, for the launcher
 };
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -74,6 +75,10 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     const uint32_t acts_resident_addr = smem_u32(acts_resident);
     const int nstages = P.stages;
 
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as every
+    // CTA of this grid has got here; it can then set up and prefetch weights while this grid drains.
+    pdl_launch_dependents();
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(&full[s], 1);
@@ -92,6 +97,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         const StripProblem& pr = P.prob[0];
         const int K = pr.K, R = pr.rows;
         constexpr int kT = kConsumers * 32;
+        pdl_wait();   // x may be the output of the kernel before this one
         constexpr int kMaxFusedRows = 8;
         constexpr int kGroups = 16384 / 16 / kT;     // 16-element groups per thread
         const int total_groups = R * K / 16;
@@ -215,6 +221,11 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     const int s_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_strips / gridDim.x);
     const bool producer = warp == kConsumers;
     const int slot = warp / WPS, part = warp % WPS;
+    // Everything but the weights (quantised activations, their scales and sums, row counts) may come
+    // from the preceding kernel: consumers wait for it here, the producer just before its first
+    // activation copy, so the first weight stage is already in flight.
+    bool upstream_done = P.fused != 0;
+    if (!producer && !upstream_done) { pdl_wait(); upstream_done = true; }
     const int g = lane >> 2, t = lane & 3;
     // byte offset, inside a 256-byte activation row block, of the 16-byte group (quarter x, chunk t)
     // of activation row g (row nt*8+g adds nt*2048; the XOR term is the same since 8 is even)
@@ -234,6 +245,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         const int cnt = min(P.slots, min(s_end - s, nstrips - local));
         s += cnt;
         int rows = pr.rows;
+        if ((pr.rows_dev || pr.offset_dev) && !upstream_done) { pdl_wait(); upstream_done = true; }
         if (pr.rows_dev) rows = min(rows, __ldg(pr.rows_dev));
         if (rows <= 0) continue;
         const int row0 = pr.offset_dev ? __ldg(pr.offset_dev) : 0;
@@ -266,13 +278,21 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                     const int bs = min(4, nblk - 4 * slab);
                     const uint8_t* slab_src = pr.strips + ((static_cast<size_t>(4) * slab * nstrips +
                                                             static_cast<size_t>(local) * bs) << 10);
-                    if (nb == bs) {
-                        // the stage is the whole slab of cnt adjacent strips: one contiguous copy
-                        if (lane == 0) bulk_g2s(wst, slab_src, cnt * nb * 1024, &full[st]);
+                    if (nblk_stage >= 4) {
+                        // the stage is one or more whole slabs of cnt adjacent strips: one contiguous copy
+                        // per slab, laid out [slab][strip][block in slab]
+                        if (lane < ((nb + 3) >> 2)) {
+                            const int sl = slab + lane;
+                            const int sbs = min(4, nblk - 4 * sl);
+                            bulk_g2s(wst + lane * cnt * 4096,
+                                     pr.strips + ((static_cast<size_t>(4) * sl * nstrips + static_cast<size_t>(local) * sbs) << 10),
+                                     cnt * sbs * 1024, &full[st]);
+                        }
                     } else if (lane < cnt) {
                         bulk_g2s(wst + lane * nb * 1024, slab_src + ((static_cast<size_t>(lane) * bs + bin) << 10),
                                  nb * 1024, &full[st]);
                     }
+                    if (!upstream_done) { pdl_wait(); upstream_done = true; }
                     if (lane == kStripSlots && !P.fused)
                         bulk_g2s(wst + wstage, qtile + static_cast<size_t>(b0) * R * 256, nb * R * 256,
                                  &full[st]);
@@ -296,20 +316,16 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 if (active) {
                     const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
                     const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
-                    const uint32_t wst = stage_addr + slot * nb * 1024 + lane * 16;
                     // activations: this stage's slab, or the resident copy at the stage's first block
                     const uint32_t ast = P.fused ? acts_resident_addr + ksi * nblk_stage * R * 256 : stage_addr + wstage;
-                    // blocks of this stage are global blocks ksi*nblk_stage + b; this warp takes its residue class
-                    const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
-#pragma unroll 2
-                    for (int b = first; b < nb; b += WPS) {
-                        const uint4 lo = lds128(wst + b * 1024);
-                        const uint4 hi = lds128(wst + b * 1024 + 512);
+                    // one 1 KB weight block (lane's two 16-byte chunks at wblk, wblk + 512) against the
+                    // activation block at ablk.  Rows m >= R of that block are stale shared memory: their
+                    // accumulator columns are never stored, so the loads need no predicate.
+                    auto process_block = [&](const uint32_t wblk, const uint32_t ablk) {
+                        const uint4 lo = lds128(wblk);
+                        const uint4 hi = lds128(wblk + 512);
                         const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
                         const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
-                        // rows m >= R of the slab are stale shared memory: their accumulator columns are
-                        // never stored, so the loads need no predicate
-                        const uint32_t ablk = ast + b * R * 256;
                         // Word pairs (0,1) and (2,3) of the lane's chunk feed one MMA each per 2-bit position j.
                         // Loop order keeps consecutive MMAs on different accumulators (sets j when SCALED,
                         // activation tiles nt otherwise), so none waits on the one issued just before it.
@@ -341,6 +357,29 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                                     mma_u8s8(acc[SCALED ? j : 0][nt], a0, a1, a2, a3, bw[nt][0][j], bw[nt][1][j]);
                             }
                         }
+                    };
+                    if (nblk_stage >= 4) {
+                        // stage layout [slab][strip][block in slab]; blocks of this stage are global blocks
+                        // ksi*nblk_stage + 4*sl + bin and this warp takes its residue class modulo WPS
+                        static_assert(4 % WPS == 0, "a slab must split evenly over the warps of a strip");
+                        const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
+                        const uint32_t astep = WPS * R * 256;
+                        for (int sl = 0; 4 * sl < nb; ++sl) {
+                            const int sbs = min(4, nb - 4 * sl);
+                            const uint32_t wslab = stage_addr + lane * 16 + sl * cnt * 4096 + (slot * sbs + first) * 1024;
+                            uint32_t ablk = ast + (4 * sl + first) * R * 256;
+#pragma unroll
+                            for (int i = 0; i < 4 / WPS; ++i) {
+                                if (first + i * WPS < sbs) process_block(wslab + i * WPS * 1024, ablk);
+                                ablk += astep;
+                            }
+                        }
+                    } else {
+                        // stage layout [strip][block]
+                        const uint32_t wst = stage_addr + slot * nb * 1024 + lane * 16;
+                        const int first = (part + WPS - (ksi * nblk_stage) % WPS) % WPS;
+#pragma unroll 2
+                        for (int b = first; b < nb; b += WPS) process_block(wst + b * 1024, ast + b * R * 256);
                     }
                 }
                 __syncwarp();
@@ -486,10 +525,23 @@ cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStre
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     if (g_event_start) cudaEventRecord(g_event_start, stream);
-    kernel<<<grid, (kStripSlots * WPS + 1) * 32, smem, stream>>>(P);
+    // launched as a programmatic dependent of the preceding kernel of the stream (the kernel orders
+    // itself after that kernel with griddepcontrol.wait before it touches anything but the weights)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((kStripSlots * WPS + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    // measured: the overlap pays for short kernels (4096^2: 7.0 -> 6.2 us) and costs a long one 2 %
+    cfg.numAttrs = P.weight_bytes <= (32ll << 20) ? 1 : 0;
+    const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, P);
     if (g_event_stop) cudaEventRecord(g_event_stop, stream);
     note_launch();
-    return cudaGetLastError();
+    return launched != cudaSuccess ? launched : cudaGetLastError();
 }
 
 }  // namespace
@@ -537,11 +589,16 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
         P.prob[i] = problems[i];
         P.prob[i].strip_begin = total;
         total += (problems[i].N + 15) / 16;
+        P.weight_bytes += static_cast<long long>((problems[i].N + 15) / 16) * 4 * problems[i].K;
     }
     P.total_strips = total;
     const int nt = max_rows <= 8 ? 1 : (max_rows <= 16 ? 2 : (max_rows <= 32 ? 4 : 8));
-    // stage depth in k: 1024 keeps each strip copy at 4 KB; shrink for tall activation tiles
-    P.ks = nt <= 2 ? 1024 : 512;
+    // Stage depth in k.  Two slabs (2048) per stage halve the per-stage synchronisation of a consumer warp
+    // (16384^2, M = 1: 20.8 -> 18.5 us); three are no better, with only two stages left in the ring.
+    // Tall activation tiles leave room for half a slab only.
+    int max_k = 0;
+    for (int i = 0; i < count; ++i) max_k = problems[i].K > max_k ? problems[i].K : max_k;
+    P.ks = nt <= 2 ? (max_k >= 2048 ? 2048 : 1024) : 512;
     int grid = (total + kStripSlots - 1) / kStripSlots;
     if (grid > kNumSm) grid = kNumSm;
     // spread small problems over more SMs (fewer strips per CTA)
@@ -557,8 +614,12 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const size_t fused_bytes = P.fused ? 1024 + ((static_cast<size_t>(problems[0].rows) * problems[0].K + 127) & ~size_t(127)) : 0;
     const size_t stage_bytes = static_cast<size_t>(P.slots) * (P.ks / 256) * 1024 +
                                static_cast<size_t>(P.ks / 256) * P.act_rows * 256;
-    P.stages = kMaxStages;
-    while (P.stages > 2 && 128 + fused_bytes + P.stages * stage_bytes > 208 * 1024) --P.stages;
+    // the ring takes what the 227 KB of a CTA leave after the fixed parts (barriers, fused quantiser state,
+    // the slack below and the cross-warp reduction buffer the launcher adds for the two-warps-per-strip variant)
+    const size_t fixed = 128 + fused_bytes + static_cast<size_t>(8 * nt) * 256 + (nt == 1 ? kStripSlots * 32 * 4 * 4 : 0);
+    const size_t room = 227 * 1024 - fixed;
+    P.stages = static_cast<int>(room / stage_bytes < static_cast<size_t>(kMaxStages) ? room / stage_bytes : kMaxStages);
+    if (P.stages < 2) return cudaErrorInvalidValue;
     // slack after the last stage: lanes of activation rows >= act_rows read (and ignore) stale bytes
     const size_t smem = 128 + fused_bytes + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
     switch (nt) {
