@@ -49,7 +49,12 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 
 // WPS warps share one strip: warp `part` of a strip takes the 1 KB blocks b with b % WPS == part and
 // the partial sums meet in shared memory before the epilogue (more warps in flight per SM).
-template <int NT, bool SCALED, int WPS>
+//
+// FAST is the single-row decode case (one activation row quantised in the prologue, K a multiple of
+// the 2048-deep stage): every shared-memory offset of a stage is then a compile-time constant off three
+// base registers, the four blocks of a warp are fully unrolled, and all lanes read row 0's activation
+// fragment (one 128-byte wavefront per load instead of four).
+template <int NT, bool SCALED, int WPS, bool FAST>
 __global__ void __launch_bounds__((kStripSlots * WPS + 1) * 32, 1)
 gemv_strip_kernel(const __grid_constant__ StripParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -358,7 +363,36 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                             }
                         }
                     };
-                    if (nblk_stage >= 4) {
+                    if constexpr (FAST) {
+                        static_assert(NT == 1 && WPS == 2 && SCALED, "single-row fast path");
+                        // blocks part, part+2 of both slabs; activation block b of the resident row at b*256
+                        const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
+                        const uint32_t w1 = w0 + cnt * 4096;
+                        const uint32_t a0 = acts_resident_addr + t * 16 + (ksi * 8 + part) * 256;
+                        auto fast_block = [&](const uint32_t wblk, const uint32_t ablk) {
+                            const uint4 lo = lds128(wblk);
+                            const uint4 hi = lds128(wblk + 512);
+                            const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
+                            const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                            for (int xp = 0; xp < 2; ++xp) {
+                                const uint4 B0 = lds128(ablk + (2 * xp) * 64);
+                                const uint4 B1 = lds128(ablk + (2 * xp + 1) * 64);
+                                const uint32_t b0[4] = {B0.x, B0.y, B0.z, B0.w};
+                                const uint32_t b1[4] = {B1.x, B1.y, B1.z, B1.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t mk = 0x03030303u << (2 * j);
+                                    mma_u8s8(acc[j][0], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
+                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                }
+                            }
+                        };
+                        fast_block(w0, a0);
+                        fast_block(w0 + 2048, a0 + 512);
+                        fast_block(w1, a0 + 1024);
+                        fast_block(w1 + 2048, a0 + 1536);
+                    } else if (nblk_stage >= 4) {
                         // stage layout [slab][strip][block in slab]; blocks of this stage are global blocks
                         // ksi*nblk_stage + 4*sl + bin and this warp takes its residue class modulo WPS
                         static_assert(4 % WPS == 0, "a slab must split evenly over the warps of a strip");
@@ -512,9 +546,9 @@ __global__ void __launch_bounds__(256) permute_q_kernel(const int8_t* __restrict
 
 cudaEvent_t g_event_start = nullptr, g_event_stop = nullptr;
 
-template <int NT, bool SCALED, int WPS>
+template <int NT, bool SCALED, int WPS, bool FAST = false>
 cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStream_t stream) {
-    auto kernel = gemv_strip_kernel<NT, SCALED, WPS>;
+    auto kernel = gemv_strip_kernel<NT, SCALED, WPS, FAST>;
     smem += WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
     static bool configured[64] = {};
     int dev = 0;
@@ -623,7 +657,10 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     // slack after the last stage: lanes of activation rows >= act_rows read (and ignore) stale bytes
     const size_t smem = 128 + fused_bytes + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
     switch (nt) {
-        case 1: return launch_variant<1, true, 2>(P, grid, smem, stream);
+        case 1:
+            if (P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0)
+                return launch_variant<1, true, 2, true>(P, grid, smem, stream);
+            return launch_variant<1, true, 2>(P, grid, smem, stream);
         case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);
         case 4: return launch_variant<4, true, 1>(P, grid, smem, stream);
         default: return launch_variant<8, false, 1>(P, grid, smem, stream);
