@@ -30,8 +30,10 @@ struct StripParams {
     StripProblem prob[TBL_MAX_GROUPS];
     int count;
     int total_strips;
+    int share_base, share_rem;   // CTA b owns share_base strips, one more when b < share_rem
     int ks;       // k per stage, multiple of 256
     int stages;
+    int stage_shift;   // log2(ks / 256)
     int slots;    // strips per pass (<= kStripSlots): sized to the CTA's share so no stage space idles
     int act_rows; // activation rows held per stage (<= 8*NT); 0 when the activations are resident
     int fused;    // 1: prob[0].x is quantised in the prologue into a resident shared-memory copy
@@ -84,6 +86,8 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
     // CTA of this grid has got here; it can then set up and prefetch weights while this grid drains.
     pdl_launch_dependents();
 
+    uint32_t* s_amax = reinterpret_cast<uint32_t*>(s_red + 16 * 8);      // [8] row absmax as bit patterns
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(&full[s], 1);
@@ -92,29 +96,33 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         fence_mbar_init();
         fence_proxy_async();
     }
+    if (P.fused && threadIdx.x < 8) { s_qsum[threadIdx.x] = 0; s_amax[threadIdx.x] = 0u; }
     __syncthreads();
 
     if (P.fused && warp < kConsumers) {
         // ---- fused per-token absmax quantiser (consumer warps only; the producer warp is already
         // streaming weights).  Same arithmetic as the stand-alone quantiser kernel.  The rows*K <= 16384
-        // inputs are read from memory once, 16 consecutive elements x 2 groups per thread, and stay in
-        // registers between the absmax reduction and the rounding. ----
+        // inputs are read once, 16 consecutive elements per group and up to two groups per thread, and
+        // stay in registers between the absmax reduction and the rounding. ----
         const StripProblem& pr = P.prob[0];
         const int K = pr.K, R = pr.rows;
         constexpr int kT = kConsumers * 32;
-        pdl_wait();   // x may be the output of the kernel before this one
         constexpr int kMaxFusedRows = 8;
         constexpr int kGroups = 16384 / 16 / kT;     // 16-element groups per thread
         const int total_groups = R * K / 16;
+        pdl_wait();   // x may be the output of the kernel before this one
         float4 xv[kGroups][4];
         int grow[kGroups];
 #pragma unroll
         for (int i = 0; i < kGroups; ++i) {
-            const int G = threadIdx.x + i * kT;
+            const int Gl = threadIdx.x + i * kT;
             grow[i] = -1;
-            if (G < total_groups) {
-                const int e = G * 16;
-                grow[i] = e / K;
+            if (Gl < total_groups) {
+                const int e = Gl * 16;
+                int row = 0;
+#pragma unroll
+                for (int m = 1; m < kMaxFusedRows; ++m) row += e >= m * K ? 1 : 0;
+                grow[i] = row;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = __ldg(reinterpret_cast<const float4*>(pr.x + e + 4 * q4));
             } else {
@@ -122,52 +130,43 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        if (threadIdx.x < kMaxFusedRows) s_qsum[threadIdx.x] = 0;
-        // block-wide reduction of one value per row (rows >= R carry the identity)
-        auto reduce_rows = [&](float (&v)[kMaxFusedRows], bool is_max) {
-#pragma unroll
-            for (int m = 0; m < kMaxFusedRows; ++m) {
-                if (m < R) {
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v[m], o);
-                        v[m] = is_max ? fmaxf(v[m], other) : v[m] + other;
-                    }
-                }
-            }
-            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
-#pragma unroll
-            for (int m = 0; m < kMaxFusedRows; ++m)
-                if (lane == m && m < R) s_red[warp * kMaxFusedRows + m] = v[m];
-            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
-#pragma unroll
-            for (int m = 0; m < kMaxFusedRows; ++m) {
-                if (m < R) {
-                    float r = s_red[m];
-                    for (int w = 1; w < kConsumers; ++w)
-                        r = is_max ? fmaxf(r, s_red[w * kMaxFusedRows + m]) : r + s_red[w * kMaxFusedRows + m];
-                    v[m] = r;
-                }
-            }
-        };
-        float red[kMaxFusedRows], inv[kMaxFusedRows];
-#pragma unroll
-        for (int m = 0; m < kMaxFusedRows; ++m) { red[m] = 0.0f; inv[m] = 1.0f; }
+        // The loads above are in the memory pipeline: only now may the producer warp queue its (much
+        // larger) weight copies behind them.  Issued the other way round, x waits for up to a ring of
+        // weights (measured: 3.5K .. 10.5K cycles until the last x load returned, against ~2K).
+        asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
         if (pr.rms_fast) {
+            // per-row sum of squares: thread partials, warp shuffles, then a
+            // fixed-order sum over the warps
+            float ss[kMaxFusedRows];
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) ss[m] = 0.0f;
 #pragma unroll
             for (int i = 0; i < kGroups; ++i) {
-                float ss = 0.0f;
+                float q = 0.0f;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
-                    ss += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
+                    q += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
 #pragma unroll
-                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) red[m] += ss;
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) ss[m] += q;
             }
-            reduce_rows(red, false);
 #pragma unroll
             for (int m = 0; m < kMaxFusedRows; ++m) {
-                if (m < R) inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(red[m], static_cast<float>(K)), 1e-6f)));
-                red[m] = 0.0f;
+                if (m < R) {
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+                    if (lane == 0) s_red[warp * kMaxFusedRows + m] = ss[m];
+                }
+            }
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+            float inv[kMaxFusedRows];
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                inv[m] = 1.0f;
+                if (m < R) {
+                    float r = s_red[m];
+                    for (int w = 1; w < kConsumers; ++w) r += s_red[w * kMaxFusedRows + m];
+                    inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(r, static_cast<float>(K)), 1e-6f)));
+                }
             }
 #pragma unroll
             for (int i = 0; i < kGroups; ++i) {
@@ -181,50 +180,76 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 }
             }
         }
+        // absmax: thread maxima (fmaxf drops NaNs), one redux and one shared atomic max per warp and row;
+        // non-negative floats order like their bit patterns
+        {
+            float mx[kMaxFusedRows];
 #pragma unroll
-        for (int i = 0; i < kGroups; ++i) {
-            float mx = 0.0f;
+            for (int m = 0; m < kMaxFusedRows; ++m) mx[m] = 0.0f;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[i][q4].x), fabsf(xv[i][q4].y)), fmaxf(fabsf(xv[i][q4].z), fabsf(xv[i][q4].w))));
+            for (int i = 0; i < kGroups; ++i) {
+                float q = 0.0f;
 #pragma unroll
-            for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) red[m] = fmaxf(red[m], mx);
+                for (int q4 = 0; q4 < 4; ++q4)
+                    q = fmaxf(q, fmaxf(fmaxf(fabsf(xv[i][q4].x), fabsf(xv[i][q4].y)), fmaxf(fabsf(xv[i][q4].z), fabsf(xv[i][q4].w))));
+#pragma unroll
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) mx[m] = fmaxf(mx[m], q);
+            }
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                if (m < R) {
+                    const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(mx[m]));
+                    if (lane == 0 && wmax != 0u) atomicMax(&s_amax[m], wmax);
+                }
+            }
         }
-        reduce_rows(red, true);
+        asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+        // rounding: q = rint(x * scale) by adding 1.5 * 2^23 (round-to-nearest-even at integer granularity,
+        // exact for |x * scale| < 2^22): the low byte of the sum's bit pattern is the int8 code
+        int qsum[kMaxFusedRows];
+#pragma unroll
+        for (int m = 0; m < kMaxFusedRows; ++m) qsum[m] = 0;
 #pragma unroll
         for (int i = 0; i < kGroups; ++i) {
             if (grow[i] >= 0) {
-                float mx = 0.0f;
-#pragma unroll
-                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) mx = red[m];
-                const float denom = __fadd_rn(mx, 1e-8f);
+                const int m = grow[i];
+                const float denom = __fadd_rn(__uint_as_float(s_amax[m]), 1e-8f);
                 const float scale = __fdiv_rn(pr.q_max, denom);
                 uint32_t wds[4];
-                int local_sum = 0;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int q0 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].x, scale)));
-                    const int q1 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].y, scale)));
-                    const int q2 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].z, scale)));
-                    const int q3 = static_cast<int>(rintf(__fmul_rn(xv[i][q4].w, scale)));
-                    local_sum += q0 + q1 + q2 + q3;
-                    wds[q4] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (static_cast<uint32_t>(q3 & 0xff) << 24);
+                    const uint32_t c0 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].x, scale), 12582912.0f));
+                    const uint32_t c1 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].y, scale), 12582912.0f));
+                    const uint32_t c2 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].z, scale), 12582912.0f));
+                    const uint32_t c3 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].w, scale), 12582912.0f));
+                    wds[q4] = __byte_perm(__byte_perm(c0, c1, 0x0040), __byte_perm(c2, c3, 0x0040), 0x5410);
+                    const int s4 = dp4a_ss(static_cast<int>(wds[q4]), 0x01010101, 0);
+#pragma unroll
+                    for (int r = 0; r < kMaxFusedRows; ++r) if (m == r) qsum[r] += s4;
                 }
                 const int e = (threadIdx.x + i * kT) * 16;
-                const int m = grow[i];
-                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) =
-                    transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
-                atomicAdd(&s_qsum[m], local_sum);
-                if (e == m * K) s_scale[m] = __fdiv_rn(denom, pr.q_max);   // one writer per row
+                const uint4 codes = transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
+                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) = codes;
             }
         }
+#pragma unroll
+        for (int m = 0; m < kMaxFusedRows; ++m) {
+            if (m < R) {
+                const int wsum = __reduce_add_sync(0xffffffffu, qsum[m]);
+                if (lane == 0 && wsum != 0) atomicAdd(&s_qsum[m], wsum);
+            }
+        }
+        if (static_cast<int>(threadIdx.x) < R)
+            s_scale[threadIdx.x] = __fdiv_rn(__fadd_rn(__uint_as_float(s_amax[threadIdx.x]), 1e-8f), pr.q_max);
         asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
     }
 
     // contiguous, balanced share of the global strip list
-    const int s_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_strips / gridDim.x);
-    const int s_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_strips / gridDim.x);
+    const int bid = static_cast<int>(blockIdx.x);
+    const int s_begin = bid * P.share_base + min(bid, P.share_rem);
+    const int s_end = s_begin + P.share_base + (bid < P.share_rem ? 1 : 0);
     const bool producer = warp == kConsumers;
+    if (producer && P.fused) asm volatile("bar.sync 11, %0;" ::"r"(kConsumers * 32 + 32) : "memory");
     const int slot = warp / WPS, part = warp % WPS;
     // Everything but the weights (quantised activations, their scales and sums, row counts) may come
     // from the preceding kernel: consumers wait for it here, the producer just before its first
@@ -255,7 +280,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
         if (rows <= 0) continue;
         const int row0 = pr.offset_dev ? __ldg(pr.offset_dev) : 0;
         const int nblk = K >> 8;
-        const int ksteps = (nblk + nblk_stage - 1) / nblk_stage;
+        const int ksteps = (nblk + nblk_stage - 1) >> P.stage_shift;   // nblk_stage = 1 << stage_shift
         const int mtiles = (rows + MPAD - 1) / MPAD;   // > 1 only in the NT = 8 variant
         const int8_t* qsrc = pr.qp + static_cast<size_t>(row0) * K;
 
@@ -318,6 +343,7 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 alive = mbar_wait_bounded(&full[st], (it / nstages) & 1, P.status);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
+
                 if (active) {
                     const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
                     const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
@@ -369,17 +395,24 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                         const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
                         const uint32_t w1 = w0 + cnt * 4096;
                         const uint32_t a0 = acts_resident_addr + t * 16 + (ksi * 8 + part) * 256;
-                        auto fast_block = [&](const uint32_t wblk, const uint32_t ablk) {
-                            const uint4 lo = lds128(wblk);
-                            const uint4 hi = lds128(wblk + 512);
-                            const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
-                            const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
+                        // software pipeline: the six shared loads of a block are issued before the MMAs of
+                        // the block ahead of it (the asm statements keep this order)
+                        struct Operands { uint4 lo, hi, b[4]; };
+                        auto load_block = [&](const uint32_t wblk, const uint32_t ablk) {
+                            Operands o;
+                            o.lo = lds128(wblk);
+                            o.hi = lds128(wblk + 512);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + x * 64);
+                            return o;
+                        };
+                        auto mma_block = [&](const Operands& o) {
+                            const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
+                            const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
 #pragma unroll
                             for (int xp = 0; xp < 2; ++xp) {
-                                const uint4 B0 = lds128(ablk + (2 * xp) * 64);
-                                const uint4 B1 = lds128(ablk + (2 * xp + 1) * 64);
-                                const uint32_t b0[4] = {B0.x, B0.y, B0.z, B0.w};
-                                const uint32_t b1[4] = {B1.x, B1.y, B1.z, B1.w};
+                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
+                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const uint32_t mk = 0x03030303u << (2 * j);
@@ -388,10 +421,14 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                                 }
                             }
                         };
-                        fast_block(w0, a0);
-                        fast_block(w0 + 2048, a0 + 512);
-                        fast_block(w1, a0 + 1024);
-                        fast_block(w1 + 2048, a0 + 1536);
+                        const Operands o0 = load_block(w0, a0);
+                        const Operands o1 = load_block(w0 + 2048, a0 + 512);
+                        mma_block(o0);
+                        const Operands o2 = load_block(w1, a0 + 1024);
+                        mma_block(o1);
+                        const Operands o3 = load_block(w1 + 2048, a0 + 1536);
+                        mma_block(o2);
+                        mma_block(o3);
                     } else if (nblk_stage >= 4) {
                         // stage layout [slab][strip][block in slab]; blocks of this stage are global blocks
                         // ksi*nblk_stage + 4*sl + bin and this warp takes its residue class modulo WPS
@@ -566,12 +603,16 @@ cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStre
     cfg.blockDim = dim3((kStripSlots * WPS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
+    cudaLaunchAttribute attrs[2]{};
+    int na = 0;
     // measured: the overlap pays for short kernels (4096^2: 7.0 -> 6.2 us) and costs a long one 2 %
-    cfg.numAttrs = P.weight_bytes <= (32ll << 20) ? 1 : 0;
+    if (P.weight_bytes <= (32ll << 20)) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
     const cudaError_t launched = cudaLaunchKernelEx(&cfg, kernel, P);
     if (g_event_stop) cudaEventRecord(g_event_stop, stream);
     note_launch();
@@ -633,17 +674,21 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     int max_k = 0;
     for (int i = 0; i < count; ++i) max_k = problems[i].K > max_k ? problems[i].K : max_k;
     P.ks = nt <= 2 ? (max_k >= 2048 ? 2048 : 1024) : 512;
+    P.stage_shift = P.ks == 2048 ? 3 : (P.ks == 1024 ? 2 : 1);
     int grid = (total + kStripSlots - 1) / kStripSlots;
     if (grid > kNumSm) grid = kNumSm;
     // spread small problems over more SMs (fewer strips per CTA)
     if (total < kNumSm * kStripSlots) grid = total < kNumSm ? total : kNumSm;
-    // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
-    const int share = (total + grid - 1) / grid;
-    const int passes = (share + kStripSlots - 1) / kStripSlots;
-    P.slots = (share + passes - 1) / passes;
     P.fused = count == 1 && problems[0].x != nullptr;
     if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
         return cudaErrorInvalidValue;
+    const bool fast = nt == 1 && P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0;
+    // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
+    P.share_base = total / grid;
+    P.share_rem = total % grid;
+    const int share = (total + grid - 1) / grid;
+    const int passes = (share + kStripSlots - 1) / kStripSlots;
+    P.slots = (share + passes - 1) / passes;
     P.act_rows = P.fused ? 0 : (max_rows < 8 * nt ? max_rows : 8 * nt);
     const size_t fused_bytes = P.fused ? 1024 + ((static_cast<size_t>(problems[0].rows) * problems[0].K + 127) & ~size_t(127)) : 0;
     const size_t stage_bytes = static_cast<size_t>(P.slots) * (P.ks / 256) * 1024 +
@@ -658,7 +703,7 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const size_t smem = 128 + fused_bytes + P.stages * stage_bytes + static_cast<size_t>(8 * nt) * 256;
     switch (nt) {
         case 1:
-            if (P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0)
+            if (fast)
                 return launch_variant<1, true, 2, true>(P, grid, smem, stream);
             return launch_variant<1, true, 2>(P, grid, smem, stream);
         case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);
