@@ -108,6 +108,14 @@ __host__ __device__ __forceinline__ float qmax_for_bits(int bits) {
 }
 
 // Rounds v to an integer-valued float with the requested tie rule.
+// Integer code of v (|v| < 2^22).  Ties-to-even is done on the FMA pipe: v + 1.5 * 2^23 rounds to
+// nearest-even at integer granularity and leaves the integer in the low mantissa bits (float-to-int
+// conversions run on the quarter-rate XU pipe, which bounds a quantiser that converts every element).
+__device__ __forceinline__ int round_code(float v, bool away) {
+    if (away) return static_cast<int>(roundf(v));
+    return __float_as_int(__fadd_rn(v, 12582912.0f)) - 0x4B400000;
+}
+
 __device__ __forceinline__ float round_tie(float v, bool away) {
     return away ? roundf(v) : rintf(v);
 }

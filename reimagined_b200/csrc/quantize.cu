@@ -171,12 +171,12 @@ quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ ro
                     v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
                     v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
                 }
-                const int a = static_cast<int>(round_tie(__fmul_rn(v.x, scale), tie_away));
-                const int b = static_cast<int>(round_tie(__fmul_rn(v.y, scale), tie_away));
-                const int c = static_cast<int>(round_tie(__fmul_rn(v.z, scale), tie_away));
-                const int d = static_cast<int>(round_tie(__fmul_rn(v.w, scale), tie_away));
-                local_sum += a + b + c + d;
+                const int a = round_code(__fmul_rn(v.x, scale), tie_away);
+                const int b = round_code(__fmul_rn(v.y, scale), tie_away);
+                const int c = round_code(__fmul_rn(v.z, scale), tie_away);
+                const int d = round_code(__fmul_rn(v.w, scale), tie_away);
                 words[e] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+                local_sum = dp4a_ss(static_cast<int>(words[e]), 0x01010101, local_sum);   // the sum of the stored codes
             }
             const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
             if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
@@ -297,12 +297,12 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
             uint32_t words[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int a = static_cast<int>(round_tie(__fmul_rn(v[i][e].x, scale), tie_away));
-                const int b = static_cast<int>(round_tie(__fmul_rn(v[i][e].y, scale), tie_away));
-                const int c = static_cast<int>(round_tie(__fmul_rn(v[i][e].z, scale), tie_away));
-                const int d = static_cast<int>(round_tie(__fmul_rn(v[i][e].w, scale), tie_away));
-                local_sum += a + b + c + d;
+                const int a = round_code(__fmul_rn(v[i][e].x, scale), tie_away);
+                const int b = round_code(__fmul_rn(v[i][e].y, scale), tie_away);
+                const int c = round_code(__fmul_rn(v[i][e].z, scale), tie_away);
+                const int d = round_code(__fmul_rn(v[i][e].w, scale), tie_away);
                 words[e] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+                local_sum = dp4a_ss(static_cast<int>(words[e]), 0x01010101, local_sum);   // the sum of the stored codes
             }
             const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
             if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
