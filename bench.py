@@ -326,7 +326,7 @@ def run_ours(args):
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gemv_strip_kernel<1,true,2> (quantiser fused)", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "gemv_strip_kernel<1,true,2,true> (quantiser fused, single-row path)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "kernel_us": kernel_ms * 1e3,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
@@ -353,7 +353,7 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_strip_kernel launch at K = N = 16384, M = 1,
 # from the ncu capture summarised in profiles/gemv_strip_16384x16384_m1.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 67240448 + 1207040
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 67235584 + 899328
 
 
 def main():
