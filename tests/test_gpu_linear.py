@@ -45,6 +45,39 @@ def test_quantize_rows_bit_exact(cuda, port, tbl, M, K, bits):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,K", [(256, 2048), (300, 4096), (449, 8192), (256, 16384), (257, 8208), (1000, 12288)])
+@pytest.mark.parametrize("bits,tie", [(8, 0), (4, 1)])
+def test_quantize_rows_prefill_sized_bit_exact(cuda, port, tbl, M, K, bits, tie):
+    """Many rows: the persistent streaming quantiser (K >= 8192: rows dealt round-robin to 148 CTAs, ragged
+    last round, gathered rows, zero rows) and the one-CTA-per-row kernel below that, against the oracle."""
+    import gpu_helpers as H
+    rng = np.random.default_rng(M + K + bits)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.01, 50, size=(M, 1))).astype(np.float32)
+    x[5] = 0.0
+    x[7, ::2] = 0.5 * np.abs(x[7]).max() / 127.0 * 3.0     # values on rounding boundaries
+    idx = rng.permutation(M).astype(np.int32)
+    q, sc, sums = H.quantize_rows(H.dev(x), bits=bits, tie_mode=tie, row_index=H.dev(idx))
+    oq, osc = port.quantize_rows(x[idx], bits=bits, tie_mode=tie)
+    assert np.array_equal(q.cpu().numpy(), oq)
+    assert bits_equal(sc.cpu().numpy(), osc)
+    assert np.array_equal(sums.cpu().numpy(), oq.astype(np.int32).sum(axis=1))
+    assert H.device_status() == 0
+
+
+def test_prefill_linear_reference_order_rms_wide_rows(cuda, port, tbl):
+    """M > 64 at K = 8192 with the reference-order RMSNorm: rms kernel -> streaming quantiser -> tcgen05 GEMM."""
+    import gpu_helpers as H
+    N, K, M = 48, 8192, 200
+    w, x, mag, bias = make_case(99, N, K, M, affine=True)
+    words, scale, t, _ = port.pack_weights(w)
+    oy, *_ = port.linear_forward(x, words, scale, N, rms_input=1, magnitude=mag, bias=bias)
+    dwords = H.words_dev(words)
+    y = H.linear_forward(H.dev(x), dwords, scale, N, w_i8=H.expand_i8(dwords, N, K), rms_mode=2,
+                         magnitude=H.dev(mag), bias=H.dev(bias))
+    assert bits_equal(y.cpu().numpy(), oy), f"max diff {np.abs(y.cpu().numpy() - oy).max()}"
+    assert H.device_status() == 0
+
+
 def test_quantize_ties_zero_rows_and_gather(cuda, port, tbl):
     import gpu_helpers as H
     x = np.zeros((3, 32), np.float32)
