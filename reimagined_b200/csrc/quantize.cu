@@ -1,6 +1,8 @@
 // Per-row absmax int8 activation quantiser (optionally preceded by the input RMSNorm), and the
 // 2-bit -> int8 weight expansion that feeds the tensor-core GEMM.  Both are pure HBM/L2
 // streaming kernels.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -290,6 +292,7 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
     if (threadIdx.x == 0) act_scales[row] = __fdiv_rn(denom, q_max);
 
     int local_sum = 0;
+    auto round_and_store = [&](auto away) {
 #pragma unroll
     for (int i = 0; i < G; ++i) {
         const int j = (threadIdx.x + i * blockDim.x) * 16;
@@ -297,10 +300,10 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
             uint32_t words[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int a = round_code(__fmul_rn(v[i][e].x, scale), tie_away);
-                const int b = round_code(__fmul_rn(v[i][e].y, scale), tie_away);
-                const int c = round_code(__fmul_rn(v[i][e].z, scale), tie_away);
-                const int d = round_code(__fmul_rn(v[i][e].w, scale), tie_away);
+                const int a = round_code(__fmul_rn(v[i][e].x, scale), decltype(away)::value);
+                const int b = round_code(__fmul_rn(v[i][e].y, scale), decltype(away)::value);
+                const int c = round_code(__fmul_rn(v[i][e].z, scale), decltype(away)::value);
+                const int d = round_code(__fmul_rn(v[i][e].w, scale), decltype(away)::value);
                 words[e] = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
                 local_sum = dp4a_ss(static_cast<int>(words[e]), 0x01010101, local_sum);   // the sum of the stored codes
             }
@@ -309,6 +312,9 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
             if (qp) *reinterpret_cast<uint4*>(qp + pbase + qp_offset(prow, prows, K, j)) = transpose4x4_bytes(natural);
         }
     }
+    };
+    // one uniform branch: the half-away path converts on the XU pipe
+    if (tie_away) round_and_store(std::true_type{}); else round_and_store(std::false_type{});
     if (q_sums) {
         local_sum = warp_sum_i(local_sum);
         if (lane == 0) sum_scratch[warp] = local_sum;
@@ -424,19 +430,24 @@ quantize_rows_stream_kernel(const float* __restrict__ x, const int32_t* __restri
         if (leader) act_scales[row] = __fdiv_rn(denom, q_max);
         uint32_t* dst = reinterpret_cast<uint32_t*>(q + static_cast<size_t>(row) * K);
         int local_sum = 0;
+        // one uniform branch per row: the half-away path converts on the XU pipe, which the compiler would
+        // otherwise execute for every element and select away
+        auto round_and_store = [&](auto away) {
 #pragma unroll
-        for (int e = 0; e < kStreamVec; ++e) {
-            const int i = tw * 32 * kStreamVec + e * 32 + lane;
-            if (i < nvec) {
-                const int a = round_code(__fmul_rn(v[e].x, scale), tie_away);
-                const int b = round_code(__fmul_rn(v[e].y, scale), tie_away);
-                const int c = round_code(__fmul_rn(v[e].z, scale), tie_away);
-                const int d = round_code(__fmul_rn(v[e].w, scale), tie_away);
-                const uint32_t w = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
-                dst[i] = w;
-                local_sum = dp4a_ss(static_cast<int>(w), 0x01010101, local_sum);
+            for (int e = 0; e < kStreamVec; ++e) {
+                const int i = tw * 32 * kStreamVec + e * 32 + lane;
+                if (i < nvec) {
+                    const int a = round_code(__fmul_rn(v[e].x, scale), decltype(away)::value);
+                    const int b = round_code(__fmul_rn(v[e].y, scale), decltype(away)::value);
+                    const int c = round_code(__fmul_rn(v[e].z, scale), decltype(away)::value);
+                    const int d = round_code(__fmul_rn(v[e].w, scale), decltype(away)::value);
+                    const uint32_t w = (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+                    dst[i] = w;
+                    local_sum = dp4a_ss(static_cast<int>(w), 0x01010101, local_sum);
+                }
             }
-        }
+        };
+        if (tie_away) round_and_store(std::true_type{}); else round_and_store(std::false_type{});
         if (q_sums) {
             local_sum = __reduce_add_sync(0xffffffffu, local_sum);
             if (lane == 0 && local_sum != 0) atomicAdd(&sum[slot], local_sum);
