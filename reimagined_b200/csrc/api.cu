@@ -367,6 +367,21 @@ int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const flo
     const Workspace w = carve(workspace_dev, 1, K);
     const int mode = views_host[0].rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
     const bool mma = all_have_strips(views_host, groups);
+    if (mma && mode != TBL_RMS_REFERENCE_ORDER && gemv_strip_fused_rows(K) >= 1) {
+        // one launch: the shared input row is quantised in the prologue of the grouped GEMV
+        StripProblem pr[TBL_MAX_GROUPS];
+        for (int g = 0; g < groups; ++g) {
+            pr[g] = StripProblem{};
+            pr[g].strips = static_cast<const uint8_t*>(views_host[g].strips);
+            pr[g].x = input_dev; pr[g].q_max = qmax_for_bits(views_host[0].activation_bits);
+            pr[g].rms_fast = mode == TBL_RMS_FAST;
+            pr[g].magnitude = views_host[g].magnitude; pr[g].bias = views_host[g].bias;
+            pr[g].y = output_dev + static_cast<size_t>(g) * output_stride;
+            pr[g].weight_scale = views_host[g].weight_scale; pr[g].rows = 1;
+            pr[g].N = views_host[g].outputs; pr[g].K = K; pr[g].ldy = views_host[g].outputs;
+        }
+        return cuda_status(launch_gemv_strip(pr, groups, st));
+    }
     cudaError_t e = launch_quantize_rows(input_dev, nullptr, 1, K, views_host[0].activation_bits, mode,
                                          TBL_TIE_EVEN, w.q, mma ? w.qp : nullptr, w.act_scales, w.q_sums,
                                          w.inv_norm, nullptr, QuantSegments{}, st);

@@ -679,10 +679,17 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     if (grid > kNumSm) grid = kNumSm;
     // spread small problems over more SMs (fewer strips per CTA)
     if (total < kNumSm * kStripSlots) grid = total < kNumSm ? total : kNumSm;
-    P.fused = count == 1 && problems[0].x != nullptr;
+    // fused quantiser: one problem, or several that share the input rows (grouped projections)
+    P.fused = problems[0].x != nullptr;
+    for (int i = 0; i < count; ++i) {
+        const bool same = problems[i].x == problems[0].x && problems[i].K == problems[0].K &&
+                          problems[i].rows == problems[0].rows && problems[i].rms_fast == problems[0].rms_fast &&
+                          problems[i].q_max == problems[0].q_max;
+        if ((P.fused || problems[i].x != nullptr) && !same) return cudaErrorInvalidValue;
+    }
     if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
         return cudaErrorInvalidValue;
-    const bool fast = nt == 1 && P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0;
+    const bool fast = nt == 1 && count == 1 && P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0;
     // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
     P.share_base = total / grid;
     P.share_rem = total % grid;

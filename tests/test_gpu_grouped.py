@@ -13,7 +13,8 @@ def bits_equal(a, b):
 
 
 @pytest.mark.parametrize("K,outs,strips", [(768, [1536, 1536, 16, 16, 24], True), (768, [768, 1536], False),
-                                           (48, [3, 17, 33], False), (1024, [40], True)])
+                                           (48, [3, 17, 33], False), (1024, [40], True),
+                                           (4096, [100, 16, 2064], True), (32768, [20, 33], True)])
 def test_grouped_projections_share_one_quantised_row(cuda, port, tbl, K, outs, strips):
     """Mamba x/z/B/C/dt or attention Q/KV: several ternary linears on the same input row, one call."""
     import gpu_helpers as H
@@ -33,7 +34,9 @@ def test_grouped_projections_share_one_quantised_row(cuda, port, tbl, K, outs, s
     before = tbl.tbl_launch_count()
     out = H.grouped_forward(views, H.dev(x), max(outs)).cpu().numpy()
     if strips:
-        assert tbl.tbl_launch_count() - before == 2  # one quantiser + one grouped GEMV launch
+        # one grouped GEMV launch with the quantiser in its prologue; a row too long for that (K > 16384)
+        # is quantised by a kernel of its own first
+        assert tbl.tbl_launch_count() - before == (1 if K <= 16384 else 2)
     for g, n in enumerate(outs):
         assert bits_equal(out[g, :n], want[g]), f"group {g}"
     assert H.device_status() == 0
