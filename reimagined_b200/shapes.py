@@ -18,7 +18,13 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true", help="launch from the stream instead of replaying a CUDA graph")
+    ap.add_argument("--moe", action="store_true",
+                    help="time tbl_moe_forward instead: --m tokens, --k model width, --n expert hidden width")
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=2)
     args = ap.parse_args()
+    if args.moe:
+        return moe(args)
 
     import torch
     from . import capi
@@ -86,6 +92,83 @@ def main() -> None:
     print(json.dumps({"m": m, "n": n, "k": k, "us_per_call": round(us, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
                       "tops": round(2.0 * m * n * k / us / 1e6, 1), "weight_buffers": buffers,
                       "graph": not args.no_graph, "device_status": status}))
+
+
+def moe(args) -> None:
+    """Expert FFN of a mixture-of-experts block: tokens x [m, k], E experts up k->n, squared ReLU, down n->k, top-k routing."""
+    import torch
+    from . import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the ternary linear path has no CPU fallback")
+    L = capi.lib()
+    torch.cuda.set_device(0)
+    rows, dim, hidden, E, topk = args.m, args.k, args.n, args.experts, args.topk
+    stream = torch.cuda.current_stream().cuda_stream
+    keep = []
+
+    def make_view(n: int, k: int) -> capi.LinearView:
+        words = torch.randint(0, 2 ** 31 - 1, (n * k // 16,), dtype=torch.int32, device="cuda") & 0x2AAAAAAA
+        strips = None
+        if k % 256 == 0:
+            strips = torch.empty(L.tbl_strip_bytes(n, k), dtype=torch.uint8, device="cuda")
+            capi.check(L.tbl_relayout_strips(words.data_ptr(), n, k, strips.data_ptr(), stream), "tbl_relayout_strips")
+        keep.extend([words, strips])
+        v = capi.LinearView()
+        v.weight, v.magnitude, v.bias = None, None, None
+        v.packed = words.data_ptr()
+        v.strips = None if strips is None else strips.data_ptr()
+        v.inputs, v.outputs, v.activation_bits, v.rms_input, v.weight_scale = k, n, 8, 1, 0.016
+        return v
+
+    views = [make_view(hidden, dim) for _ in range(E)] + [make_view(dim, hidden) for _ in range(E)]
+    arr = (capi.LinearView * (2 * E))(*views)
+    x = torch.randn((rows, dim), device="cuda")
+    # top-k routing weights: k distinct experts per token, weights summing to one
+    scores = torch.rand((rows, E), device="cuda")
+    top = scores.topk(topk, dim=1)
+    routing = torch.zeros((rows, E), device="cuda")
+    routing.scatter_(1, top.indices, top.values / top.values.sum(dim=1, keepdim=True))
+    out = torch.empty((rows, dim), device="cuda")
+    ws_bytes = L.tbl_moe_workspace_bytes(rows, dim, hidden, E, topk)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+
+    def call() -> None:
+        capi.check(L.tbl_moe_forward(arr, routing.data_ptr(), x.data_ptr(), rows, dim, hidden, E, topk, 1, 0,
+                                     out.data_ptr(), ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream),
+                   "tbl_moe_forward")
+
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    before = L.tbl_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.no_graph:
+        e0.record()
+        for _ in range(args.iters):
+            call()
+        e1.record()
+        launches = (L.tbl_launch_count() - before) // args.iters
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+        launches = L.tbl_launch_count() - before
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.iters):
+            graph.replay()
+        e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / args.iters
+    active = int((routing.sum(dim=0) > 0).sum().item())
+    packed_bytes = active * 2 * dim * hidden // 4
+    ops = 2.0 * rows * topk * 2 * dim * hidden
+    print(json.dumps({"moe": True, "tokens": rows, "dim": dim, "hidden": hidden, "experts": E, "topk": topk,
+                      "active_experts": active, "us_per_call": round(us, 1), "kernel_launches": int(launches),
+                      "packed_mb": round(packed_bytes / 1e6, 1), "packed_gb_per_s": round(packed_bytes / us / 1e3, 1),
+                      "tops": round(ops / us / 1e6, 1), "device_status": L.tbl_device_status(stream)}))
 
 
 if __name__ == "__main__":
