@@ -213,11 +213,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int n0 = tn * BN + c * 32;
                 tmem_ld_wait();
                 if (c + 2 < nblocks) tmem_ld32(t_row + (c + 2) * 32, rn);   // in flight while this block is stored
+                // float(acc) * (act_scale * weight_scale) [* magnitude[n]] [+ bias[n]], one rounding each.  The
+                // per-column factors are loaded once per block (lane i holds column n0 + i) and handed round
+                // with shuffles; columns past N are clipped by the store.  (An earlier form tested and
+                // loaded per element: 825 instructions per 32 x 32 block, and the epilogue, not the tensor
+                // pipe, set the pace of small-K shapes.)
                 float v[32];
+                if (!p.magnitude && !p.bias) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int n = n0 + i;
-                    v[i] = n < p.N ? epilogue(static_cast<int>(r[i]), comb, p.magnitude, p.bias, n) : 0.0f;
+                    for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(static_cast<float>(static_cast<int>(r[i])), comb);
+                } else {
+                    const int nl = n0 + lane;
+                    const float mag_l = p.magnitude && nl < p.N ? __ldg(p.magnitude + nl) : 1.0f;
+                    const float bias_l = p.bias && nl < p.N ? __ldg(p.bias + nl) : 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __fmul_rn(static_cast<float>(static_cast<int>(r[i])), comb);
+                        if (p.magnitude) x = __fmul_rn(x, __shfl_sync(0xffffffffu, mag_l, i));
+                        if (p.bias) x = __fadd_rn(x, __shfl_sync(0xffffffffu, bias_l, i));
+                        v[i] = x;
+                    }
                 }
                 if (p.acc_debug && m < p.M) {
                     for (int i = 0; i < 32; ++i)
