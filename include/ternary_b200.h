@@ -188,8 +188,9 @@ int tbl_linear_forward_noalloc(const float* x_dev, const uint32_t* words_dev, co
 /* ---- grouped variant ------------------------------------------------------------------- */
 
 /* Borrowed descriptor of one linear; the first nine fields are field-for-field the reference's
- * GpuLinearView (OXN/nsos/include/gpu_linear_view.h:8-26); `strips` is this library's addition
- * (strip-major copy of `packed`, or NULL).  Only the packed mode (packed != NULL, weight == NULL,
+ * GpuLinearView (OXN/nsos/include/gpu_linear_view.h:8-26); `strips` and `w_i8` are this library's
+ * additions (strip-major copy of `packed` from tbl_relayout_strips, int8 expansion from
+ * tbl_expand_weights_i8; either may be NULL).  Only the packed mode (packed != NULL, weight == NULL,
  * activation_bits in [2,8]) is implemented; others -> TBL_ERR_UNSUPPORTED. */
 typedef struct tbl_linear_view {
     const float* weight;
@@ -202,6 +203,7 @@ typedef struct tbl_linear_view {
     int rms_input;
     float weight_scale;
     const void* strips;
+    const int8_t* w_i8;
 } tbl_linear_view;
 
 #define TBL_MAX_GROUPS 32
@@ -226,6 +228,9 @@ size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, i
  * views_host holds 2*experts views: [0,E) the up linears (dim -> hidden_dim), [E,2E) the down
  * linears (hidden_dim -> dim).  routing_dev fp32 [rows,experts].  At most max_routes_per_row
  * non-zero routing weights per row (else the device status reports TBL_DEV_ROUTE_OVERFLOW).
+ * With >= 16 routed rows per expert on average and `w_i8` set in every view, both expert stages run as
+ * one grouped tensor-core GEMM each (row counts stay on the device); otherwise on the strip / canonical
+ * GEMV path.
  * Replaces: launch_moe_sparse_decode (OXN/nsos/src/cuda/moe_kernels.cu:786-795) and the CPU
  * composition in JambaBlock::forward_moe (OXN/nsos/src/jamba.cpp:3865-3972). */
 int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev, const float* x_dev,

@@ -27,7 +27,7 @@ class LinearView(C.Structure):
     _fields_ = [("weight", C.c_void_p), ("packed", C.c_void_p), ("magnitude", C.c_void_p),
                 ("bias", C.c_void_p), ("inputs", C.c_int), ("outputs", C.c_int),
                 ("activation_bits", C.c_int), ("rms_input", C.c_int), ("weight_scale", C.c_float),
-                ("strips", C.c_void_p)]
+                ("strips", C.c_void_p), ("w_i8", C.c_void_p)]
 
 
 _vp = C.c_void_p

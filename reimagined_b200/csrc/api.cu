@@ -102,7 +102,7 @@ const char* tbl_status_string(int status) {
     }
 }
 
-int tbl_abi_version(void) { return 1; }
+int tbl_abi_version(void) { return 2; }
 
 uint64_t tbl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -329,6 +329,28 @@ int run_expert_stage(const tbl_linear_view* views, int experts, const int8_t* q,
     return TBL_OK;
 }
 
+bool all_have_i8(const tbl_linear_view* views, int count) {
+    for (int i = 0; i < count; ++i)
+        if (!views[i].w_i8 || !aligned16(views[i].w_i8)) return false;
+    return views[0].inputs % 16 == 0;
+}
+
+// One expert stage as a grouped tensor-core GEMM on the int8 expansions.
+int run_expert_stage_gemm(const tbl_linear_view* views, int experts, const int8_t* q, const float* scales,
+                          const MoeLists& lists, int capacity, int rows_cap, float* y, int squared_relu,
+                          cudaStream_t st) {
+    const int8_t* w[TBL_MAX_GROUPS];
+    float ws[TBL_MAX_GROUPS];
+    const float* mag[TBL_MAX_GROUPS];
+    const float* bias[TBL_MAX_GROUPS];
+    for (int e = 0; e < experts; ++e) {
+        w[e] = views[e].w_i8; ws[e] = views[e].weight_scale; mag[e] = views[e].magnitude; bias[e] = views[e].bias;
+    }
+    return cuda_status(launch_gemm_tcgen05_grouped(q, scales, w, ws, mag, bias, lists.counts, lists.offsets, experts,
+                                                   rows_cap, capacity, views[0].inputs, views[0].outputs, y,
+                                                   squared_relu, st));
+}
+
 bool all_have_strips(const tbl_linear_view* views, int count) {
     for (int i = 0; i < count; ++i)
         if (!views[i].strips || !aligned16(views[i].strips)) return false;
@@ -450,9 +472,24 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
     cudaError_t e = launch_moe_route(routing_dev, rows, experts, capacity, w.lists, status, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
     // expert inputs: gather routed rows, [RMSNorm], quantise once per slot
+    const QuantSegments seg{w.lists.offsets, w.lists.counts, experts};
+    // enough rows per expert for 128-row tensor-core tiles, and the int8 expansions at hand: grouped GEMMs
+    if (capacity >= 16 * experts && all_have_i8(views_host, 2 * experts)) {
+        e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, w.q1, nullptr, w.scales1,
+                                 nullptr, w.inv1, w.lists.total, QuantSegments{}, st);
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+        int rcg = run_expert_stage_gemm(views_host, experts, w.q1, w.scales1, w.lists, capacity, rows, w.hidden, 1, st);
+        if (rcg != TBL_OK) return rcg;
+        e = launch_quantize_rows(w.hidden, nullptr, capacity, hidden_dim, bits, mode, tie_mode, w.q2, nullptr,
+                                 w.scales2, nullptr, w.inv2, w.lists.total, QuantSegments{}, st);
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+        rcg = run_expert_stage_gemm(views_host + experts, experts, w.q2, w.scales2, w.lists, capacity, rows, w.contrib,
+                                    0, st);
+        if (rcg != TBL_OK) return rcg;
+        return cuda_status(launch_moe_merge(routing_dev, w.contrib, w.lists.slot_of, rows, experts, dim, out_dev, st));
+    }
     const bool mma1 = all_have_strips(views_host, experts);
     const bool mma2 = all_have_strips(views_host + experts, experts);
-    const QuantSegments seg{w.lists.offsets, w.lists.counts, experts};
     e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, mma1 ? nullptr : w.q1,
                              mma1 ? w.q1 : nullptr, w.scales1, w.sums1, w.inv1, w.lists.total, seg, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;

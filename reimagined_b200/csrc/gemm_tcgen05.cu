@@ -15,6 +15,8 @@
 // the common exit, where TMEM is released.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -40,6 +42,48 @@ struct GemmParams {
     int use_tma_store;
     int* status;
 };
+
+// Grouped mode (mixture-of-experts stages): problem g multiplies rows [offset[g], offset[g] + rows[g]) of the
+// shared activation / output arrays by its own weight matrix.  Row counts and offsets live on the device
+// (they come from the routing kernel), so every role of the kernel derives the tile list from them itself.
+struct GroupTable {
+    CUtensorMap b[TBL_MAX_GROUPS];
+    float weight_scale[TBL_MAX_GROUPS];
+    const float* magnitude[TBL_MAX_GROUPS];
+    const float* bias[TBL_MAX_GROUPS];
+    const int* rows_dev;
+    const int* offset_dev;
+    int groups;
+    int cap;              // host-side upper bound on the rows of any problem
+    int squared_relu;
+};
+struct NoGroups {};
+
+// Tile t of the launch -> (problem, first row in the shared arrays, rows left in the problem, n-tile).
+template <bool GROUPED, typename Table>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const Table& gt, int t, int& g, int& row0, int& rows,
+                                            int& tn) {
+    if constexpr (!GROUPED) {
+        if (t >= p.tiles_m * p.tiles_n) return false;
+        const int tm = t % p.tiles_m;
+        g = 0; tn = t / p.tiles_m; row0 = tm * 128; rows = p.M - row0;
+        return true;
+    } else {
+        int base = 0;
+        for (int e = 0; e < gt.groups; ++e) {
+            const int r = min(__ldg(gt.rows_dev + e), gt.cap);
+            const int tiles_m = (r + 127) >> 7;
+            const int tiles = tiles_m * p.tiles_n;
+            if (t < base + tiles) {
+                const int local = t - base, tm = local % tiles_m;
+                g = e; tn = local / tiles_m; row0 = __ldg(gt.offset_dev + e) + tm * 128; rows = r - tm * 128;
+                return true;
+            }
+            base += tiles;
+        }
+        return false;
+    }
+}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile(
@@ -96,10 +140,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
-template <int BN>
+template <int BN, bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_y, const GemmParams p,
+                    const __grid_constant__ std::conditional_t<GROUPED, GroupTable, NoGroups> gt) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -114,7 +159,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;
     const int kblocks = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -138,8 +182,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             int it = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int g, row0, rows, tn;
+            for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn); tile += gridDim.x) {
+                const CUtensorMap* bmap = &map_b;
+                if constexpr (GROUPED) bmap = &gt.b[g];
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages) {
@@ -149,8 +195,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t* a_dst = smem + s * kStageBytes;
                     uint8_t* b_dst = a_dst + kABytes;
                     mbar_arrive_expect_tx(&full[s], kStageBytes);
-                    tma_load_2d(a_dst, &map_a, kb * BK, tm * BM, &full[s]);
-                    tma_load_2d(b_dst, &map_b, kb * BK, tn * BN, &full[s]);
+                    // (grouped: rows past the problem's last belong to the next problem or lie past the
+                    // array, where the copy fills zeros; their accumulator rows are never stored)
+                    tma_load_2d(a_dst, &map_a, kb * BK, row0, &full[s]);
+                    tma_load_2d(b_dst, bmap, kb * BK, tn * BN, &full[s]);
                 }
             }
         }
@@ -162,7 +210,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                    (static_cast<uint32_t>(BM >> 4) << 24);
             int it = 0, local = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
+            int g, row0, rows, tn;
+            for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn);
+                 tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 if (local >= 2) {
                     alive = mbar_wait_bounded(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status);
@@ -194,15 +244,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint8_t* stage = epi_stage + (warp - 2) * 4096;
         int local = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++local) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int g, row0, rows, tn;
+        for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn);
+             tile += gridDim.x, ++local) {
             const int buf = local & 1;
             alive = mbar_wait_bounded(&tmem_full[buf], (local >> 1) & 1, p.status);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
-            const int m = tm * BM + quarter * 32 + lane;
-            const float comb = m < p.M ? __fmul_rn(__ldg(p.act_scales + m), p.weight_scale) : 0.0f;
+            const int m = row0 + quarter * 32 + lane;            // row in the activation / output arrays
+            const bool row_ok = quarter * 32 + lane < rows;
+            float wscale = p.weight_scale;
+            const float* magnitude = p.magnitude;
+            const float* bias = p.bias;
+            if constexpr (GROUPED) { wscale = gt.weight_scale[g]; magnitude = gt.magnitude[g]; bias = gt.bias[g]; }
+            const float comb = row_ok ? __fmul_rn(__ldg(p.act_scales + m), wscale) : 0.0f;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             // blocks of 32 columns this warp owns inside the tile, clipped at N
             const int nblocks = min(BN / 32, (p.N - tn * BN + 31) / 32);
@@ -219,26 +275,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // loaded per element: 825 instructions per 32 x 32 block, and the epilogue, not the tensor
                 // pipe, set the pace of small-K shapes.)
                 float v[32];
-                if (!p.magnitude && !p.bias) {
+                if (!magnitude && !bias) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(static_cast<float>(static_cast<int>(r[i])), comb);
                 } else {
                     const int nl = n0 + lane;
-                    const float mag_l = p.magnitude && nl < p.N ? __ldg(p.magnitude + nl) : 1.0f;
-                    const float bias_l = p.bias && nl < p.N ? __ldg(p.bias + nl) : 0.0f;
+                    const float mag_l = magnitude && nl < p.N ? __ldg(magnitude + nl) : 1.0f;
+                    const float bias_l = bias && nl < p.N ? __ldg(bias + nl) : 0.0f;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         float x = __fmul_rn(static_cast<float>(static_cast<int>(r[i])), comb);
-                        if (p.magnitude) x = __fmul_rn(x, __shfl_sync(0xffffffffu, mag_l, i));
-                        if (p.bias) x = __fadd_rn(x, __shfl_sync(0xffffffffu, bias_l, i));
+                        if (magnitude) x = __fmul_rn(x, __shfl_sync(0xffffffffu, mag_l, i));
+                        if (bias) x = __fadd_rn(x, __shfl_sync(0xffffffffu, bias_l, i));
                         v[i] = x;
                     }
                 }
-                if (p.acc_debug && m < p.M) {
+                if constexpr (GROUPED) {
+                    if (gt.squared_relu) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) { const float x = fmaxf(v[i], 0.0f); v[i] = __fmul_rn(x, x); }
+                    }
+                }
+                if (p.acc_debug && row_ok) {
                     for (int i = 0; i < 32; ++i)
                         if (n0 + i < p.N) p.acc_debug[static_cast<size_t>(m) * p.N + n0 + i] = static_cast<int>(r[i]);
                 }
-                if (p.use_tma_store) {
+                if constexpr (GROUPED) {
+                    // rows of other problems follow this one's in y: no clipped box store here.  Stage the
+                    // block (row = lane, same swizzle as below), then one coalesced 128-byte store per row.
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = f;
+                    }
+                    __syncwarp();
+                    const int valid = min(32, rows - quarter * 32);
+                    const int col = n0 + lane;
+                    for (int rr = 0; rr < valid; ++rr) {
+                        const float x = *reinterpret_cast<const float*>(stage + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                                        ((lane & 3) << 2));
+                        if (col < p.N) p.y[static_cast<size_t>(row0 + quarter * 32 + rr) * p.N + col] = x;
+                    }
+                } else if (p.use_tma_store) {
                     // the previous block's store must have finished reading the staging buffer
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     __syncwarp();
@@ -251,10 +330,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&map_y, n0, tm * BM + quarter * 32, stage);
+                        tma_store_2d(&map_y, n0, row0 + quarter * 32, stage);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                } else if (m < p.M) {
+                } else if (row_ok) {
                     for (int i = 0; i < 32; ++i)
                         if (n0 + i < p.N) p.y[static_cast<size_t>(m) * p.N + n0 + i] = v[i];
                 }
@@ -311,7 +390,7 @@ bool make_map(CUtensorMap* map, CUtensorMapDataType type, int elem, const void* 
 template <int BN>
 cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const GemmParams& p,
                       cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN>;
+    auto kernel = gemm_tcgen05_kernel<BN, false>;
     const size_t smem = 1024 + kStages * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
     static bool configured[64] = {};
     int dev = 0;
@@ -323,12 +402,60 @@ cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < kNumSm ? tiles : kNumSm;
-    kernel<<<grid, kThreads, smem, stream>>>(ma, mb, my, p);
+    kernel<<<grid, kThreads, smem, stream>>>(ma, mb, my, p, NoGroups{});
+    note_launch();
+    return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t launch_grouped_bn(const CUtensorMap& ma, const GemmParams& p, const GroupTable& gt, int grid,
+                              cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<BN, true>;
+    const size_t smem = 1024 + kStages * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, kThreads, smem, stream>>>(ma, ma, ma, p, gt);
     note_launch();
     return cudaGetLastError();
 }
 
 }  // namespace
+
+// Grouped prefill GEMM: problem g = rows [offset_dev[g], offset_dev[g] + rows_dev[g]) of q / act_scales / y
+// against w_i8[g]; `total_rows` is the extent of those arrays, `cap` an upper bound on any rows_dev[g].
+cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales, const int8_t* const* w_i8,
+                                        const float* weight_scales, const float* const* magnitudes,
+                                        const float* const* biases, const int* rows_dev, const int* offset_dev,
+                                        int groups, int cap, int total_rows, int K, int N, float* y,
+                                        int squared_relu, cudaStream_t stream) {
+    if (groups < 1 || groups > TBL_MAX_GROUPS) return cudaErrorInvalidValue;
+    GemmParams p{};
+    p.act_scales = act_scales; p.y = y; p.K = K; p.N = N; p.M = total_rows;
+    p.status = device_status_ptr();
+    if (!p.status) return cudaErrorUnknown;
+    const int bn = N > 128 ? 256 : 128;
+    p.tiles_n = (N + bn - 1) / bn;
+    GroupTable gt{};
+    gt.groups = groups; gt.cap = cap; gt.squared_relu = squared_relu; gt.rows_dev = rows_dev; gt.offset_dev = offset_dev;
+    CUtensorMap ma;
+    if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, total_rows, K, BK, BM)) return cudaErrorUnknown;
+    for (int g = 0; g < groups; ++g) {
+        if (!make_map(&gt.b[g], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_i8[g], N, K, BK, bn)) return cudaErrorUnknown;
+        gt.weight_scale[g] = weight_scales[g];
+        gt.magnitude[g] = magnitudes[g];
+        gt.bias[g] = biases[g];
+    }
+    // tiles: at most ceil(total/128) + groups row tiles (one ragged tile per problem) times the n-tiles
+    const long long tiles = (static_cast<long long>((total_rows + BM - 1) / BM) + groups) * p.tiles_n;
+    const int grid = tiles < kNumSm ? static_cast<int>(tiles) : kNumSm;
+    return bn == 256 ? launch_grouped_bn<256>(ma, p, gt, grid, stream) : launch_grouped_bn<128>(ma, p, gt, grid, stream);
+}
 
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8, float weight_scale,
                                 const float* magnitude, const float* bias, int M, int K, int N, float* y,

@@ -107,6 +107,11 @@ cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t*
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8,
                                 float weight_scale, const float* magnitude, const float* bias,
                                 int M, int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream);
+cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales, const int8_t* const* w_i8,
+                                        const float* weight_scales, const float* const* magnitudes,
+                                        const float* const* biases, const int* rows_dev, const int* offset_dev,
+                                        int groups, int cap, int total_rows, int K, int N, float* y,
+                                        int squared_relu, cudaStream_t stream);
 
 // moe.cu — routing lists and the final merge.
 struct MoeLists {

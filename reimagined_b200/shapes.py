@@ -22,6 +22,7 @@ def main() -> None:
                     help="time tbl_moe_forward instead: --m tokens, --k model width, --n expert hidden width")
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--no-i8", action="store_true", help="MoE: views without the int8 expansion (strip GEMV path)")
     args = ap.parse_args()
     if args.moe:
         return moe(args)
@@ -113,11 +114,14 @@ def moe(args) -> None:
         if k % 256 == 0:
             strips = torch.empty(L.tbl_strip_bytes(n, k), dtype=torch.uint8, device="cuda")
             capi.check(L.tbl_relayout_strips(words.data_ptr(), n, k, strips.data_ptr(), stream), "tbl_relayout_strips")
-        keep.extend([words, strips])
+        w8 = torch.empty((n, k), dtype=torch.int8, device="cuda")      # for the grouped tensor-core GEMM
+        capi.check(L.tbl_expand_weights_i8(words.data_ptr(), n, k, w8.data_ptr(), stream), "tbl_expand_weights_i8")
+        keep.extend([words, strips, w8])
         v = capi.LinearView()
         v.weight, v.magnitude, v.bias = None, None, None
         v.packed = words.data_ptr()
         v.strips = None if strips is None else strips.data_ptr()
+        v.w_i8 = None if args.no_i8 else w8.data_ptr()
         v.inputs, v.outputs, v.activation_bits, v.rms_input, v.weight_scale = k, n, 8, 1, 0.016
         return v
 

@@ -96,9 +96,9 @@ def linear_forward(x, words, weight_scale, N, w_i8=None, bits=8, rms_mode=0, mag
 
 
 def make_view(words_t, inputs, outputs, weight_scale, bits=8, rms_input=0, magnitude=None, bias=None,
-              strips=None):
+              strips=None, w_i8=None):
     return capi.LinearView(None, ptr(words_t), ptr(magnitude) or None, ptr(bias) or None, inputs, outputs, bits,
-                           rms_input, float(weight_scale), ptr(strips) or None)
+                           rms_input, float(weight_scale), ptr(strips) or None, ptr(w_i8) or None)
 
 
 def grouped_forward(views, x_row, output_stride, rms_mode=0):

@@ -42,7 +42,7 @@ def test_grouped_projections_share_one_quantised_row(cuda, port, tbl, K, outs, s
     assert H.device_status() == 0
 
 
-def _moe_setup(port, H, x, up, down, strips):
+def _moe_setup(port, H, x, up, down, strips, i8=False):
     E, Hd, D = up.shape
     views_up, views_down, keep, packed = [], [], [], []
     for e in range(E):
@@ -51,9 +51,11 @@ def _moe_setup(port, H, x, up, down, strips):
         du, dd = H.words_dev(wu), H.words_dev(wd)
         su_t = H.relayout_strips(du, Hd, D) if strips else None
         sd_t = H.relayout_strips(dd, D, Hd) if strips else None
-        keep += [du, dd, su_t, sd_t]
-        views_up.append(H.make_view(du, D, Hd, su, rms_input=1, strips=su_t))
-        views_down.append(H.make_view(dd, Hd, D, sd, rms_input=1, strips=sd_t))
+        iu = H.expand_i8(du, Hd, D) if i8 else None
+        idn = H.expand_i8(dd, D, Hd) if i8 else None
+        keep += [du, dd, su_t, sd_t, iu, idn]
+        views_up.append(H.make_view(du, D, Hd, su, rms_input=1, strips=su_t, w_i8=iu))
+        views_down.append(H.make_view(dd, Hd, D, sd, rms_input=1, strips=sd_t, w_i8=idn))
         packed.append((wu, su, wd, sd))
     return views_up + views_down, keep, packed
 
@@ -89,6 +91,29 @@ def test_moe_matches_oracle(cuda, port, tbl, rows, D, Hd, E, top_k):
     assert bits_equal(out, want), f"max diff {np.abs(out - want).max()}"
     fast = H.moe_forward(views, H.dev(routing), H.dev(x), Hd, top_k, rms_mode=1).cpu().numpy()
     assert np.abs(fast - want).max() <= 3e-2 * np.abs(want).max()
+    assert H.device_status() == 0
+
+
+@pytest.mark.parametrize("rows,D,Hd,E,top_k", [(130, 256, 256, 3, 1), (300, 512, 768, 4, 2), (257, 272, 144, 5, 3),
+                                               (64, 64, 128, 4, 2)])
+def test_moe_grouped_tensor_core_gemm_matches_oracle(cuda, port, tbl, rows, D, Hd, E, top_k):
+    """Views that carry the int8 expansion and >= 16 routed rows per expert: both expert stages run as one
+    grouped tcgen05 GEMM each (device-side row counts, ragged last tiles, experts with few or no rows)."""
+    import gpu_helpers as H
+    rng = np.random.default_rng(rows * 13 + D)
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    up = (rng.standard_normal((E, Hd, D)) * 0.02).astype(np.float32)
+    down = (rng.standard_normal((E, D, Hd)) * 0.02).astype(np.float32)
+    logits = rng.standard_normal((rows, E)).astype(np.float32)
+    logits[:, E - 1] -= 4.0                      # the last expert gets (almost) no rows
+    routing = port.router_topk(logits, top_k)
+    views, keep, packed = _moe_setup(port, H, x, up, down, False, i8=True)
+    want = port.moe_forward(x, routing, [p[0] for p in packed], [p[1] for p in packed], [p[2] for p in packed],
+                            [p[3] for p in packed], Hd, rms_input=1)
+    before = tbl.tbl_launch_count()
+    out = H.moe_forward(views, H.dev(routing), H.dev(x), Hd, top_k, rms_mode=2).cpu().numpy()
+    assert tbl.tbl_launch_count() - before == 8      # route, 2 x (rms, quantise, grouped GEMM), merge
+    assert bits_equal(out, want), f"max diff {np.abs(out - want).max()}"
     assert H.device_status() == 0
 
 
