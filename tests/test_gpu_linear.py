@@ -297,3 +297,38 @@ def test_roundtrip_properties_at_scale(cuda, port, tbl):
     bias = np.random.default_rng(1).standard_normal(N).astype(np.float32)
     y0 = H.linear_forward(H.dev(np.zeros((2, K), np.float32)), dw, scale, N, bias=H.dev(bias)).cpu().numpy()
     assert bits_equal(y0, np.broadcast_to(bias, (2, N)))
+
+
+@pytest.mark.parametrize("M", [1, 8, 200])
+def test_checksums_at_full_size_16384(cuda, port, tbl, M):
+    """K = N = 16384 (the bench's size; 64 MiB of packed weights, codes drawn on the device): the layer's
+    outputs through the fused decode kernel (M = 1), the strip GEMV behind a separate quantiser (M = 8)
+    and the tcgen05 GEMM (M = 200) agree with (i) the oracle on 48 sampled weight rows, bit for bit, and
+    (ii) the checksum identity sum_n acc[m,n] = q[m,:] . sum_n t[n,:] over all 16384 columns."""
+    import gpu_helpers as H
+    import torch
+    N = K = 16384
+    gen = torch.Generator(device="cuda").manual_seed(16384 + M)
+    codes = torch.randint(0, 3, (N, K), dtype=torch.int32, device="cuda", generator=gen)     # 0, 1, 2
+    shifts = (2 * torch.arange(16, device="cuda", dtype=torch.int32)).view(1, 1, 16)
+    words = (codes.view(N, K // 16, 16) << shifts).sum(dim=2, dtype=torch.int32).contiguous().view(-1)
+    scale = 0.0159
+    x = (np.random.default_rng(M).standard_normal((M, K)) * 1.7).astype(np.float32)
+    oq, osc = port.quantize_rows(x)
+    strips = H.relayout_strips(words, N, K)
+    w_i8 = H.expand_i8(words, N, K) if M > 64 else None
+    y = H.linear_forward(H.dev(x), words, scale, N, strips=strips, w_i8=w_i8).cpu().numpy()
+    # (i) sampled rows against the integer oracle and the reference's epilogue
+    rows = np.random.default_rng(7).choice(N, 48, replace=False)
+    t_rows = (codes[torch.from_numpy(rows).cuda()].cpu().numpy().astype(np.int32) - 1)
+    acc = oq.astype(np.int32) @ t_rows.T
+    want = acc.astype(np.float32) * (osc[:, None] * np.float32(scale)).astype(np.float32)
+    assert bits_equal(y[:, rows], want)
+    # (ii) checksum over every column, from the raw accumulators of the GEMV / GEMM entry points
+    col = (codes.to(torch.int64) - 1).sum(dim=0).cpu().numpy()
+    if M <= 64:
+        _, acc_all = H.gemv(H.dev(oq), H.dev(osc), None, scale, N, strips=strips)
+    else:
+        _, acc_all = H.gemm(H.dev(oq), H.dev(osc), w_i8, scale)
+    assert np.array_equal(acc_all.cpu().numpy().astype(np.int64).sum(axis=1), oq.astype(np.int64) @ col)
+    assert H.device_status() == 0
