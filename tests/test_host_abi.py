@@ -126,3 +126,17 @@ def test_header_is_plain_c_and_links(tbl, tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, f"abi_check exited {out.returncode}: {out.stdout} {out.stderr}"
     assert "abi ok" in out.stdout
+
+
+def test_cpp_shim_maps_status_codes_to_the_reference_exceptions(tbl, tmp_path):
+    """The header-only C++ shim compiles as C++17, links, and throws the reference's exception types."""
+    import subprocess
+    from reimagined_b200 import capi
+    exe = tmp_path / "shim_check"
+    lib_dir = os.path.dirname(capi.LIB_PATH)
+    subprocess.run(["/usr/bin/g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "shim_check.cpp"), "-o", str(exe),
+                    "-L", lib_dir, "-lternary_b200", "-Wl,-rpath," + lib_dir], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, f"shim_check exited {out.returncode}: {out.stdout} {out.stderr}"
+    assert "shim ok" in out.stdout
