@@ -220,6 +220,17 @@ int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const flo
                         float* output_dev, int output_stride, int rms_mode,
                         void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* tbl_grouped_forward for `rows` <= 64 input rows (batched decode: B sequences go through the same
+ * projections).  input_dev is fp32 [rows, inputs]; view g writes a contiguous [rows, outputs_g] block at
+ * output_dev + g*output_stride (output_stride in floats, >= rows*outputs_g).  One launch when
+ * rows*inputs <= 16384 (the rows are quantised in the prologue of the grouped GEMV), else two.
+ * No counterpart in the reference: its grouped launch takes a single row
+ * (OXN/nsos/src/gpu_projection_group.cpp:12-47) and batches fall back to one BitLinear call per projection. */
+size_t tbl_grouped_rows_workspace_bytes(int groups, int rows, int max_inputs);
+int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, const float* input_dev, int rows,
+                             float* output_dev, long long output_stride, int rms_mode, void* workspace_dev,
+                             size_t workspace_bytes, void* stream);
+
 /* Bytes of scratch for tbl_moe_forward. */
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row);
 

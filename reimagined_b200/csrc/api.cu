@@ -366,69 +366,80 @@ size_t tbl_grouped_workspace_bytes(int groups, int max_inputs) {
     return carve(nullptr, 1, max_inputs).bytes;
 }
 
-int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const float* input_dev,
-                        float* output_dev, int output_stride, int rms_mode, void* workspace_dev,
-                        size_t workspace_bytes, void* stream) {
-    if (!views_host || !input_dev || !output_dev || groups <= 0 || groups > TBL_MAX_GROUPS ||
+size_t tbl_grouped_rows_workspace_bytes(int groups, int rows, int max_inputs) {
+    if (groups <= 0 || rows <= 0 || max_inputs <= 0) return 0;
+    return carve(nullptr, rows, max_inputs).bytes;
+}
+
+int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, const float* input_dev, int rows,
+                             float* output_dev, long long output_stride, int rms_mode, void* workspace_dev,
+                             size_t workspace_bytes, void* stream) {
+    if (!views_host || !input_dev || !output_dev || groups <= 0 || groups > TBL_MAX_GROUPS || rows <= 0 ||
         output_stride <= 0)
         return TBL_ERR_INVALID_ARG;
+    if (rows > 64) return TBL_ERR_SHAPE;      // one activation tile; larger batches go through tbl_linear_forward
     if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
     const int K = views_host[0].inputs;
     for (int g = 0; g < groups; ++g) {
         const int rc = check_view(views_host[g]);
         if (rc != TBL_OK) return rc;
-        // one shared input row is quantised once, so the views must agree on how
+        // the shared input rows are quantised once, so the views must agree on how
         if (views_host[g].inputs != K || views_host[g].activation_bits != views_host[0].activation_bits ||
             (views_host[g].rms_input != 0) != (views_host[0].rms_input != 0))
             return TBL_ERR_UNSUPPORTED;
-        if (views_host[g].outputs > output_stride) return TBL_ERR_SHAPE;
+        if (static_cast<long long>(views_host[g].outputs) * rows > output_stride) return TBL_ERR_SHAPE;
     }
-    if (!workspace_dev || workspace_bytes < tbl_grouped_workspace_bytes(groups, K)) return TBL_ERR_WORKSPACE;
+    if (!workspace_dev || workspace_bytes < tbl_grouped_rows_workspace_bytes(groups, rows, K)) return TBL_ERR_WORKSPACE;
     if (!aligned16(workspace_dev) || !aligned16(input_dev)) return TBL_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const Workspace w = carve(workspace_dev, 1, K);
+    const Workspace w = carve(workspace_dev, rows, K);
     const int mode = views_host[0].rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
     const bool mma = all_have_strips(views_host, groups);
-    if (mma && mode != TBL_RMS_REFERENCE_ORDER && gemv_strip_fused_rows(K) >= 1) {
-        // one launch: the shared input row is quantised in the prologue of the grouped GEMV
+    auto fill = [&](StripProblem& pr, int g) {
+        pr = StripProblem{};
+        pr.strips = static_cast<const uint8_t*>(views_host[g].strips);
+        pr.magnitude = views_host[g].magnitude; pr.bias = views_host[g].bias;
+        pr.y = output_dev + static_cast<size_t>(g) * output_stride;
+        pr.weight_scale = views_host[g].weight_scale; pr.rows = rows;
+        pr.N = views_host[g].outputs; pr.K = K; pr.ldy = views_host[g].outputs;
+    };
+    if (mma && mode != TBL_RMS_REFERENCE_ORDER && rows <= gemv_strip_fused_rows(K)) {
+        // one launch: the shared input rows are quantised in the prologue of the grouped GEMV
         StripProblem pr[TBL_MAX_GROUPS];
         for (int g = 0; g < groups; ++g) {
-            pr[g] = StripProblem{};
-            pr[g].strips = static_cast<const uint8_t*>(views_host[g].strips);
+            fill(pr[g], g);
             pr[g].x = input_dev; pr[g].q_max = qmax_for_bits(views_host[0].activation_bits);
             pr[g].rms_fast = mode == TBL_RMS_FAST;
-            pr[g].magnitude = views_host[g].magnitude; pr[g].bias = views_host[g].bias;
-            pr[g].y = output_dev + static_cast<size_t>(g) * output_stride;
-            pr[g].weight_scale = views_host[g].weight_scale; pr[g].rows = 1;
-            pr[g].N = views_host[g].outputs; pr[g].K = K; pr[g].ldy = views_host[g].outputs;
         }
         return cuda_status(launch_gemv_strip(pr, groups, st));
     }
-    cudaError_t e = launch_quantize_rows(input_dev, nullptr, 1, K, views_host[0].activation_bits, mode,
-                                         TBL_TIE_EVEN, w.q, mma ? w.qp : nullptr, w.act_scales, w.q_sums,
-                                         w.inv_norm, nullptr, QuantSegments{}, st);
+    cudaError_t e = launch_quantize_rows(input_dev, nullptr, rows, K, views_host[0].activation_bits, mode,
+                                         TBL_TIE_EVEN, mma ? nullptr : w.q, mma ? w.qp : nullptr, w.act_scales,
+                                         w.q_sums, w.inv_norm, nullptr, QuantSegments{}, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;
     if (mma) {
         StripProblem pr[TBL_MAX_GROUPS];
         for (int g = 0; g < groups; ++g) {
-            pr[g] = StripProblem{};
-            pr[g].strips = static_cast<const uint8_t*>(views_host[g].strips); pr[g].qp = w.qp;
-            pr[g].act_scales = w.act_scales;
-            pr[g].q_sums = w.q_sums; pr[g].magnitude = views_host[g].magnitude; pr[g].bias = views_host[g].bias;
-            pr[g].y = output_dev + static_cast<size_t>(g) * output_stride;
-            pr[g].weight_scale = views_host[g].weight_scale; pr[g].rows = 1;
-            pr[g].N = views_host[g].outputs; pr[g].K = K; pr[g].ldy = views_host[g].outputs;
+            fill(pr[g], g);
+            pr[g].qp = w.qp; pr[g].act_scales = w.act_scales; pr[g].q_sums = w.q_sums;
         }
         return cuda_status(launch_gemv_strip(pr, groups, st));
     }
     for (int g = 0; g < groups; ++g) {
         e = launch_gemv_generic(w.q, w.act_scales, views_host[g].packed, views_host[g].weight_scale,
-                                views_host[g].magnitude, views_host[g].bias, 1, K, views_host[g].outputs,
+                                views_host[g].magnitude, views_host[g].bias, rows, K, views_host[g].outputs,
                                 output_dev + static_cast<size_t>(g) * output_stride, nullptr, 0, nullptr,
                                 nullptr, st);
         if (e != cudaSuccess) return TBL_ERR_CUDA;
     }
     return TBL_OK;
+}
+
+int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const float* input_dev,
+                        float* output_dev, int output_stride, int rms_mode, void* workspace_dev,
+                        size_t workspace_bytes, void* stream) {
+    return tbl_grouped_forward_rows(views_host, groups, input_dev, 1, output_dev, output_stride, rms_mode,
+                                    workspace_dev, workspace_bytes, stream);
 }
 
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row) {

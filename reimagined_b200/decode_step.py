@@ -7,7 +7,7 @@ out 768->768 and an FFN 768->3072->768 with squared ReLU; LM head 768->32000): 9
 24.0 MB packed.  Only the linears run -- the state-space scan, attention over the KV cache, norms and gates
 between them are not part of this library -- so the figure is the linear path's share of a token, an upper
 bound on tokens/s, with real data dependencies (every linear consumes an earlier linear's output).
-At batch 1 the projections that share an input go through `tbl_grouped_forward` (one launch for five).
+Projections that share an input go through `tbl_grouped_forward_rows` (one launch for five up to batch 8).
 Weights are synthetic (random codes).  Prints one JSON line.
 """
 from __future__ import annotations
@@ -71,7 +71,7 @@ def main() -> None:
         blocks.append(blk)
     head = make_linear(VOCAB, D)
 
-    ws_bytes = max(L.tbl_linear_workspace_bytes(B, FFN, VOCAB), L.tbl_grouped_workspace_bytes(5, D))
+    ws_bytes = max(L.tbl_linear_workspace_bytes(B, FFN, VOCAB), L.tbl_grouped_rows_workspace_bytes(5, min(B, 64), D))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
     hidden = [torch.randn((B, D), device="cuda"), torch.empty((B, D), device="cuda")]
     # slot i of a group buffer receives linear i's [B, n] output, contiguous with row pitch n
@@ -86,12 +86,12 @@ def main() -> None:
                                         torch.cuda.current_stream().cuda_stream), "tbl_linear_forward")
 
     def group(lins, x, out) -> None:
-        """Several linears on the same input: one grouped launch at batch 1, else one call each."""
-        if B == 1:
+        """Several linears on the same input rows: one grouped call (up to 64 rows), else one call each."""
+        if B <= 64:
             arr = (capi.LinearView * len(lins))(*[view(l) for l in lins])
-            capi.check(L.tbl_grouped_forward(arr, len(lins), x.data_ptr(), out.data_ptr(), out.shape[1], 0,
-                                             ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream),
-                       "tbl_grouped_forward")
+            capi.check(L.tbl_grouped_forward_rows(arr, len(lins), x.data_ptr(), B, out.data_ptr(), out.shape[1], 0,
+                                                  ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream),
+                       "tbl_grouped_forward_rows")
         else:
             for i, l in enumerate(lins):
                 linear(l, x.data_ptr(), out[i].data_ptr())

@@ -113,6 +113,21 @@ def grouped_forward(views, x_row, output_stride, rms_mode=0):
     return out
 
 
+def grouped_forward_rows(views, x, rms_mode=0):
+    """x [rows, K] -> list of [rows, outputs_g] tensors."""
+    L = capi.lib()
+    G = len(views)
+    rows = x.shape[0]
+    arr = (capi.LinearView * G)(*views)
+    stride = rows * max(v.outputs for v in views)
+    out = torch.zeros((G, stride), dtype=torch.float32, device="cuda")
+    nbytes = L.tbl_grouped_rows_workspace_bytes(G, rows, views[0].inputs)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    capi.check(L.tbl_grouped_forward_rows(arr, G, ptr(x), rows, ptr(out), stride, rms_mode, ptr(ws), nbytes,
+                                          stream_ptr()), "tbl_grouped_forward_rows")
+    return [out[g, : rows * views[g].outputs].view(rows, views[g].outputs) for g in range(G)]
+
+
 def moe_forward(views, routing, x, hidden_dim, max_routes, rms_mode=2, tie_mode=0):
     L = capi.lib()
     rows, dim = x.shape

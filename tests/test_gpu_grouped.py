@@ -42,6 +42,35 @@ def test_grouped_projections_share_one_quantised_row(cuda, port, tbl, K, outs, s
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("rows,K,outs,strips", [(8, 768, [1536, 1536, 16, 16, 24], True), (3, 4096, [100, 2064], True),
+                                                (16, 768, [768, 1536], True), (64, 1024, [40, 17], True),
+                                                (5, 48, [3, 33], False), (2, 32768, [20], True)])
+def test_grouped_projections_on_a_batch_of_rows(cuda, port, tbl, rows, K, outs, strips):
+    """Batched decode: the same projections on several rows, one grouped call (fused quantiser when
+    rows*K <= 16384, separate quantiser kernel above that, canonical-words fallback without strips)."""
+    import gpu_helpers as H
+    rng = np.random.default_rng(rows + K + len(outs))
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    views, keep, want = [], [], []
+    for n in outs:
+        w = (rng.standard_normal((n, K)) * 0.02).astype(np.float32)
+        words, scale, *_ = port.pack_weights(w)
+        mag = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        bias = rng.standard_normal(n).astype(np.float32)
+        dw, dm, db = H.words_dev(words), H.dev(mag), H.dev(bias)
+        ds = H.relayout_strips(dw, n, K) if strips else None
+        keep += [dw, dm, db, ds]
+        views.append(H.make_view(dw, K, n, scale, magnitude=dm, bias=db, strips=ds))
+        want.append(port.linear_forward(x, words, scale, n, magnitude=mag, bias=bias)[0])
+    before = tbl.tbl_launch_count()
+    got = H.grouped_forward_rows(views, H.dev(x))
+    if strips:
+        assert tbl.tbl_launch_count() - before == (1 if rows * K <= 16384 and rows <= 8 else 2)
+    for g in range(len(outs)):
+        assert bits_equal(got[g].cpu().numpy(), want[g]), f"group {g}"
+    assert H.device_status() == 0
+
+
 def _moe_setup(port, H, x, up, down, strips, i8=False):
     E, Hd, D = up.shape
     views_up, views_down, keep, packed = [], [], [], []
