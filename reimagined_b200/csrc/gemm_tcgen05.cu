@@ -2,13 +2,18 @@
 // tensor cores.  tcgen05.mma kind::i8 (s8 x s8 -> s32), both operands K-major in shared memory in
 // the 128-byte-swizzled canonical layout written by TMA, accumulators in tensor memory (TMEM).
 //
-// One persistent CTA per SM, six warps:
+// One persistent CTA per SM, ten warps:
 //   warp 0    TMA producer: per k-block one box of q [128 rows x 128 B] and one of w [BN x 128 B]
 //   warp 1    MMA issuer (one lane): 4 x tcgen05.mma (K = 32 each) per k-block, tcgen05.commit
 //             releases the stage; also owns the TMEM allocation (512 columns = 2 accumulators)
 //   warps 2-9 epilogue: tcgen05.ld the 128 x BN s32 tile (a TMEM lane quarter per warp pair), apply
 //             float(acc) * (act_scale*weight_scale) [* magnitude] [+ bias], stage 32x32 fp32 blocks
 //             in swizzled shared memory and write them with TMA stores (clipped at the edges)
+// Grouped mode (GROUPED = true) runs a table of problems in one launch -- the expert stages of a
+// mixture-of-experts block: problem g owns rows [offset[g], offset[g] + rows[g]) of the shared activation
+// and output arrays and its own weight matrix (one tensor map each); the counts live on the device, so
+// every role walks the same tile list derived from them, and the epilogue masks rows past a problem's
+// end and stores rows with plain coalesced stores instead of box stores.
 // The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1; the next
 // block's tcgen05.ld is issued before the current block is converted and stored.
 // Every wait is bounded: on a timeout the role records the status word and falls through to

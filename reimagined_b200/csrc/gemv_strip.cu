@@ -8,8 +8,9 @@
 // (rows g / g+8) with no bank conflicts.  Blocks are ordered slab-major: a slab is 4 consecutive
 // k-blocks (1024 weights of K) of EVERY strip, [slab][strip][block in slab].  CTAs own runs of
 // adjacent strips and walk the slabs in step, so at any moment the whole GPU is reading one
-// contiguous window of memory (DRAM pages are swept once, front to back) and a CTA's stage is a
-// single contiguous bulk copy (strips x 4 KB) plus the matching slab of activations.
+// contiguous window of memory (DRAM pages are swept once, front to back) and a CTA's stage is one
+// contiguous bulk copy per slab (strips x 4 KB; two slabs per stage for M <= 16) plus, unless the
+// quantiser ran in the prologue and left the activations resident, the matching slab of activations.
 //
 // Widening: for 2-bit position j, (word & (0x03030303 << 2j)) is the unsigned byte vector
 // 4^j * code of weights {j,4+j,8+j,12+j} of that word.  With one accumulator set per j the four
