@@ -376,7 +376,10 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "kernel": "gemv_strip_kernel<1,true,2,true> (quantiser fused, single-row path)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "kernel_us": kernel_ms * 1e3,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     # supplementary: the same bytes over the two-requests-in-flight region, where the head of
+                     # one chain's kernel overlaps the tail of the other's (throughput, not a kernel duration)
+                     "two_requests_in_flight": {"achieved": value / world, "frac": value / world / peak}},
         "device_status": status,
     }
     if rank == 0 and world == 1:

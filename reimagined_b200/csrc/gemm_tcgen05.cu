@@ -30,7 +30,10 @@ namespace {
 
 constexpr int BM = 128;          // activation rows per tile (UMMA M)
 constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
-constexpr int kStages = 4;
+// ring depth: what fits beside the 32 KB of epilogue staging (narrow tiles get a deeper ring: with few
+// rows the kernel streams weights and wants more bytes in flight per SM)
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8); }
+constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;        // two warps per TMEM lane quarter, each taking every other 32-column block
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kNumSm = 148;
@@ -153,13 +156,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kStages = stages_for(BN);
     constexpr int kABytes = BM * BK;
     constexpr int kBBytes = BN * BK;
     constexpr int kStageBytes = kABytes + kBBytes;
     uint8_t* epi_stage = smem + kStages * kStageBytes;                 // 8 warps x 4 KB
     uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + kEpiWarps * 4096);
-    uint64_t* empty = full + kStages;
-    uint64_t* tmem_full = empty + kStages;
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tmem_full = empty + kMaxStages;
     uint64_t* tmem_empty = tmem_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
@@ -396,7 +400,7 @@ template <int BN>
 cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const GemmParams& p,
                       cudaStream_t stream) {
     auto kernel = gemm_tcgen05_kernel<BN, false>;
-    const size_t smem = 1024 + kStages * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
+    const size_t smem = 1024 + stages_for(BN) * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -416,7 +420,7 @@ template <int BN>
 cudaError_t launch_grouped_bn(const CUtensorMap& ma, const GemmParams& p, const GroupTable& gt, int grid,
                               cudaStream_t stream) {
     auto kernel = gemm_tcgen05_kernel<BN, true>;
-    const size_t smem = 1024 + kStages * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
+    const size_t smem = 1024 + stages_for(BN) * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -478,6 +482,8 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
         const double e256 = static_cast<double>(t256) / (((t256 + kNumSm - 1) / kNumSm) * kNumSm);
         const double e128 = static_cast<double>(t128) / (((t128 + kNumSm - 1) / kNumSm) * kNumSm);
         if (e128 > 1.15 * e256) bn = 128;
+        // few rows: the launch streams the weights once and wants every SM pulling -- narrower tiles
+        if (bn == 128 && t128 < 100 && N > 64) bn = 64;
     }
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
@@ -491,7 +497,8 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
     } else {
         my = ma;  // unused
     }
-    return bn == 256 ? launch_bn<256>(ma, mb, my, p, stream) : launch_bn<128>(ma, mb, my, p, stream);
+    return bn == 256 ? launch_bn<256>(ma, mb, my, p, stream)
+                     : (bn == 128 ? launch_bn<128>(ma, mb, my, p, stream) : launch_bn<64>(ma, mb, my, p, stream));
 }
 
 }  // namespace tbl
