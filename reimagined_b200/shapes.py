@@ -18,6 +18,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true", help="launch from the stream instead of replaying a CUDA graph")
+    ap.add_argument("--canonical", action="store_true",
+                    help="give the call only the canonical 2-bit words (no strip copy, no int8 expansion)")
     ap.add_argument("--moe", action="store_true",
                     help="time tbl_moe_forward instead: --m tokens, --k model width, --n expert hidden width")
     ap.add_argument("--experts", type=int, default=8)
@@ -39,12 +41,14 @@ def main() -> None:
         raise SystemExit("K must be a multiple of 16")
     stream = torch.cuda.current_stream().cuda_stream
     packed = n * k // 4
-    buffers = max(2, min(24, int(400e6 // (packed * (1 if m <= 64 else 4)))))
+    buffers = max(2, min(24, int(400e6 // (packed * (1 if m <= 64 or args.canonical else 4)))))
     weights = []
     for b in range(buffers):
         # random codes in {0, 1, 2} (two bits each, never 3)
         words = torch.randint(0, 2 ** 31 - 1, (n * k // 16,), dtype=torch.int32, device="cuda") & 0x2AAAAAAA
-        if m <= 64 and k % 256 == 0:
+        if args.canonical:
+            weights.append((words, None, None))
+        elif m <= 64 and k % 256 == 0:
             dev = torch.empty(L.tbl_strip_bytes(n, k), dtype=torch.uint8, device="cuda")
             capi.check(L.tbl_relayout_strips(words.data_ptr(), n, k, dev.data_ptr(), stream), "tbl_relayout_strips")
             weights.append((None, dev, None))
@@ -88,7 +92,7 @@ def main() -> None:
         e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1000.0 / args.iters
-    algorithmic = packed * (1 if m <= 64 else 4) + 4 * m * k + 4 * m * n + 4 * (1 + m)
+    algorithmic = packed * (1 if m <= 64 or args.canonical else 4) + 4 * m * k + 4 * m * n + 4 * (1 + m)
     status = L.tbl_device_status(stream)
     print(json.dumps({"m": m, "n": n, "k": k, "us_per_call": round(us, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
                       "tops": round(2.0 * m * n * k / us / 1e6, 1), "weight_buffers": buffers,
