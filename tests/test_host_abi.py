@@ -140,3 +140,10 @@ def test_cpp_shim_maps_status_codes_to_the_reference_exceptions(tbl, tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, f"shim_check exited {out.returncode}: {out.stdout} {out.stderr}"
     assert "shim ok" in out.stdout
+
+
+def test_graft_entry_build_runs(tbl):
+    """The build hook (extension + oracle checkers) completes and imports the package on a machine without a GPU."""
+    import importlib
+    entry = importlib.import_module("__graft_entry__")
+    entry.build()
