@@ -40,6 +40,8 @@ extern "C" {
 #define TBL_ERR_CODE (-8)          /* packed words contain the illegal code 0b11          */
 #define TBL_ERR_CUDA (-9)          /* a CUDA runtime call or launch failed                */
 #define TBL_ERR_UNSUPPORTED (-10)  /* descriptor mode this library does not implement     */
+#define TBL_ERR_FORMAT (-11)       /* edge pack: bad magic/version, truncated, bad flag, non-finite value */
+#define TBL_ERR_INTEGRITY (-12)    /* edge pack: trailer missing or SHA-256 mismatch      */
 
 const char* tbl_status_string(int status);
 
@@ -248,6 +250,47 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
                     int rows, int dim, int hidden_dim, int experts, int max_routes_per_row,
                     int rms_mode, int tie_mode, float* out_dev,
                     void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* ---- edge-linear pack ("DGE1") ---------------------------------------------------------- */
+
+/* The file in which the reference ships a model's packed linears (JambaModel::save_edge_linear_pack /
+ * load_edge_linear_pack, OXN/nsos/src/jamba.cpp:1325-1663; helpers :505-606; format in csrc/edge_pack.cpp).
+ * Host only, over a memory image of the file.  Payload offsets are in bytes from the start of the image and
+ * are NOT aligned (copy out with memcpy). */
+typedef struct tbl_edge_layer {
+    int sensitive, in_features, out_features, use_bias;
+    float weight_scale;
+    uint64_t packed_offset, packed_words;        /* canonical 2-bit words, ceil(in*out/16)          */
+    uint64_t magnitude_offset;                   /* fp32 [out]                                       */
+    uint64_t bias_offset;                        /* fp32 [out] when use_bias                         */
+    uint64_t flat_alpha_offset, flat_beta_offset;/* fp32 [in] each                                   */
+    uint64_t weight_offset, weight_count;        /* fp32 [out*in] of a sensitive layer, else 0       */
+} tbl_edge_layer;
+
+typedef struct tbl_edge_layer_src {
+    int sensitive, in_features, out_features, use_bias;
+    float weight_scale;
+    const uint32_t* packed;
+    const float* magnitude;
+    const float* bias;
+    const float* flat_alpha;
+    const float* flat_beta;
+    const float* weight;                         /* sensitive layers only */
+} tbl_edge_layer_src;
+
+/* Validates the whole image (header, every layer's lengths / finite values / scale / codes, nothing after the
+ * last layer, version-3 trailer length and SHA-256) and reports version (2 or 3) and layer count.
+ * Replaces: the parsing and validation half of load_edge_linear_pack (jamba.cpp:1451-1616). */
+int tbl_edge_pack_open(const void* data, size_t bytes, int* version_out, int* layers_out);
+/* Layer `index` of a pack (validated up to and including that layer). */
+int tbl_edge_pack_layer(const void* data, size_t bytes, int index, tbl_edge_layer* out);
+/* Size of, and writer for, a version-3 pack.  Replaces: save_edge_linear_pack's serialisation
+ * (jamba.cpp:1345-1439); the caller does the atomic temp-file replace. */
+size_t tbl_edge_pack_bytes(const tbl_edge_layer_src* layers, int count);
+int tbl_edge_pack_write(const tbl_edge_layer_src* layers, int count, void* out, size_t capacity, size_t* written);
+/* Lower-case hex SHA-256 of a buffer (the trailer's digest; integrity::sha256_hex,
+ * OXN/nsos/include/nsos/sha256.h:12). */
+void tbl_sha256_hex(const void* data, size_t bytes, char out[65]);
 
 /* ---- device status ---------------------------------------------------------------------- */
 #define TBL_DEV_OK 0

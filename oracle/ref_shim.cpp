@@ -8,6 +8,7 @@
 // computes, and so the bench can time the reference's CPU path.
 #include "bitlinear.h"
 #include "bitnet_adapter.h"
+#include "nsos/sha256.h"
 
 #include <algorithm>
 #include <cstdint>
@@ -181,6 +182,13 @@ int ref_moe_forward(const float* x, int rows, int D, int H, int E, const float* 
     } catch (...) {
         return -1;
     }
+}
+
+// The reference's own SHA-256 (integrity::sha256_hex, include/nsos/sha256.h:12): pins the digest of the
+// edge-pack trailer.  out must hold 65 bytes.
+void ref_sha256_hex(const void* data, size_t size, char* out) {
+    const std::string hex = nsos::integrity::sha256_hex(data, size);
+    std::memcpy(out, hex.c_str(), hex.size() + 1);
 }
 
 }  // extern "C"

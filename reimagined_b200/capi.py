@@ -30,6 +30,23 @@ class LinearView(C.Structure):
                 ("strips", C.c_void_p), ("w_i8", C.c_void_p)]
 
 
+class EdgeLayer(C.Structure):
+    """tbl_edge_layer: one layer record of an edge-linear pack (byte offsets into the image)."""
+
+    _fields_ = [("sensitive", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int), ("use_bias", C.c_int),
+                ("weight_scale", C.c_float), ("packed_offset", C.c_uint64), ("packed_words", C.c_uint64),
+                ("magnitude_offset", C.c_uint64), ("bias_offset", C.c_uint64), ("flat_alpha_offset", C.c_uint64),
+                ("flat_beta_offset", C.c_uint64), ("weight_offset", C.c_uint64), ("weight_count", C.c_uint64)]
+
+
+class EdgeLayerSrc(C.Structure):
+    """tbl_edge_layer_src: one layer handed to the pack writer."""
+
+    _fields_ = [("sensitive", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int), ("use_bias", C.c_int),
+                ("weight_scale", C.c_float), ("packed", C.c_void_p), ("magnitude", C.c_void_p), ("bias", C.c_void_p),
+                ("flat_alpha", C.c_void_p), ("flat_beta", C.c_void_p), ("weight", C.c_void_p)]
+
+
 _vp = C.c_void_p
 _SIGNATURES = {
     # name: (restype, argtypes)
@@ -61,6 +78,11 @@ _SIGNATURES = {
     "tbl_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tbl_moe_forward": (C.c_int, [C.POINTER(LinearView), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_size_t, _vp]),
+    "tbl_edge_pack_open": (C.c_int, [_vp, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tbl_edge_pack_layer": (C.c_int, [_vp, C.c_size_t, C.c_int, C.POINTER(EdgeLayer)]),
+    "tbl_edge_pack_bytes": (C.c_size_t, [C.POINTER(EdgeLayerSrc), C.c_int]),
+    "tbl_edge_pack_write": (C.c_int, [C.POINTER(EdgeLayerSrc), C.c_int, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "tbl_sha256_hex": (None, [_vp, C.c_size_t, C.c_char_p]),
     "tbl_device_status": (C.c_int, [_vp]),
     "tbl_set_kernel_events": (None, [_vp, _vp]),
     "tbl_launch_count": (C.c_uint64, []),

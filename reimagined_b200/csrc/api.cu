@@ -95,6 +95,8 @@ const char* tbl_status_string(int status) {
         case TBL_ERR_BITS: return "activation bits must be in [2,8]";
         case TBL_ERR_ALIGNMENT: return "device pointer must be 16-byte aligned";
         case TBL_ERR_WORKSPACE: return "workspace too small";
+        case TBL_ERR_FORMAT: return "edge pack malformed";
+        case TBL_ERR_INTEGRITY: return "edge pack integrity trailer missing or digest mismatch";
         case TBL_ERR_CODE: return "packed words contain the reserved code 0b11";
         case TBL_ERR_CUDA: return "CUDA runtime error";
         case TBL_ERR_UNSUPPORTED: return "descriptor mode not implemented";
