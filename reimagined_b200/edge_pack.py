@@ -107,3 +107,18 @@ def sha256_hex(data: bytes) -> str:
     out = C.create_string_buffer(65)
     capi.lib().tbl_sha256_hex(data, len(data), out)
     return out.value.decode()
+
+
+def to_bitlinear(layer: Dict):
+    """A non-sensitive pack layer as a `BitLinear` (import_packed_state re-validates before installing).
+    Sensitive layers stay on the reference's fp32 path and have no ternary linear to build."""
+    from .bitlinear import BitLinear, BitLinearPackedState
+
+    if layer["sensitive"]:
+        raise ValueError("a quantisation-sensitive layer runs in fp32 in the reference; it has no packed linear")
+    lin = BitLinear(layer["in_features"], layer["out_features"], bias=layer["use_bias"])
+    lin.import_packed_state(BitLinearPackedState(
+        in_features=layer["in_features"], out_features=layer["out_features"], use_bias=layer["use_bias"],
+        weight_scale=float(layer["weight_scale"]), packed_weights=layer["packed_weights"],
+        magnitude=layer["magnitude"], bias=layer["bias"]))
+    return lin

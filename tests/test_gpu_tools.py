@@ -29,3 +29,32 @@ def test_decode_step_tool(cuda, tbl):
     d = _run(["reimagined_b200.decode_step", "--batch", "2", "--iters", "2"])
     assert d["device_status"] == 0 and d["linears"] == 107 and d["ternary_weights"] == 96043008
     assert d["kernel_launches_per_step"] <= 43
+
+
+def test_layers_loaded_from_an_edge_pack_run_bit_exact(cuda, port, tbl, tmp_path):
+    """Pack file -> BitLinear mirror -> device -> forward, against the oracle on the packed state."""
+    import numpy as np
+    import torch
+    from reimagined_b200 import edge_pack
+    rng = np.random.default_rng(11)
+    layers = []
+    for (n, k, bias) in [(96, 768, True), (40, 256, False)]:
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        words, scale, *_ = port.pack_weights(w)
+        layers.append({"sensitive": False, "in_features": k, "out_features": n, "use_bias": bias,
+                       "weight_scale": np.float32(scale), "packed_weights": np.asarray(words, np.uint32),
+                       "magnitude": (1 + 0.1 * rng.standard_normal(n)).astype(np.float32),
+                       "bias": rng.standard_normal(n).astype(np.float32) if bias else np.zeros(0, np.float32),
+                       "flat_alpha": np.ones(k, np.float32), "flat_beta": np.zeros(k, np.float32), "weight": None})
+    path = tmp_path / "model.edge"
+    edge_pack.save(str(path), layers)
+    for layer in edge_pack.load(str(path)):
+        lin = edge_pack.to_bitlinear(layer).to("cuda")
+        lin.rms_mode = 2          # reference-order RMSNorm: bit-identical to the CPU path
+        for m in (1, 5, 70):
+            x = rng.standard_normal((m, layer["in_features"])).astype(np.float32)
+            want = port.linear_forward(x, layer["packed_weights"], layer["weight_scale"], layer["out_features"],
+                                       rms_input=1, magnitude=layer["magnitude"],
+                                       bias=layer["bias"] if layer["use_bias"] else None)[0]
+            got = lin.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (layer["out_features"], m)
