@@ -233,6 +233,15 @@ int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, cons
                              float* output_dev, long long output_stride, int rms_mode, void* workspace_dev,
                              size_t workspace_bytes, void* stream);
 
+/* Router post-processing on the device: logits fp32 [rows, experts] (the gate's output) -> routing weights
+ * [rows, experts] as tbl_moe_forward takes them: softmax, keep the top_k largest per row (ties -> lower
+ * index), renormalise, zero the rest; top_k == 0 or >= experts leaves the softmax.  May run in place.
+ * Sums follow the reference's order; exp is the device's expf, so weights agree with the CPU path to a few
+ * ulp, not bit for bit.  Replaces: Tensor::softmax + moe_topk_mask_kernel / the CPU partial_sort in
+ * MoERouter::forward (OXN/nsos/src/tensor.cpp:3402-3450, src/cuda/moe_kernels.cu:32-91,
+ * src/jamba.cpp:8268-8296). */
+int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, float* weights_dev, void* stream);
+
 /* Bytes of scratch for tbl_moe_forward. */
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row);
 

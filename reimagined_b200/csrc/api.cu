@@ -444,6 +444,13 @@ int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const flo
                                     workspace_dev, workspace_bytes, stream);
 }
 
+int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, float* weights_dev, void* stream) {
+    if (!logits_dev || !weights_dev || rows <= 0 || experts <= 0 || experts > TBL_MAX_GROUPS || top_k < 0)
+        return TBL_ERR_INVALID_ARG;
+    return cuda_status(launch_router_topk(logits_dev, rows, experts, top_k, weights_dev,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row) {
     if (rows <= 0 || dim <= 0 || hidden_dim <= 0 || experts <= 0 || max_routes_per_row <= 0) return 0;
     if (max_routes_per_row > experts) max_routes_per_row = experts;

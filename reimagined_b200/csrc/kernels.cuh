@@ -123,6 +123,8 @@ struct MoeLists {
 };
 cudaError_t launch_moe_route(const float* routing, int rows, int experts, int capacity, MoeLists lists,
                              int* status, cudaStream_t stream);
+cudaError_t launch_router_topk(const float* logits, int rows, int experts, int top_k, float* weights,
+                               cudaStream_t stream);
 cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,
                              int experts, int dim, float* out, cudaStream_t stream);
 

@@ -79,6 +79,39 @@ moe_merge_kernel(const float* __restrict__ routing, const float* __restrict__ co
     out[static_cast<size_t>(r) * dim + n] = sum;
 }
 
+
+// Router post-processing, one thread per token: softmax over the experts' logits (max-subtracted,
+// 1/max(sum, 1e-8)), keep the top_k largest (ties -> lower index), renormalise by 1/max(sum_selected, 1e-9),
+// zero the rest.  Sums run in the reference's order (expert index, then rank).
+__global__ void router_topk_kernel(const float* __restrict__ logits, int rows, int experts, int top_k,
+                                   float* __restrict__ weights) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const float* l = logits + static_cast<size_t>(r) * experts;
+    float* w = weights + static_cast<size_t>(r) * experts;
+    float p[TBL_MAX_GROUPS];
+    float mx = l[0];
+    for (int e = 1; e < experts; ++e) mx = l[e] > mx ? l[e] : mx;
+    float sum = 0.0f;
+    for (int e = 0; e < experts; ++e) { p[e] = expf(__fsub_rn(l[e], mx)); sum = __fadd_rn(sum, p[e]); }
+    const float inv = __fdiv_rn(1.0f, sum > 1e-8f ? sum : 1e-8f);
+    for (int e = 0; e < experts; ++e) p[e] = __fmul_rn(p[e], inv);
+    if (top_k > 0 && top_k < experts) {
+        unsigned keep = 0u;
+        float selected = 0.0f;
+        for (int rank = 0; rank < top_k; ++rank) {
+            int best = -1;
+            for (int e = 0; e < experts; ++e)
+                if (!((keep >> e) & 1u) && (best < 0 || p[e] > p[best])) best = e;
+            keep |= 1u << best;
+            selected = __fadd_rn(selected, p[best]);
+        }
+        const float inv_sel = __fdiv_rn(1.0f, selected > 1e-9f ? selected : 1e-9f);
+        for (int e = 0; e < experts; ++e) p[e] = ((keep >> e) & 1u) ? __fmul_rn(p[e], inv_sel) : 0.0f;
+    }
+    for (int e = 0; e < experts; ++e) w[e] = p[e];
+}
+
 }  // namespace
 
 cudaError_t launch_moe_route(const float* routing, int rows, int experts, int capacity, MoeLists lists,
@@ -92,6 +125,14 @@ cudaError_t launch_moe_merge(const float* routing, const float* contrib, const i
                              int experts, int dim, float* out, cudaStream_t stream) {
     const dim3 grid((dim + 255) / 256, rows);
     moe_merge_kernel<<<grid, 256, 0, stream>>>(routing, contrib, slot_of, experts, dim, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_topk(const float* logits, int rows, int experts, int top_k, float* weights,
+                               cudaStream_t stream) {
+    if (experts < 1 || experts > TBL_MAX_GROUPS) return cudaErrorInvalidValue;
+    router_topk_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(logits, rows, experts, top_k, weights);
     note_launch();
     return cudaGetLastError();
 }

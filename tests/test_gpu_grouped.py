@@ -182,3 +182,30 @@ def test_moe_route_overflow_is_reported(cuda, port, tbl):
     H.moe_forward(views, H.dev(routing), H.dev(x), Hd, 2, rms_mode=1)
     assert H.device_status() == 2   # TBL_DEV_ROUTE_OVERFLOW, and the status word is cleared by the read
     assert H.device_status() == 0
+
+
+@pytest.mark.parametrize("rows,E,top_k", [(256, 8, 2), (5, 4, 1), (33, 32, 4), (7, 3, 3), (9, 6, 0)])
+def test_router_topk_on_device(cuda, port, tbl, rows, E, top_k):
+    """softmax -> top-k mask -> renormalise: same experts kept as the CPU path (ties -> lower index), weights
+    within 1e-6 relative (the device's expf is not the host's), rows sum to one; then the routed MoE on those
+    weights runs without a host round trip."""
+    import gpu_helpers as H
+    import torch
+    rng = np.random.default_rng(rows + E)
+    logits = rng.standard_normal((rows, E)).astype(np.float32) * 2
+    logits[0, :] = 0.25                      # a full tie: the lowest indices win
+    if E > 2:
+        logits[1, 1] = logits[1, 2] = logits[1].max() + 1.0
+    want = port.router_topk(logits, top_k)
+    d_logits = H.dev(logits)
+    out = torch.empty_like(d_logits)
+    from reimagined_b200 import capi
+    capi.check(tbl.tbl_router_topk(H.ptr(d_logits), rows, E, top_k, H.ptr(out), H.stream_ptr()), "tbl_router_topk")
+    got = out.cpu().numpy()
+    assert np.array_equal(got != 0, want != 0)
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-9)
+    np.testing.assert_allclose(got.sum(axis=1), 1.0, rtol=1e-6)
+    # in place
+    capi.check(tbl.tbl_router_topk(H.ptr(d_logits), rows, E, top_k, H.ptr(d_logits), H.stream_ptr()), "tbl_router_topk")
+    assert np.array_equal(d_logits.cpu().numpy(), got)
+    assert H.device_status() == 0
