@@ -128,14 +128,36 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
                 inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), 1e-6f)));
             }
             const bool normed = a.rms_mode != TBL_RMS_NONE;
+            // Rows of up to 16 * 4 * nthreads elements stay in registers between the absmax pass and the
+            // rounding pass (one trip through L2 instead of two); longer rows are read again.
+            constexpr int kCached = 4;                         // 16-element groups per thread
+            const bool cached = K <= 16 * kCached * nthreads;
+            float4 xc[kCached][4];
             float mx = 0.0f;
-            for (int j = threadIdx.x * 4; j < K; j += nthreads * 4) {
-                float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
-                if (normed) {
-                    v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
-                    v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < kCached; ++i) {
+                    const int j = (threadIdx.x + i * nthreads) * 16;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float4 v = j < K ? __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (normed) {
+                            v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                            v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                        }
+                        xc[i][e] = v;
+                        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                    }
                 }
-                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            } else {
+                for (int j = threadIdx.x * 4; j < K; j += nthreads * 4) {
+                    float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
+                    if (normed) {
+                        v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                        v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                    }
+                    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
             }
             mx = blk_max(mx, red, warps);
             const float denom = __fadd_rn(mx, 1e-8f);
@@ -145,28 +167,45 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
                 s_scale[m] = as;
                 if (a.scales_out && blockIdx.x == 0) a.scales_out[m] = as;
             }
-            for (int j = threadIdx.x * 16; j < K; j += nthreads * 16) {
+            // codes: ties-to-even on the FMA pipe (round_code), their sum from the stored bytes
+            auto emit_group = [&](int j, const float4 (&g)[4]) {
                 uint32_t wds[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float4 v = __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e));
-                    if (normed) {
-                        v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
-                        v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
-                    }
-                    const int q0 = static_cast<int>(rintf(__fmul_rn(v.x, scale)));
-                    const int q1 = static_cast<int>(rintf(__fmul_rn(v.y, scale)));
-                    const int q2 = static_cast<int>(rintf(__fmul_rn(v.z, scale)));
-                    const int q3 = static_cast<int>(rintf(__fmul_rn(v.w, scale)));
-                    local_sum += q0 + q1 + q2 + q3;
+                    const int q0 = round_code(__fmul_rn(g[e].x, scale), false);
+                    const int q1 = round_code(__fmul_rn(g[e].y, scale), false);
+                    const int q2 = round_code(__fmul_rn(g[e].z, scale), false);
+                    const int q3 = round_code(__fmul_rn(g[e].w, scale), false);
                     wds[e] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) |
                              (static_cast<uint32_t>(q3 & 0xff) << 24);
+                    local_sum = dp4a_ss(static_cast<int>(wds[e]), 0x01010101, local_sum);
                 }
                 const uint4 natural = make_uint4(wds[0], wds[1], wds[2], wds[3]);
                 if (a.q_out && blockIdx.x == 0)
                     *reinterpret_cast<uint4*>(a.q_out + static_cast<size_t>(m) * K + j) = natural;
                 *reinterpret_cast<uint4*>(act + act_offset(m, (j >> 4) & 3, j >> 6, K, C)) =
                     transpose4x4_bytes(natural);
+            };
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < kCached; ++i) {
+                    const int j = (threadIdx.x + i * nthreads) * 16;
+                    if (j < K) emit_group(j, xc[i]);
+                }
+            } else {
+                for (int j = threadIdx.x * 16; j < K; j += nthreads * 16) {
+                    float4 g[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float4 v = __ldg(reinterpret_cast<const float4*>(xr + j + 4 * e));
+                        if (normed) {
+                            v.x = __fmul_rn(v.x, inv); v.y = __fmul_rn(v.y, inv);
+                            v.z = __fmul_rn(v.z, inv); v.w = __fmul_rn(v.w, inv);
+                        }
+                        g[e] = v;
+                    }
+                    emit_group(j, g);
+                }
             }
         } else {
             const int8_t* qr = a.q + static_cast<size_t>(m) * K;
