@@ -90,11 +90,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
     const int row_bytes = K >> 2;
     const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(a.words);
 
-    // ---- start streaming weights before touching the activations ---------------------------
+    // ---- the weight rings start as early as possible, but behind the first row's activation loads: issued
+    // the other way round, those loads queue behind a ring's worth of weight copies in the memory pipeline
     if (lane == 0) {
         for (int s = 0; s < p.stages; ++s) mbar_init(&my_bars[s], 1);
         fence_mbar_init();
         fence_proxy_async();
+    }
+    bool ring_started = false;
+    auto start_ring = [&]() {
+        if (ring_started) return;
+        ring_started = true;
+        if (lane != 0) return;
         for (int s = 0; s < p.stages; ++s) {
             const int u = gw + s * wstride;
             if (u < p.units) {
@@ -106,7 +113,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
                          &my_bars[s]);
             }
         }
-    }
+    };
     if (threadIdx.x < M) s_qsum[threadIdx.x] = 0;
     __syncthreads();
 
@@ -119,6 +126,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
             const float* xr = a.x + static_cast<size_t>(m) * K;
             float inv = 1.0f;
             if (a.rms_mode == TBL_RMS_FAST) {
+                start_ring();
                 float ss = 0.0f;
                 for (int j = threadIdx.x * 4; j < K; j += nthreads * 4) {
                     const float4 v = __ldg(reinterpret_cast<const float4*>(xr + j));
@@ -134,6 +142,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
             const bool cached = K <= 16 * kCached * nthreads;
             float4 xc[kCached][4];
             float mx = 0.0f;
+            if (!cached || a.rms_mode == TBL_RMS_FAST) start_ring();
             if (cached) {
 #pragma unroll
                 for (int i = 0; i < kCached; ++i) {
@@ -159,6 +168,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
                     mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
             }
+            start_ring();        // this row's loads are in flight (the block reduction below waits for them)
             mx = blk_max(mx, red, warps);
             const float denom = __fadd_rn(mx, 1e-8f);
             const float scale = __fdiv_rn(a.q_max, denom);
@@ -208,6 +218,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const KP
                 }
             }
         } else {
+            start_ring();
             const int8_t* qr = a.q + static_cast<size_t>(m) * K;
             if (threadIdx.x == 0) s_scale[m] = a.act_scales[m];
             for (int j = threadIdx.x * 16; j < K; j += nthreads * 16) {
