@@ -147,3 +147,22 @@ def test_graft_entry_build_runs(tbl):
     import importlib
     entry = importlib.import_module("__graft_entry__")
     entry.build()
+
+
+def test_new_entry_points_validate_before_touching_a_device(tbl):
+    """Argument errors of the batched grouped call, the router and the pack reader come back as status codes
+    on a machine without a GPU (nothing is enqueued)."""
+    import ctypes as C
+    from reimagined_b200 import capi
+    view = capi.LinearView(None, 0x1000, None, None, 256, 16, 8, 0, 1.0, None, None)
+    arr = (capi.LinearView * 1)(view)
+    assert tbl.tbl_grouped_forward_rows(arr, 1, 0x1000, 65, 0x2000, 65 * 16, 0, 0x3000, 1 << 20, None) == -2   # rows > 64
+    assert tbl.tbl_grouped_forward_rows(arr, 1, 0x1000, 4, 0x2000, 8, 0, 0x3000, 1 << 20, None) == -2         # stride too small
+    assert tbl.tbl_grouped_forward_rows(arr, 0, 0x1000, 4, 0x2000, 64, 0, 0x3000, 1 << 20, None) == -1
+    assert tbl.tbl_grouped_rows_workspace_bytes(5, 8, 768) >= 2 * 8 * 768
+    assert tbl.tbl_router_topk(None, 4, 8, 2, 0x1000, None) == -1
+    assert tbl.tbl_router_topk(0x1000, 4, 33, 2, 0x1000, None) == -1                                          # > TBL_MAX_GROUPS
+    version, layers = C.c_int(0), C.c_int(0)
+    assert tbl.tbl_edge_pack_open(b"DGE1", 4, C.byref(version), C.byref(layers)) == -11
+    assert tbl.tbl_status_string(-11).decode().startswith("edge pack")
+    assert tbl.tbl_status_string(-12).decode().startswith("edge pack")
