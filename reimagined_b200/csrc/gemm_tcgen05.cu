@@ -367,7 +367,21 @@ cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales
     p.act_scales = act_scales; p.y = y; p.K = K; p.N = N; p.M = total_rows;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
-    const int bn = N > 128 ? 256 : 128;
+    // tile width: 256, unless that leaves SMs without a tile -- then the narrower width whose rounds over the
+    // 148 SMs cost least (rounds x width; narrower tiles re-read the activations more often, so they are only
+    // worth it while the launch is short of tiles).  The row-tile count is an estimate: the real one depends
+    // on the device-side row counts (about half a ragged tile per problem).
+    const long long row_tiles = (total_rows + BM - 1) / BM + (groups + 1) / 2;
+    int bn = 256;
+    if (row_tiles * ((N + 255) / 256) < kNumSm) {
+        long long best = -1;
+        for (int cand = 256; cand >= 64; cand >>= 1) {
+            if (cand > 64 && N <= cand / 2) continue;
+            const long long tiles = row_tiles * ((N + cand - 1) / cand);
+            const long long cost = ((tiles + kNumSm - 1) / kNumSm) * cand;
+            if (best < 0 || cost < best) { best = cost; bn = cand; }
+        }
+    }
     p.tiles_n = (N + bn - 1) / bn;
     GroupTable gt{};
     gt.groups = groups; gt.cap = cap; gt.squared_relu = squared_relu; gt.rows_dev = rows_dev; gt.offset_dev = offset_dev;
@@ -382,7 +396,8 @@ cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales
     // tiles: at most ceil(total/128) + groups row tiles (one ragged tile per problem) times the n-tiles
     const long long tiles = (static_cast<long long>((total_rows + BM - 1) / BM) + groups) * p.tiles_n;
     const int grid = tiles < kNumSm ? static_cast<int>(tiles) : kNumSm;
-    return bn == 256 ? launch_grouped_bn<256>(ma, p, gt, grid, stream) : launch_grouped_bn<128>(ma, p, gt, grid, stream);
+    return bn == 256 ? launch_grouped_bn<256>(ma, p, gt, grid, stream)
+                     : (bn == 128 ? launch_grouped_bn<128>(ma, p, gt, grid, stream) : launch_grouped_bn<64>(ma, p, gt, grid, stream));
 }
 
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8, float weight_scale,
