@@ -367,15 +367,15 @@ cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales
     p.act_scales = act_scales; p.y = y; p.K = K; p.N = N; p.M = total_rows;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
-    // tile width: 256, unless that leaves SMs without a tile -- then the narrower width whose rounds over the
-    // 148 SMs cost least (rounds x width; narrower tiles re-read the activations more often, so they are only
-    // worth it while the launch is short of tiles).  The row-tile count is an estimate: the real one depends
+    // tile width: the one whose rounds over the 148 SMs cost least (rounds x width) among 256 and 128, and 64
+    // too while even 256-wide tiles leave SMs without one (narrow tiles re-read the activations more often).  The row-tile count is an estimate: the real one depends
     // on the device-side row counts (about half a ragged tile per problem).
     const long long row_tiles = (total_rows + BM - 1) / BM + (groups + 1) / 2;
     int bn = 256;
-    if (row_tiles * ((N + 255) / 256) < kNumSm) {
+    {
+        const bool short_of_tiles = row_tiles * ((N + 255) / 256) < kNumSm;
         long long best = -1;
-        for (int cand = 256; cand >= 64; cand >>= 1) {
+        for (int cand = 256; cand >= (short_of_tiles ? 64 : 128); cand >>= 1) {
             if (cand > 64 && N <= cand / 2) continue;
             const long long tiles = row_tiles * ((N + cand - 1) / cand);
             const long long cost = ((tiles + kNumSm - 1) / kNumSm) * cand;

@@ -131,6 +131,7 @@ def moe(args) -> None:
 
     views = [make_view(hidden, dim) for _ in range(E)] + [make_view(dim, hidden) for _ in range(E)]
     arr = (capi.LinearView * (2 * E))(*views)
+    torch.manual_seed(0)          # the same routing every run
     x = torch.randn((rows, dim), device="cuda")
     # top-k routing weights: k distinct experts per token, weights summing to one
     scores = torch.rand((rows, E), device="cuda")
