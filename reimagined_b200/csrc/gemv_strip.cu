@@ -57,7 +57,7 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 // the 2048-deep stage): every shared-memory offset of a stage is then a compile-time constant off three
 // base registers, the four blocks of a warp are fully unrolled, and all lanes read row 0's activation
 // fragment (one 128-byte wavefront per load instead of four).
-template <int NT, bool SCALED, int WPS, bool FAST>
+template <int NT, bool SCALED, int WPS, int FAST>
 __global__ void __launch_bounds__((kStripSlots * WPS + 1) * 32, 1)
 gemv_strip_kernel(const __grid_constant__ StripParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -390,7 +390,49 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                             }
                         }
                     };
-                    if constexpr (FAST) {
+                    if constexpr (FAST == 2) {
+                        // Up to eight rows, fused or staged activations, full 2048-deep stages: the stage's four
+                        // blocks of this warp unrolled with constant weight offsets and the loads of a block
+                        // issued ahead of the MMAs of the block before it (as in the single-row path below);
+                        // only the activation addresses depend on the row count.
+                        static_assert(NT == 1 && WPS == 2 && SCALED, "pipelined few-row path");
+                        const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
+                        const uint32_t w1 = w0 + cnt * 4096;
+                        const uint32_t rstride = R * 256;
+                        const uint32_t a0 = (P.fused ? acts_resident_addr + ksi * 8 * rstride : stage_addr + wstage) + part * rstride;
+                        struct Operands { uint4 lo, hi, b[4]; };
+                        auto load_block = [&](const uint32_t wblk, const uint32_t ablk) {
+                            Operands o;
+                            o.lo = lds128(wblk);
+                            o.hi = lds128(wblk + 512);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + aoff[x]);
+                            return o;
+                        };
+                        auto mma_block = [&](const Operands& o) {
+                            const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
+                            const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
+#pragma unroll
+                            for (int xp = 0; xp < 2; ++xp) {
+                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
+                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t mk = 0x03030303u << (2 * j);
+                                    mma_u8s8(acc[j][0], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
+                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                }
+                            }
+                        };
+                        const Operands o0 = load_block(w0, a0);
+                        const Operands o1 = load_block(w0 + 2048, a0 + 2 * rstride);
+                        mma_block(o0);
+                        const Operands o2 = load_block(w1, a0 + 4 * rstride);
+                        mma_block(o1);
+                        const Operands o3 = load_block(w1 + 2048, a0 + 6 * rstride);
+                        mma_block(o2);
+                        mma_block(o3);
+                    } else if constexpr (FAST == 1) {
                         static_assert(NT == 1 && WPS == 2 && SCALED, "single-row fast path");
                         // blocks part, part+2 of both slabs; activation block b of the resident row at b*256
                         const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
@@ -584,7 +626,7 @@ __global__ void __launch_bounds__(256) permute_q_kernel(const int8_t* __restrict
 
 cudaEvent_t g_event_start = nullptr, g_event_stop = nullptr;
 
-template <int NT, bool SCALED, int WPS, bool FAST = false>
+template <int NT, bool SCALED, int WPS, int FAST = 0>
 cudaError_t launch_variant(const StripParams& P, int grid, size_t smem, cudaStream_t stream) {
     auto kernel = gemv_strip_kernel<NT, SCALED, WPS, FAST>;
     smem += WPS > 1 ? kStripSlots * (WPS - 1) * 32 * 4 * NT * 4 : 0;
@@ -691,6 +733,9 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
         return cudaErrorInvalidValue;
     const bool fast = nt == 1 && count == 1 && P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0;
+    // up to eight rows (no device-side row counts), every stage full
+    const bool few_rows_fast = nt == 1 && count == 1 && !problems[0].rows_dev && !problems[0].offset_dev &&
+                               P.ks == 2048 && problems[0].K % 2048 == 0;
     // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
     P.share_base = total / grid;
     P.share_rem = total % grid;
@@ -712,7 +757,9 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     switch (nt) {
         case 1:
             if (fast)
-                return launch_variant<1, true, 2, true>(P, grid, smem, stream);
+                return launch_variant<1, true, 2, 1>(P, grid, smem, stream);
+            if (few_rows_fast)
+                return launch_variant<1, true, 2, 2>(P, grid, smem, stream);
             return launch_variant<1, true, 2>(P, grid, smem, stream);
         case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);
         case 4: return launch_variant<4, true, 1>(P, grid, smem, stream);
