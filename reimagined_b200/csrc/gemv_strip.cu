@@ -391,47 +391,55 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                         }
                     };
                     if constexpr (FAST == 2) {
-                        // Up to eight rows, fused or staged activations, full 2048-deep stages: the stage's four
-                        // blocks of this warp unrolled with constant weight offsets and the loads of a block
-                        // issued ahead of the MMAs of the block before it (as in the single-row path below);
-                        // only the activation addresses depend on the row count.
-                        static_assert(NT == 1 && WPS == 2 && SCALED, "pipelined few-row path");
+                        // Up to 16 rows, fused or staged activations, full 2048-deep stages: the stage's blocks of
+                        // this warp unrolled with constant weight offsets and the loads of a block issued ahead
+                        // of the MMAs of the block before it (as in the single-row path below); only the
+                        // activation addresses depend on the row count.
+                        static_assert(NT <= 2 && SCALED && 4 % WPS == 0, "pipelined few-row path");
+                        constexpr int kBlocks = 8 / WPS;                       // blocks part, part + WPS, ...
                         const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
-                        const uint32_t w1 = w0 + cnt * 4096;
+                        const uint32_t wslab = cnt * 4096;
                         const uint32_t rstride = R * 256;
                         const uint32_t a0 = (P.fused ? acts_resident_addr + ksi * 8 * rstride : stage_addr + wstage) + part * rstride;
-                        struct Operands { uint4 lo, hi, b[4]; };
-                        auto load_block = [&](const uint32_t wblk, const uint32_t ablk) {
-                            Operands o;
+                        struct Operands { uint4 lo, hi, b[NT][4]; };
+                        auto load_block = [&](Operands& o, const int i) {
+                            const int b = i * WPS;                             // relative to `part`
+                            const uint32_t wblk = w0 + (b >> 2) * wslab + (b & 3) * 1024;
+                            const uint32_t ablk = a0 + b * rstride;
                             o.lo = lds128(wblk);
                             o.hi = lds128(wblk + 512);
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + aoff[x]);
-                            return o;
+                            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) o.b[nt][x] = lds128(ablk + nt * 2048 + aoff[x]);
                         };
                         auto mma_block = [&](const Operands& o) {
                             const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
                             const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
 #pragma unroll
                             for (int xp = 0; xp < 2; ++xp) {
-                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
-                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const uint32_t mk = 0x03030303u << (2 * j);
-                                    mma_u8s8(acc[j][0], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
-                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+#pragma unroll
+                                    for (int nt = 0; nt < NT; ++nt) {
+                                        const uint4& B0 = o.b[nt][2 * xp];
+                                        const uint4& B1 = o.b[nt][2 * xp + 1];
+                                        const uint32_t b0 = j == 0 ? B0.x : (j == 1 ? B0.y : (j == 2 ? B0.z : B0.w));
+                                        const uint32_t b1 = j == 0 ? B1.x : (j == 1 ? B1.y : (j == 2 ? B1.z : B1.w));
+                                        mma_u8s8(acc[j][nt], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
+                                                 hw[2 * xp + 1] & mk, b0, b1);
+                                    }
                                 }
                             }
                         };
-                        const Operands o0 = load_block(w0, a0);
-                        const Operands o1 = load_block(w0 + 2048, a0 + 2 * rstride);
-                        mma_block(o0);
-                        const Operands o2 = load_block(w1, a0 + 4 * rstride);
-                        mma_block(o1);
-                        const Operands o3 = load_block(w1 + 2048, a0 + 6 * rstride);
-                        mma_block(o2);
-                        mma_block(o3);
+                        Operands ops[2];
+                        load_block(ops[0], 0);
+#pragma unroll
+                        for (int i = 0; i < kBlocks; ++i) {
+                            if (i + 1 < kBlocks) load_block(ops[(i + 1) & 1], i + 1);
+                            mma_block(ops[i & 1]);
+                        }
                     } else if constexpr (FAST == 1) {
                         static_assert(NT == 1 && WPS == 2 && SCALED, "single-row fast path");
                         // blocks part, part+2 of both slabs; activation block b of the resident row at b*256
@@ -733,8 +741,8 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     if (P.fused && (nt != 1 || problems[0].rows > gemv_strip_fused_rows(problems[0].K) || problems[0].rows_dev))
         return cudaErrorInvalidValue;
     const bool fast = nt == 1 && count == 1 && P.fused && problems[0].rows == 1 && P.ks == 2048 && problems[0].K % 2048 == 0;
-    // up to eight rows (no device-side row counts), every stage full
-    const bool few_rows_fast = nt == 1 && count == 1 && !problems[0].rows_dev && !problems[0].offset_dev &&
+    // up to 16 rows (no device-side row counts), every stage full
+    const bool few_rows_fast = nt <= 2 && count == 1 && !problems[0].rows_dev && !problems[0].offset_dev &&
                                P.ks == 2048 && problems[0].K % 2048 == 0;
     // a CTA's passes take at most `slots` strips: size the stages for the largest share, not for 8
     P.share_base = total / grid;
@@ -761,7 +769,9 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
             if (few_rows_fast)
                 return launch_variant<1, true, 2, 2>(P, grid, smem, stream);
             return launch_variant<1, true, 2>(P, grid, smem, stream);
-        case 2: return launch_variant<2, true, 1>(P, grid, smem, stream);
+        case 2:
+            if (few_rows_fast) return launch_variant<2, true, 1, 2>(P, grid, smem, stream);
+            return launch_variant<2, true, 1>(P, grid, smem, stream);
         case 4: return launch_variant<4, true, 1>(P, grid, smem, stream);
         default: return launch_variant<8, false, 1>(P, grid, smem, stream);
     }
