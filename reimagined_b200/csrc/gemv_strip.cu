@@ -721,10 +721,10 @@ cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t st
     const int nt = max_rows <= 8 ? 1 : (max_rows <= 16 ? 2 : (max_rows <= 32 ? 4 : 8));
     // Stage depth in k.  Two slabs (2048) per stage halve the per-stage synchronisation of a consumer warp
     // (16384^2, M = 1: 20.8 -> 18.5 us); three are no better, with only two stages left in the ring.
-    // Tall activation tiles leave room for half a slab only.
+    // Tall activation tiles leave room for one slab (long rows: 16384^2 M=64 70.9 -> 64.8 us) or half a slab.
     int max_k = 0;
     for (int i = 0; i < count; ++i) max_k = problems[i].K > max_k ? problems[i].K : max_k;
-    P.ks = nt <= 2 ? (max_k >= 2048 ? 2048 : 1024) : 512;
+    P.ks = nt <= 2 ? (max_k >= 2048 ? 2048 : 1024) : (max_k >= 4096 ? 1024 : 512);
     P.stage_shift = P.ks == 2048 ? 3 : (P.ks == 1024 ? 2 : 1);
     int grid = (total + kStripSlots - 1) / kStripSlots;
     if (grid > kNumSm) grid = kNumSm;
