@@ -378,7 +378,7 @@ def run_ours(args):
                 "ms_per_step": ms_e2e / args.steps, "matches_resident_result": e2e_matches},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gemv_strip_kernel<1,true,2,true> (quantiser fused, single-row path)", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "gemv_strip_kernel<1,true,2,1> (quantiser fused, single-row path)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "kernel_us": kernel_ms * 1e3,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
