@@ -332,3 +332,20 @@ def test_checksums_at_full_size_16384(cuda, port, tbl, M):
         _, acc_all = H.gemm(H.dev(oq), H.dev(osc), w_i8, scale)
     assert np.array_equal(acc_all.cpu().numpy().astype(np.int64).sum(axis=1), oq.astype(np.int64) @ col)
     assert H.device_status() == 0
+
+
+@pytest.mark.parametrize("K", [2048, 4096, 6144])
+@pytest.mark.parametrize("M", [2, 5, 8, 9, 13, 16])
+def test_few_row_pipelined_path_bit_exact(cuda, port, tbl, M, K):
+    """2..16 rows with K a multiple of the 2048-deep stage: the unrolled, software-pipelined variant of the strip
+    kernel (fused quantiser while rows*K <= 16384, staged activations above), ragged N, magnitude and bias."""
+    import gpu_helpers as H
+    N = {2048: 1000, 4096: 130, 6144: 17}[K]
+    w, x, mag, bias = make_case(1000 * M + K, N, K, M, affine=True)
+    words, scale, t, _ = port.pack_weights(w)
+    oy, *_ = port.linear_forward(x, words, scale, N, magnitude=mag, bias=bias)
+    dwords = H.words_dev(words)
+    y = H.linear_forward(H.dev(x), None, scale, N, magnitude=H.dev(mag), bias=H.dev(bias),
+                         strips=H.relayout_strips(dwords, N, K)).cpu().numpy()
+    assert bits_equal(y, oy), f"max diff {np.abs(y - oy).max()}"
+    assert H.device_status() == 0
