@@ -242,6 +242,25 @@ int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, cons
  * src/jamba.cpp:8268-8296). */
 int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, float* weights_dev, void* stream);
 
+/* ---- device: the norms either side of a linear ---------------------------------------- */
+
+/* Row-wise RMSNorm x weight, with the SiLU gate that precedes it in the Mamba-2 epilogue and, optionally, the
+ * per-token quantiser that follows it, in one launch (one CTA per row, the row kept in shared memory):
+ *   gate_dev == NULL:  n = value.rmsnorm(eps) * weight           block norm, OXN/nsos/src/jamba.cpp:3175-3179
+ *                                                                (Tensor::rmsnorm, OXN/nsos/src/tensor.cpp:3455-3490)
+ *   gate_dev != NULL:  n = (value * silu(gate)).rmsnorm(eps) * weight
+ *                      Replaces: launch_mamba_gated_rmsnorm (OXN/nsos/src/cuda/mamba_kernels.cu:3421-3446) and the
+ *                      unfused y.mul(z.silu()).rmsnorm(eps).mul(weight) (OXN/nsos/src/mamba2.cpp:4011).
+ * value / gate / out are fp32 [rows, dim], weight_dev fp32 [dim] or NULL (no learnable weight).
+ * out_dev (may be NULL) receives n.  q_dev (may be NULL; needs dim % 16 == 0) receives the int8 codes of n with
+ * act_scales_dev [rows] and, if not NULL, q_sums_dev [rows]: bit for bit what tbl_quantize_rows(n, bits,
+ * TBL_RMS_NONE, TBL_TIE_EVEN) gives, ready for tbl_gemv / tbl_gemm, without n going through memory.
+ * At least one of out_dev / q_dev.  dim <= 49152.  fp32 results agree with the reference's CPU ops to 1e-5
+ * relative (the sum of squares is a tree, exp is the device's expf), not bit for bit. */
+int tbl_row_norm(const float* value_dev, const float* gate_dev, const float* weight_dev, int rows, int dim,
+                 float eps, float* out_dev, int bits, int8_t* q_dev, float* act_scales_dev,
+                 int32_t* q_sums_dev, void* stream);
+
 /* Bytes of scratch for tbl_moe_forward. */
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row);
 

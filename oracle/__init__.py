@@ -63,6 +63,8 @@ class _Port:
         L.tor_linear_forward_i8_mt.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _i8p, C.c_float,
                                                C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_int]
         L.tor_squared_relu.argtypes = [_f32p, C.c_int64, _f32p]
+        L.tor_row_norm.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, _f32p]
+        L.tor_row_norm.restype = None
         L.tor_router_topk.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p]
         pp_u32 = C.POINTER(_u32p)
         pp_f32 = C.POINTER(_f32p)
@@ -95,6 +97,17 @@ class _Port:
         M, K = x.shape
         out = np.empty_like(x)
         self.lib.tor_rmsnorm_rows(_ptr(x, _f32p), M, K, eps, _ptr(out, _f32p))
+        return out
+
+    def row_norm(self, value, gate=None, weight=None, eps=1e-6):
+        """RMSNorm x weight of each row of value (x silu(gate) first when a gate is given)."""
+        value = _f32(value)
+        rows, dim = value.shape
+        gate = None if gate is None else _f32(gate)
+        weight = None if weight is None else _f32(weight)
+        out = np.empty_like(value)
+        self.lib.tor_row_norm(_ptr(value, _f32p), None if gate is None else _ptr(gate, _f32p),
+                              None if weight is None else _ptr(weight, _f32p), rows, dim, eps, _ptr(out, _f32p))
         return out
 
     def quantize_rows(self, x, bits=8, tie_mode=0):
@@ -185,6 +198,7 @@ class _Ref:
         L.ref_layer_forward_mt.argtypes = [C.POINTER(C.c_void_p), C.c_int, _f32p, C.c_int, _f32p]
         L.ref_layers_forward_parallel.argtypes = [C.POINTER(C.c_void_p), C.c_int, _f32p, C.c_int, C.POINTER(_f32p)]
         L.ref_layer_destroy.argtypes = [C.c_void_p]
+        L.ref_row_norm.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, _f32p]
         L.ref_moe_forward.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p,
                                       _f32p, _f32p, C.c_int, _f32p]
 
@@ -241,6 +255,19 @@ class _Ref:
 
     def layer_destroy(self, h):
         self.lib.ref_layer_destroy(h)
+
+    def row_norm(self, value, gate=None, weight=None, eps=1e-6):
+        """The reference's own Tensor ops: value[.mul(gate.silu())].rmsnorm(eps)[.mul(weight)]."""
+        value = _f32(value)
+        rows, dim = value.shape
+        gate = None if gate is None else _f32(gate)
+        weight = None if weight is None else _f32(weight)
+        out = np.empty_like(value)
+        rc = self.lib.ref_row_norm(_ptr(value, _f32p), None if gate is None else _ptr(gate, _f32p),
+                                   None if weight is None else _ptr(weight, _f32p), rows, dim, eps, _ptr(out, _f32p))
+        if rc != 0:
+            raise RuntimeError("reference norm composition raised")
+        return out
 
     def moe_forward(self, x, routing, up_w, down_w, bits=8):
         """up_w fp32 [E,H,D], down_w fp32 [E,D,H]; experts are default-mode BitLinears."""

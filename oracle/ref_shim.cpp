@@ -191,4 +191,32 @@ void ref_sha256_hex(const void* data, size_t size, char* out) {
     std::memcpy(out, hex.c_str(), hex.size() + 1);
 }
 
+// The decode glue either side of a linear, composed from the reference's own Tensor ops exactly as its host
+// branches compose them.  gate == NULL: block norm, x.rmsnorm(eps).mul(weight) (OXN/nsos/src/jamba.cpp:3175-3179;
+// weight may be NULL for the non-learnable norm).  gate != NULL: the Mamba-2 epilogue
+// y.mul(z.silu()).rmsnorm(eps).mul(weight) (OXN/nsos/src/mamba2.cpp:4011).  Returns 0, or -1 on error.
+int ref_row_norm(const float* value, const float* gate, const float* weight, int rows, int dim, float eps,
+                 float* out) {
+    try {
+        const size_t n = static_cast<size_t>(rows) * dim;
+        Tensor v({rows, dim}, Device::CPU);
+        std::memcpy(v.data(), value, sizeof(float) * n);
+        if (gate) {
+            Tensor z({rows, dim}, Device::CPU);
+            std::memcpy(z.data(), gate, sizeof(float) * n);
+            v = v.mul(z.silu());
+        }
+        Tensor normed = v.rmsnorm(eps);
+        if (weight) {
+            Tensor w({dim}, Device::CPU);
+            std::memcpy(w.data(), weight, sizeof(float) * dim);
+            normed = normed.mul(w);
+        }
+        std::memcpy(out, normed.data(), sizeof(float) * n);
+        return 0;
+    } catch (...) {
+        return -1;
+    }
+}
+
 }  // extern "C"

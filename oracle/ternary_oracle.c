@@ -304,6 +304,38 @@ void tor_moe_forward(const float* x, int rows, int D, int H, int E, const float*
     free(sel);
 }
 
+/* ---- F1: the norms either side of a linear in the decode step ---------------------
+ * gate == NULL: block norm x.rmsnorm(eps).mul(weight) (OXN/nsos/src/jamba.cpp:3175-3179).
+ * gate != NULL: Mamba-2 epilogue y.mul(z.silu()).rmsnorm(eps).mul(weight)
+ * (OXN/nsos/src/mamba2.cpp:4011; the fused device form is
+ * OXN/nsos/src/cuda/mamba_kernels.cu:3421-3441).  silu follows Tensor::silu's CPU branch
+ * (OXN/nsos/src/tensor.cpp:3273-3280: the two-sided sigmoid), the norm follows tor_rmsnorm_rows;
+ * every product is rounded on its own.  weight may be NULL (non-learnable norm). */
+void tor_row_norm(const float* value, const float* gate, const float* weight, int rows, int dim,
+                  float eps, float* out) {
+    for (int r = 0; r < rows; ++r) {
+        const float* v = value + (int64_t)r * dim;
+        const float* z = gate ? gate + (int64_t)r * dim : 0;
+        float* dst = out + (int64_t)r * dim;
+        float sum_sq = 0.0f;
+        for (int j = 0; j < dim; ++j) {
+            float a = v[j];
+            if (z) {
+                const float g = z[j];
+                const float sig = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
+                a = a * (g * sig);
+            }
+            dst[j] = a;
+            sum_sq += a * a;
+        }
+        const float inv = 1.0f / sqrtf(sum_sq / (float)(dim > 1 ? dim : 1) + eps);
+        for (int j = 0; j < dim; ++j) {
+            const float n = dst[j] * inv;
+            dst[j] = weight ? n * weight[j] : n;
+        }
+    }
+}
+
 /* Multi-threaded wrapper for the CPU-baseline timing legs: rows are sharded over
  * `threads` OpenMP workers (the reference's GEMM itself is single-threaded,
  * OXN/nsos/src/bitnet_adapter_avx2.cpp has no OpenMP; sharding rows is the fair

@@ -76,6 +76,7 @@ _SIGNATURES = {
     "tbl_grouped_forward_rows": (C.c_int, [C.POINTER(LinearView), C.c_int, _vp, C.c_int, _vp, C.c_longlong, C.c_int,
                                            _vp, C.c_size_t, _vp]),
     "tbl_router_topk": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, _vp]),
+    "tbl_row_norm": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_float, _vp, C.c_int, _vp, _vp, _vp, _vp]),
     "tbl_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tbl_moe_forward": (C.c_int, [C.POINTER(LinearView), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_size_t, _vp]),

@@ -451,6 +451,21 @@ int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, f
                                           static_cast<cudaStream_t>(stream)));
 }
 
+int tbl_row_norm(const float* value_dev, const float* gate_dev, const float* weight_dev, int rows, int dim,
+                 float eps, float* out_dev, int bits, int8_t* q_dev, float* act_scales_dev, int32_t* q_sums_dev,
+                 void* stream) {
+    if (!value_dev || (!out_dev && !q_dev) || rows <= 0 || dim <= 0) return TBL_ERR_INVALID_ARG;
+    if (!(eps > 0.0f) || !std::isfinite(eps)) return TBL_ERR_INVALID_ARG;     // Tensor::rmsnorm refuses the same
+    if (dim > kRowNormMaxDim) return TBL_ERR_SHAPE;
+    if (q_dev) {
+        if (!act_scales_dev) return TBL_ERR_INVALID_ARG;
+        if (bits < 2 || bits > 8) return TBL_ERR_BITS;
+        if (dim % 16 || (reinterpret_cast<uintptr_t>(q_dev) & 3)) return TBL_ERR_SHAPE;
+    }
+    return cuda_status(launch_row_norm(value_dev, gate_dev, weight_dev, rows, dim, eps, bits, out_dev, q_dev,
+                                       act_scales_dev, q_sums_dev, static_cast<cudaStream_t>(stream)));
+}
+
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row) {
     if (rows <= 0 || dim <= 0 || hidden_dim <= 0 || experts <= 0 || max_routes_per_row <= 0) return 0;
     if (max_routes_per_row > experts) max_routes_per_row = experts;

@@ -125,6 +125,13 @@ cudaError_t launch_moe_route(const float* routing, int rows, int experts, int ca
                              int* status, cudaStream_t stream);
 cudaError_t launch_router_topk(const float* logits, int rows, int experts, int top_k, float* weights,
                                cudaStream_t stream);
+// glue.cu -- row norms around a linear (block RMSNorm x weight; SiLU gate -> RMSNorm x weight), optionally
+// fused with the per-token quantiser.  gate / weight / out / q may be null (q and out not both); q needs
+// dim % 16 == 0.  The row is cached in shared memory, which bounds dim.
+constexpr int kRowNormMaxDim = 49152;
+cudaError_t launch_row_norm(const float* value, const float* gate, const float* weight, int rows, int dim, float eps,
+                            int bits, float* out, int8_t* q, float* act_scales, int32_t* q_sums,
+                            cudaStream_t stream);
 cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,
                              int experts, int dim, float* out, cudaStream_t stream);
 

@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own C++ (oracle/_ref/libnsos_ref.so,
 built by oracle/Makefile from the reference checkout) on seeded inputs.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [name-prefix]      # only fixtures whose name starts with the prefix
 
 Only runs where the reference checkout is available; the produced fixtures are committed and are
 what the CPU-only and GPU tests compare against on machines without the reference.
@@ -52,9 +52,41 @@ LINEAR_CASES = [
 ]
 
 
+def row_norm_fixtures(R, only):
+    """Block norm and gated Mamba-2 epilogue norm from the reference's own Tensor ops (ref_row_norm)."""
+    for name, seed, rows, dim, gated, weighted, eps in ROW_NORM_CASES:
+        if not name.startswith(only):
+            continue
+        rng = np.random.default_rng(seed)
+        value = rng.standard_normal((rows, dim)).astype(np.float32)
+        gate = (2.5 * rng.standard_normal((rows, dim))).astype(np.float32) if gated else None
+        weight = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32) if weighted else None
+        out = R.row_norm(value, gate, weight, eps)
+        rec = dict(seed=seed, eps=np.float32(eps), value=value, out=out)
+        if gated:
+            rec["gate"] = gate
+        if weighted:
+            rec["weight"] = weight
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), **rec)
+        print(name, "out[0,:3]", out[0, :3])
+
+
+# name, seed, rows, dim, gated, weighted, eps
+ROW_NORM_CASES = [
+    ("rownorm_block_3x768", 31, 3, 768, False, True, 1e-6),
+    ("rownorm_plain_2x50", 32, 2, 50, False, False, 1e-5),
+    ("rownorm_gated_4x1536", 33, 4, 1536, True, True, 1e-5),
+    ("rownorm_gated_2x33", 34, 2, 33, True, True, 1e-6),
+]
+
+
 def main():
+    only = sys.argv[1] if len(sys.argv) > 1 else ""
     R = oracle.ref()
+    row_norm_fixtures(R, only)
     for name, seed, N, K, M, exact, affine, bits, store in LINEAR_CASES:
+        if not name.startswith(only):
+            continue
         w, x, mag, bias = make_inputs(seed, N, K, M, affine)
         words, scale = R.pack(w)
         y = R.linear_forward(w, x, exact_linear=exact, magnitude=mag, bias=bias, bits=bits)
@@ -67,6 +99,8 @@ def main():
         np.savez_compressed(os.path.join(OUT, name + ".npz"), **rec)
         print(name, "scale", scale, "y[0,:3]", y[0, :3])
 
+    if not "moe_6x64x128_e4".startswith(only):
+        return
     # MoE expert FFN (default-mode experts: RMS input norm, magnitude 1, no bias), top-2 of 4
     rng = np.random.default_rng(21)
     rows, D, H, E, top_k = 6, 64, 128, 4, 2
