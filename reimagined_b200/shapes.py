@@ -25,9 +25,16 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--no-i8", action="store_true", help="MoE: views without the int8 expansion (strip GEMV path)")
+    ap.add_argument("--norm", action="store_true",
+                    help="time tbl_row_norm instead: --m rows of --k elements (RMSNorm x weight)")
+    ap.add_argument("--gated", action="store_true", help="row norm: SiLU gate first (the Mamba-2 epilogue)")
+    ap.add_argument("--codes", choices=["no", "also", "only"], default="no",
+                    help="row norm: also emit the int8 codes of the result, or only them (no fp32 store)")
     args = ap.parse_args()
     if args.moe:
         return moe(args)
+    if args.norm:
+        return norm(args)
 
     import torch
     from . import capi
@@ -97,6 +104,61 @@ def main() -> None:
     print(json.dumps({"m": m, "n": n, "k": k, "us_per_call": round(us, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
                       "tops": round(2.0 * m * n * k / us / 1e6, 1), "weight_buffers": buffers,
                       "graph": not args.no_graph, "device_status": status}))
+
+
+def norm(args) -> None:
+    """Row norm (optionally gated, optionally fused with the quantiser) on rotating buffers larger than L2 in total."""
+    import torch
+    from . import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the ternary linear path has no CPU fallback")
+    L = capi.lib()
+    torch.cuda.set_device(0)
+    rows, dim = args.m, args.k
+    want_out, want_q = args.codes != "only", args.codes != "no"
+    in_bytes = rows * dim * 4 * (2 if args.gated else 1)
+    out_bytes = (rows * dim * 4 if want_out else 0) + (rows * dim + 8 * rows if want_q else 0)
+    buffers = max(2, min(24, int(400e6 // (in_bytes + out_bytes)) + 1))
+    sets = []
+    for _ in range(buffers):
+        sets.append((torch.randn((rows, dim), device="cuda"),
+                     torch.randn((rows, dim), device="cuda") if args.gated else None,
+                     torch.empty((rows, dim), device="cuda") if want_out else None,
+                     torch.empty((rows, dim), dtype=torch.int8, device="cuda") if want_q else None))
+    weight = torch.rand(dim, device="cuda") + 0.5
+    scales = torch.empty(rows, device="cuda")
+    sums = torch.empty(rows, dtype=torch.int32, device="cuda")
+
+    def ptr(t):
+        return None if t is None else t.data_ptr()
+
+    def call(i: int) -> None:
+        value, gate, out, q = sets[i % buffers]
+        capi.check(L.tbl_row_norm(ptr(value), ptr(gate), ptr(weight), rows, dim, 1e-5, ptr(out), 8, ptr(q),
+                                  ptr(scales) if want_q else None, ptr(sums) if want_q else None,
+                                  torch.cuda.current_stream().cuda_stream), "tbl_row_norm")
+
+    for i in range(args.warmup):
+        call(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.iters):
+            call(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / args.iters
+    algorithmic = in_bytes + out_bytes + 4 * dim
+    print(json.dumps({"row_norm": True, "rows": rows, "dim": dim, "gated": args.gated, "codes": args.codes,
+                      "us_per_call": round(us, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
+                      "algorithmic_mb": round(algorithmic / 1e6, 2), "buffers": buffers,
+                      "device_status": L.tbl_device_status(torch.cuda.current_stream().cuda_stream)}))
 
 
 def moe(args) -> None:

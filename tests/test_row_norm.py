@@ -86,7 +86,7 @@ def test_kernel_matches_the_reference_fixture(cuda, tbl, path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows,dim", [(1, 768), (8, 1536), (64, 3072), (5, 33), (3, 1), (2, 16384), (1, 49152),
-                                      (700, 2048)])
+                                      (700, 2048), (1500, 1536), (2000, 768), (515, 36), (600, 1028)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_kernel_matches_the_oracle(cuda, port, tbl, rows, dim, gated):
     import gpu_helpers as H
@@ -108,7 +108,8 @@ def test_kernel_matches_the_oracle(cuda, port, tbl, rows, dim, gated):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("rows,dim,bits", [(1, 768, 8), (8, 1536, 8), (64, 3072, 8), (3, 16, 8), (5, 1536, 4),
-                                           (300, 4096, 8)])
+                                           (300, 4096, 8), (600, 1536, 8), (1030, 768, 8), (513, 48, 3),
+                                           (520, 2048, 8)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_fused_codes_are_the_quantiser_on_the_stored_values(cuda, tbl, rows, dim, bits, gated):
     """One launch gives the fp32 row and its int8 codes; the codes, scales and sums equal tbl_quantize_rows
