@@ -254,7 +254,8 @@ int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, f
  * value / gate / out are fp32 [rows, dim], weight_dev fp32 [dim] or NULL (no learnable weight).
  * out_dev (may be NULL) receives n.  q_dev (may be NULL; needs dim % 16 == 0) receives the int8 codes of n with
  * act_scales_dev [rows] and, if not NULL, q_sums_dev [rows]: bit for bit what tbl_quantize_rows(n, bits,
- * TBL_RMS_NONE, TBL_TIE_EVEN) gives, ready for tbl_gemv / tbl_gemm, without n going through memory.
+ * TBL_RMS_NONE, TBL_TIE_EVEN) gives, ready for tbl_gemm (prefill: no quantiser launch, no fp32 round trip) or
+ * tbl_gemv.  At decode sizes prefer out_dev + tbl_linear_forward: its GEMV quantises in its own prologue.
  * At least one of out_dev / q_dev.  dim <= 49152.  fp32 results agree with the reference's CPU ops to 1e-5
  * relative (the sum of squares is a tree, exp is the device's expf), not bit for bit. */
 int tbl_row_norm(const float* value_dev, const float* gate_dev, const float* weight_dev, int rows, int dim,

@@ -8,6 +8,11 @@ out 768->768 and an FFN 768->3072->768 with squared ReLU; LM head 768->32000): 9
 between them are not part of this library -- so the figure is the linear path's share of a token, an upper
 bound on tokens/s, with real data dependencies (every linear consumes an earlier linear's output).
 Projections that share an input go through `tbl_grouped_forward_rows` (one launch for five up to batch 8).
+With `--norms` the norms that feed those linears run too (`tbl_row_norm`): the block RMSNorm x weight before each
+projection group, attention group and FFN, the final norm before the LM head, and the Mamba-2 epilogue -- SiLU
+gate, RMSNorm x weight, one launch -- before the out-projection (the x branch stands in for the scan's output,
+the z branch is the gate).  The norms hand fp32 rows to the linears: at decode sizes the linear quantises in its
+own prologue at no extra launch, so the norm's int8-code output (made for the prefill GEMM) would only add one.
 Weights are synthetic (random codes).  Prints one JSON line.
 """
 from __future__ import annotations
@@ -23,6 +28,7 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--norms", action="store_true", help="also run the norms either side of the linears")
     args = ap.parse_args()
 
     import torch
@@ -79,6 +85,11 @@ def main() -> None:
     attn_out = torch.empty((2, B * 2 * D), device="cuda")
     ffn_mid = torch.empty((B, FFN), device="cuda")
     logits = torch.empty((B, VOCAB), device="cuda")
+    # --norms: per-block weights of the norms, the normalised row and the gated epilogue's output
+    block_norm_w = [torch.rand(D, device="cuda") + 0.5 for _ in range(LAYERS + 2 * len(HYBRID_LAYERS) + 1)]
+    gated_norm_w = [torch.rand(inner, device="cuda") + 0.5 for _ in range(LAYERS)]
+    normed = torch.empty((B, D), device="cuda")
+    gated_out = torch.empty((B, inner), device="cuda")
 
     def linear(lin, x_ptr: int, y_ptr: int) -> None:
         capi.check(L.tbl_linear_forward(x_ptr, None, lin["strips"].data_ptr(), None, lin["scale"], B, lin["k"],
@@ -96,20 +107,38 @@ def main() -> None:
             for i, l in enumerate(lins):
                 linear(l, x.data_ptr(), out[i].data_ptr())
 
+    def block_norm(x, weight):
+        """RMSNorm x weight of the residual stream into `normed` (identity without --norms)."""
+        if not args.norms:
+            return x
+        capi.check(L.tbl_row_norm(x.data_ptr(), None, weight.data_ptr(), B, D, 1e-5, normed.data_ptr(), 8, None, None,
+                                  None, torch.cuda.current_stream().cuda_stream), "tbl_row_norm")
+        return normed
+
+    def mamba_epilogue(blk, weight, y_ptr: int) -> None:
+        """x branch (gated by the z branch and normalised with --norms) -> out projection."""
+        if not args.norms:
+            return linear(blk["out"], proj_out[0].data_ptr(), y_ptr)
+        capi.check(L.tbl_row_norm(proj_out[0].data_ptr(), proj_out[1].data_ptr(), weight.data_ptr(), B, inner, 1e-5,
+                                  gated_out.data_ptr(), 8, None, None, None, torch.cuda.current_stream().cuda_stream),
+                   "tbl_row_norm")
+        linear(blk["out"], gated_out.data_ptr(), y_ptr)
+
     def step() -> None:
         cur = 0
-        for blk in blocks:
-            group(blk["proj"], hidden[cur], proj_out)
-            linear(blk["out"], proj_out[0].data_ptr(), hidden[cur ^ 1].data_ptr())   # x branch -> out projection
+        norm_w = iter(block_norm_w)
+        for layer, blk in enumerate(blocks):
+            group(blk["proj"], block_norm(hidden[cur], next(norm_w)), proj_out)
+            mamba_epilogue(blk, gated_norm_w[layer], hidden[cur ^ 1].data_ptr())
             cur ^= 1
             if "attn" in blk:
-                group(blk["attn"], hidden[cur], attn_out)
+                group(blk["attn"], block_norm(hidden[cur], next(norm_w)), attn_out)
                 linear(blk["attn_out"], attn_out[0].data_ptr(), hidden[cur ^ 1].data_ptr())
                 cur ^= 1
-                linear(blk["ffn_up"], hidden[cur].data_ptr(), ffn_mid.data_ptr())
+                linear(blk["ffn_up"], block_norm(hidden[cur], next(norm_w)).data_ptr(), ffn_mid.data_ptr())
                 linear(blk["ffn_down"], ffn_mid.data_ptr(), hidden[cur ^ 1].data_ptr())
                 cur ^= 1
-        linear(head, hidden[cur].data_ptr(), logits.data_ptr())
+        linear(head, block_norm(hidden[cur], next(norm_w)).data_ptr(), logits.data_ptr())
 
     for _ in range(3):
         step()
@@ -129,8 +158,9 @@ def main() -> None:
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1000.0 / args.iters
     packed_mb = total_weights / 4 / 1e6
-    print(json.dumps({"workload": "D768/L16 decode step, the 107 ternary linears only", "batch": B,
-                      "linears": 107, "kernel_launches_per_step": int(launches), "us_per_step": round(us, 1),
+    workload = "D768/L16 decode step, the 107 ternary linears" + (" and the 37 norms that feed them" if args.norms
+                                                                       else " only")
+    print(json.dumps({"workload": workload, "batch": B, "linears": 107, "norms": 37 if args.norms else 0, "kernel_launches_per_step": int(launches), "us_per_step": round(us, 1),
                       "tokens_per_s_linears_only": round(B / us * 1e6, 1), "ternary_weights": total_weights,
                       "packed_mb": round(packed_mb, 2), "packed_gb_per_s": round(packed_mb / us * 1e3, 1),
                       "device_status": L.tbl_device_status(stream)}))

@@ -31,6 +31,15 @@ def test_decode_step_tool(cuda, tbl):
     assert d["kernel_launches_per_step"] <= 43
 
 
+def test_decode_step_tool_with_norms(cuda, tbl):
+    """The same step with the 37 norms that feed the linears: one launch each."""
+    d = _run(["reimagined_b200.decode_step", "--batch", "2", "--iters", "2", "--norms"])
+    assert d["device_status"] == 0 and d["linears"] == 107 and d["norms"] == 37
+    assert d["kernel_launches_per_step"] <= 43 + 37
+    d = _run(["reimagined_b200.shapes", "--norm", "--m", "600", "--k", "1536", "--gated", "--codes", "only", "--iters", "2"])
+    assert d["device_status"] == 0 and d["row_norm"]
+
+
 def test_layers_loaded_from_an_edge_pack_run_bit_exact(cuda, port, tbl, tmp_path):
     """Pack file -> BitLinear mirror -> device -> forward, against the oracle on the packed state."""
     import numpy as np

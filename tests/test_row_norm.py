@@ -152,3 +152,26 @@ def test_gated_norm_feeds_the_out_projection_without_an_fp32_round_trip(cuda, po
     got = y_fp32.cpu().numpy()
     assert np.abs(got - want).max() <= 0.02 * np.abs(want).max()      # a code may flip where the norms differ by an ulp
     assert H.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_norm_codes_feed_the_prefill_gemm(cuda, port, tbl):
+    """Prefill: norm -> codes in one launch, then the tensor-core GEMM on the codes, equals
+    norm -> fp32 -> tbl_linear_forward (quantiser launch + GEMM) bit for bit."""
+    import gpu_helpers as H
+    rng = np.random.default_rng(78)
+    rows, dim, n = 640, 1536, 768
+    value = rng.standard_normal((rows, dim)).astype(np.float32)
+    gate = (2 * rng.standard_normal((rows, dim))).astype(np.float32)
+    weight = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    w = (rng.standard_normal((n, dim)) * 0.02).astype(np.float32)
+    words, scale, *_ = port.pack_weights(w)
+    dwords = H.words_dev(words)
+    w_i8 = H.expand_i8(dwords, n, dim)
+    out, q, sc, _ = run(H, value, gate, weight, 1e-5, want_q=True)
+    before = tbl.tbl_launch_count()
+    y_codes, _ = H.gemm(q, sc, w_i8, scale, want_acc=False)
+    assert tbl.tbl_launch_count() - before == 1
+    y_fp32 = H.linear_forward(out, dwords, scale, n, w_i8=w_i8)
+    assert cuda.equal(y_codes.view(cuda.int32), y_fp32.view(cuda.int32))
+    assert H.device_status() == 0
