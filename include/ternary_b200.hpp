@@ -72,6 +72,22 @@ inline void validate_packed(const std::uint32_t* words, long long nwords, int N,
     throw_on_status(tbl_validate_packed(words, nwords, N, K, weight_scale, magnitude, bias), "import_packed_state");
 }
 
+// cuda::launch_mamba_gated_rmsnorm (OXN/nsos/include/cuda/mamba_kernels.cuh:383) with its argument list plus the
+// stream: output = rmsnorm(y * silu(z), epsilon) * weight, one launch.  Throws std::invalid_argument where the
+// reference does ("Invalid Mamba RMS geometry": rows < 1, dim < 1, epsilon <= 0).
+inline void mamba_gated_rmsnorm(const float* y, const float* z, const float* weight, float* output, int rows,
+                                int dim, float epsilon, void* stream) {
+    throw_on_status(tbl_row_norm(y, z, weight, rows, dim, epsilon, output, 8, nullptr, nullptr, nullptr, stream),
+                    "mamba_gated_rmsnorm");
+}
+
+// Tensor::rmsnorm(eps).mul(weight) of the block norm (OXN/nsos/src/jamba.cpp:3175-3179); weight may be null.
+inline void rmsnorm_weight(const float* x, const float* weight, float* output, int rows, int dim, float eps,
+                           void* stream) {
+    throw_on_status(tbl_row_norm(x, nullptr, weight, rows, dim, eps, output, 8, nullptr, nullptr, nullptr, stream),
+                    "rmsnorm");
+}
+
 // Sticky device status (bounded waits that gave up, MoE route overflow); synchronises the stream.
 inline void check_device(void* stream) {
     const int status = tbl_device_status(stream);

@@ -33,7 +33,11 @@ int main() {
         tb::bitnet_gemm_158bit_gpu(&dummy, dw, 1, 8, nullptr, nullptr, &dummy, &dummy, 1u << 30, nullptr);
     } catch (const std::overflow_error&) { ++caught; }
     catch (const std::exception&) { caught += 100; }
-    if (caught != 4) { std::printf("caught %d\n", caught); return 2; }
+    try { tb::mamba_gated_rmsnorm(&dummy, &dummy, &dummy, &dummy, 0, 64, 1e-5f, nullptr); }   // rows < 1
+    catch (const std::invalid_argument&) { ++caught; }
+    try { tb::rmsnorm_weight(&dummy, nullptr, &dummy, 4, 64, 0.0f, nullptr); }               // eps must be > 0
+    catch (const std::invalid_argument&) { ++caught; }
+    if (caught != 6) { std::printf("caught %d\n", caught); return 2; }
     if (tb::workspace_bytes(4, 1024, 8) < 2u * 4u * 1024u) return 3;
     std::printf("shim ok\n");
     return 0;
