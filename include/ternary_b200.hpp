@@ -5,7 +5,7 @@
 // arguments, std::overflow_error for K > INT_MAX/254 or M*N > INT_MAX, std::runtime_error for the rest),
 // and `bitnet_gemm_158bit_gpu` has the argument list of nsos::bitnet_gemm_158bit_gpu
 // (OXN/nsos/include/bitnet_gpu_dispatch.h:46-51) with raw device pointers in place of nsos::Tensor
-// (the one-line adaptation to Tensor is shown in INTEGRATION.md).  Nothing here allocates device memory
+// (a Tensor-typed wrapper passes raw_data() of each tensor).  Nothing here allocates device memory
 // or synchronises: the caller owns the output and the scratch, and orders the stream.
 #pragma once
 

@@ -25,10 +25,20 @@ _i32p = C.POINTER(C.c_int32)
 _u32p = C.POINTER(C.c_uint32)
 
 
+def reference_root():
+    """The reference checkout: $REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    root = os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return root if os.path.isdir(os.path.join(root, "OXN", "nsos", "src")) else None
+
+
 def build(verbose: bool = False) -> None:
     """Runs oracle/Makefile (builds the port always, the reference lib when its sources exist)."""
     out = None if verbose else subprocess.DEVNULL
-    subprocess.run(["make", "-C", _HERE, "-j8"], check=True, stdout=out)
+    cmd = ["make", "-C", _HERE, "-j8"]
+    root = reference_root()
+    if root:
+        cmd.append(f"REFERENCE_ROOT={root}")
+    subprocess.run(cmd, check=True, stdout=out)
 
 
 def _ptr(a, typ):

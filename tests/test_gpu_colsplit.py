@@ -1,5 +1,5 @@
-"""Column-split ternary linear over 2 GPUs with an NCCL all-gather (the partition used for the 16384-wide
-case).  Needs two visible CUDA devices; on a single-GPU box the test is skipped."""
+"""Column-split ternary linear over 2 and 4 GPUs with an NCCL all-gather (the partition used for the
+16384-wide case).  Needs that many visible CUDA devices; with fewer the case is skipped."""
 import os
 import socket
 
@@ -25,26 +25,36 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     import oracle
+    from oracle import fast
     from reimagined_b200.bitlinear import BitLinear
     from reimagined_b200.sharding import ColumnParallelBitLinear
     P = oracle.port()
-    rng = np.random.default_rng(9)
-    N, K, M = 512, 1024, 4
-    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
-    x = rng.standard_normal((M, K)).astype(np.float32)
-    full = BitLinear.from_float(w)
-    full.set_exact_linear_mode(True)
-    layer = ColumnParallelBitLinear(full, world, rank).to("cuda")
-    y = layer.forward(torch.from_numpy(x).cuda()).cpu().numpy()
-    want, *_ = P.linear_forward(x, full.packed_weights, full.weight_scale, N)
-    ok = np.array_equal(y.view(np.uint32), want.view(np.uint32))
+    ok = True
+    # a small layer, then the 16384-wide layer the partition exists for (decode row, a 64-row batch on the
+    # 2-bit strips and a 128-row batch on the tensor-core GEMM); every output compared bit for bit with the
+    # unsharded CPU oracle
+    for (N, K, rows) in [(512, 1024, (4,)), (16384, 16384, (1, 64, 128))]:
+        rng = np.random.default_rng(9 + N)
+        w = rng.standard_normal((N, K), dtype=np.float32)
+        w *= np.float32(0.02)
+        full = BitLinear.from_float(w)
+        del w
+        full.set_exact_linear_mode(True)
+        t = P.unpack_i8(full.packed_weights, N, K)
+        layer = ColumnParallelBitLinear(full, world, rank).to("cuda")
+        for M in rows:
+            x = rng.standard_normal((M, K), dtype=np.float32)
+            y = layer.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+            want, *_ = fast.linear_forward(x, t, full.weight_scale)
+            ok = ok and y.shape == want.shape and np.array_equal(y.view(np.uint32), want.view(np.uint32))
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
         f.write("1" if ok else "0")
     dist.destroy_process_group()
 
 
-def test_column_split_all_gather_two_gpus(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two CUDA devices")
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert all(open(tmp_path / f"rank{r}.txt").read() == "1" for r in range(2))
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_split_all_gather(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all(open(tmp_path / f"rank{r}.txt").read() == "1" for r in range(world))

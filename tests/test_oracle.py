@@ -84,3 +84,35 @@ def test_zero_row_and_router(port):
     assert (w != 0).sum(axis=1).tolist() == [2, 2]
     assert w[0, 2] != 0 and w[0, 3] != 0 and w[1, 2] != 0 and w[1, 3] != 0
     assert np.allclose(w.sum(axis=1), 1.0, atol=1e-6)
+
+
+@pytest.mark.parametrize("N,K,M,rms", [(33, 48, 3, 0), (130, 520, 9, 1), (64, 4096, 5, 1), (17, 16384, 2, 0)])
+def test_fast_form_matches_port(port, N, K, M, rms):
+    """oracle/fast.py (BLAS products of the codes, exact below 2^24) against the scalar C restatement."""
+    from oracle import fast
+    rng = np.random.default_rng(N * 7 + K + M)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.1, 30)).astype(np.float32)
+    mag = (1 + 0.2 * rng.standard_normal(N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    words, scale, t, _ = port.pack_weights(w)
+    y, q, sc, acc = port.linear_forward(x, words, scale, N, rms_input=rms, magnitude=mag, bias=bias)
+    fy, fq, fsc, facc = fast.linear_forward(x, t, scale, rms_input=rms, magnitude=mag, bias=bias)
+    assert np.array_equal(fq, q) and bits_equal(fsc, sc) and np.array_equal(facc, acc)
+    assert bits_equal(fy, y)
+    # worst case for exactness: every product at its extreme
+    qx = np.full((2, K), 127, np.int8)
+    tx = np.ones((3, K), np.int8)
+    assert np.array_equal(fast.acc_exact(qx, tx), np.full((2, 3), 127 * K, np.int32))
+
+
+def test_fast_moe_matches_port(port):
+    from oracle import fast
+    g = load_golden([p for p in golden_cases() if "moe_" in p][0])
+    E, H, D = g["up"].shape
+    up_t, dn_t, us, ds = [], [], [], []
+    for e in range(E):
+        _, s, t, _ = port.pack_weights(g["up"][e]); up_t.append(t); us.append(s)
+        _, s, t, _ = port.pack_weights(g["down"][e]); dn_t.append(t); ds.append(s)
+    out = fast.moe_forward(g["x"], g["routing"], up_t, us, dn_t, ds, rms_input=1)
+    assert bits_equal(out, g["out"]), f"max abs diff {np.abs(out - g['out']).max()}"

@@ -29,27 +29,37 @@ def test_noalloc_matches_workspace_entry_point_on_consecutive_calls(cuda, port, 
     import gpu_helpers as H
     torch = cuda
     rng = np.random.default_rng(123)
-    # two back-to-back calls per shape with different inputs share the same fixed scratch; the shapes
-    # visit the strip GEMV, the canonical-words GEMV, the generic kernel and the tcgen05 GEMM
-    for (M, K, N, use_strips, use_i8) in [(1, 1024, 300, True, False), (8, 768, 96, True, False),
-                                          (3, 256, 64, False, False), (5, 48, 17, False, False),
-                                          (130, 256, 160, False, True)]:
-        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
-        words, scale, *_ = port.pack_weights(w)
-        dwords = H.words_dev(words)
-        strips = H.relayout_strips(dwords, N, K) if use_strips else None
-        w_i8 = H.expand_i8(dwords, N, K) if use_i8 else None
-        mag = H.dev((1 + 0.1 * rng.standard_normal(N)).astype(np.float32))
-        bias = H.dev(rng.standard_normal(N).astype(np.float32))
-        for call in range(2):
-            x = H.dev((rng.standard_normal((M, K)) * (1 + call)).astype(np.float32))
-            want = H.linear_forward(x, dwords, scale, N, w_i8=w_i8, rms_mode=1, magnitude=mag, bias=bias, strips=strips)
-            got = _noalloc(tbl, H, torch, x, dwords, strips, w_i8, scale, N, rms_mode=1, magnitude=mag, bias=bias)
-            # same kernels, same inputs: the tolerance of this suite for integer-exact paths is zero
-            assert torch.equal(got, want), f"M={M} K={K} N={N} call {call}: max diff {(got - want).abs().max().item()}"
-            oy, *_ = port.linear_forward(x.cpu().numpy(), words, scale, N, rms_input=0,
-                                         magnitude=mag.cpu().numpy(), bias=bias.cpu().numpy())
-            assert got.shape == oy.shape
+    # Two back-to-back calls per shape, with different inputs, share the same fixed scratch.  The shapes visit
+    # every kernel family and every part of the scratch: the fused strip GEMV (no scratch), strips with more
+    # rows than the fused prologue takes (interleaved codes + row sums), strips serving more than one 64-row
+    # tile, the canonical-words GEMV, the generic kernel and the tcgen05 GEMM (row-major codes); a large shape
+    # is followed by a small one so that stale contents of the array would show.
+    shapes = [(1, 1024, 300, True, False), (8, 768, 96, True, False), (24, 1024, 300, True, False),
+              (70, 768, 96, True, False), (3, 256, 64, False, False), (5, 48, 17, False, False),
+              (130, 256, 160, False, True), (64, 16384, 48, True, False), (2, 256, 64, True, False)]
+    for rms_mode in (1, 2):
+        for (M, K, N, use_strips, use_i8) in shapes:
+            w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+            words, scale, *_ = port.pack_weights(w)
+            dwords = H.words_dev(words)
+            strips = H.relayout_strips(dwords, N, K) if use_strips else None
+            w_i8 = H.expand_i8(dwords, N, K) if use_i8 else None
+            mag_h = (1 + 0.1 * rng.standard_normal(N)).astype(np.float32)
+            bias_h = rng.standard_normal(N).astype(np.float32)
+            mag, bias = H.dev(mag_h), H.dev(bias_h)
+            for call in range(2):
+                x_h = (rng.standard_normal((M, K)) * (1 + call)).astype(np.float32)
+                x = H.dev(x_h)
+                want = H.linear_forward(x, dwords, scale, N, w_i8=w_i8, rms_mode=rms_mode, magnitude=mag, bias=bias,
+                                        strips=strips)
+                got = _noalloc(tbl, H, torch, x, dwords, strips, w_i8, scale, N, rms_mode=rms_mode, magnitude=mag,
+                               bias=bias)
+                # same kernels, same inputs: the tolerance of this suite for integer-exact paths is zero
+                assert torch.equal(got, want), f"M={M} K={K} N={N} call {call}: max diff {(got - want).abs().max().item()}"
+                if rms_mode == 2 and M * K * N <= 1 << 27:
+                    # with the reference's summation order in the input norm the CPU oracle must agree too
+                    oy, *_ = port.linear_forward(x_h, words, scale, N, rms_input=1, magnitude=mag_h, bias=bias_h)
+                    assert np.array_equal(got.cpu().numpy().view(np.uint32), oy.view(np.uint32))
     assert H.device_status() == 0
 
 
@@ -67,6 +77,5 @@ def test_noalloc_rejects_shapes_beyond_the_fixed_scratch(cuda, tbl):
     assert rc == -7, rc  # TBL_ERR_WORKSPACE
     assert b"workspace" in tbl.tbl_status_string(rc)
     assert tbl.tbl_launch_count() == before  # nothing was launched
-    # the largest shape that still fits is accepted
-    M2 = 64
-    assert tbl.tbl_linear_workspace_bytes(M2, 16384, 32) <= NOALLOC_SCRATCH_BYTES
+    # the largest shape that still fits is accepted (the call itself is made in the test above)
+    assert tbl.tbl_linear_workspace_bytes(64, 16384, 48) <= NOALLOC_SCRATCH_BYTES
