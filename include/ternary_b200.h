@@ -233,6 +233,32 @@ int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, cons
                              float* output_dev, long long output_stride, int rms_mode, void* workspace_dev,
                              size_t workspace_bytes, void* stream);
 
+/* ---- a stack of linears in one launch --------------------------------------------------------- */
+
+#define TBL_MAX_CHAIN 16
+
+/* Bytes of scratch for tbl_chain_forward (activations between the layers, the barrier words of the persistent
+ * kernel and, for shapes that take the layer-by-layer route, one layer's quantiser scratch). */
+size_t tbl_chain_workspace_bytes(const tbl_linear_view* views_host, int count, int rows);
+
+/* y = L[count-1]( ... L[1]( L[0](x) ) ): `count` <= TBL_MAX_CHAIN ternary linears applied one after the other to
+ * x fp32 [rows, views[0].inputs]; views[i].inputs must equal views[i-1].outputs.  Layer i is exactly one
+ * tbl_linear_forward (input RMSNorm when views[i].rms_input, quantiser, ternary GEMV, magnitude, bias) followed,
+ * when squared_relu_host != NULL and squared_relu_host[i] != 0, by max(y,0)^2.  y_dev is fp32 [rows, last outputs].
+ * With rows <= 8, every view carrying `strips`, inputs % 256 == 0 and rows*inputs <= 16384, the whole stack runs
+ * as ONE persistent cooperative kernel: a CTA per SM streams the weights of all layers back to back while the
+ * grid meets at a bounded barrier between layers (the weight stream never stops at a layer boundary).  Other
+ * shapes run layer by layer through tbl_linear_forward.  rms_mode as in tbl_linear_forward (used by the layers
+ * whose view has rms_input set; TBL_RMS_NONE there selects TBL_RMS_FAST).
+ * Replaces: a run of BitLinear::forward calls whose only glue is an optional squared ReLU -- the block FFN
+ * ffn_gate_up -> squared_relu -> ffn_down (OXN/nsos/src/jamba.cpp:3286-3367), an expert's
+ * expert_gate_up -> squared_relu -> expert_down (OXN/nsos/src/jamba.cpp:3938-3941), and the fixed launch
+ * sequence the reference replays from a captured graph (JambaModel::forward_ids_decode_graph,
+ * OXN/nsos/src/jamba.cpp:2074-2376). */
+int tbl_chain_forward(const tbl_linear_view* views_host, int count, const int* squared_relu_host,
+                      const float* x_dev, int rows, int rms_mode, float* y_dev, void* workspace_dev,
+                      size_t workspace_bytes, void* stream);
+
 /* Router post-processing on the device: logits fp32 [rows, experts] (the gate's output) -> routing weights
  * [rows, experts] as tbl_moe_forward takes them: softmax, keep the top_k largest per row (ties -> lower
  * index), renormalise, zero the rest; top_k == 0 or >= experts leaves the softmax.  May run in place.
@@ -336,6 +362,14 @@ int tbl_device_status(void* stream);
  * Replaces: the per-kernel timing the reference's benchmarks take around launch_bitnet_gemv_scaled
  * (OXN/nsos/benchmarks/bench_decode_gemv.cpp:75-90). */
 void tbl_set_kernel_events(void* start_event, void* stop_event);
+
+/* Profiling aid for tbl_chain_forward's persistent kernel: while a device buffer of at least
+ * CTAs * count * 8 * sizeof(uint64_t) bytes is set (CTAs = SM count of the device), each CTA records, per layer,
+ * globaltimer nanosecond stamps: [0] layer entered, [1] grid barrier passed, [2] input quantised, [3] first
+ * weight stage landed, [4] last stage consumed, [5] outputs stored, [6] arrived on the layer's counter,
+ * [7] producer warp finished issuing the layer's copies.  Pass NULL to switch it off.  Process-wide.
+ * Replaces: the per-layer timing the reference prints with NSOS_LAYER_TIMING=1 (OXN/nsos/src/jamba.cpp:902-963). */
+void tbl_set_chain_trace(void* buffer_dev, size_t bytes);
 
 /* Number of kernels this library has launched in this process (all streams). */
 uint64_t tbl_launch_count(void);

@@ -75,6 +75,9 @@ _SIGNATURES = {
     "tbl_grouped_rows_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "tbl_grouped_forward_rows": (C.c_int, [C.POINTER(LinearView), C.c_int, _vp, C.c_int, _vp, C.c_longlong, C.c_int,
                                            _vp, C.c_size_t, _vp]),
+    "tbl_chain_workspace_bytes": (C.c_size_t, [C.POINTER(LinearView), C.c_int, C.c_int]),
+    "tbl_chain_forward": (C.c_int, [C.POINTER(LinearView), C.c_int, C.POINTER(C.c_int), _vp, C.c_int, C.c_int, _vp, _vp,
+                                    C.c_size_t, _vp]),
     "tbl_router_topk": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "tbl_row_norm": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_float, _vp, C.c_int, _vp, _vp, _vp, _vp]),
     "tbl_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -87,6 +90,7 @@ _SIGNATURES = {
     "tbl_sha256_hex": (None, [_vp, C.c_size_t, C.c_char_p]),
     "tbl_device_status": (C.c_int, [_vp]),
     "tbl_set_kernel_events": (None, [_vp, _vp]),
+    "tbl_set_chain_trace": (None, [_vp, C.c_size_t]),
     "tbl_launch_count": (C.c_uint64, []),
 }
 

@@ -104,13 +104,15 @@ const char* tbl_status_string(int status) {
     }
 }
 
-int tbl_abi_version(void) { return 2; }
+int tbl_abi_version(void) { return 3; }
 
 uint64_t tbl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 void tbl_set_kernel_events(void* start_event, void* stop_event) {
     set_gemv_events(static_cast<cudaEvent_t>(start_event), static_cast<cudaEvent_t>(stop_event));
 }
+
+void tbl_set_chain_trace(void* buffer_dev, size_t bytes) { set_chain_trace(buffer_dev, bytes); }
 
 int tbl_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
@@ -359,6 +361,25 @@ bool all_have_strips(const tbl_linear_view* views, int count) {
     return gemv_strip_supported(views[0].inputs);
 }
 
+// The persistent route serves a stack when every layer has strips and the kernel's shape rules hold.
+bool chain_layers(const tbl_linear_view* views, int count, const int* squared_relu, int rows, int rms_mode,
+                  ChainLayer* out) {
+    if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
+        for (int i = 0; i < count; ++i) if (views[i].rms_input) return false;
+    }
+    for (int i = 0; i < count; ++i) {
+        if (!views[i].strips || !aligned16(views[i].strips)) return false;
+        out[i] = ChainLayer{static_cast<const uint8_t*>(views[i].strips), views[i].magnitude, views[i].bias,
+                            views[i].weight_scale, qmax_for_bits(views[i].activation_bits), views[i].outputs,
+                            views[i].inputs, views[i].rms_input ? 1 : 0, squared_relu && squared_relu[i] ? 1 : 0};
+    }
+    return gemv_chain_supported(out, count, rows);
+}
+size_t chain_act_bytes(const tbl_linear_view* views, int count, int rows) {
+    size_t width = 0;
+    for (int i = 0; i + 1 < count; ++i) width = static_cast<size_t>(views[i].outputs) > width ? views[i].outputs : width;
+    return round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
+}
 }  // namespace
 
 extern "C" {
@@ -442,6 +463,57 @@ int tbl_grouped_forward(const tbl_linear_view* views_host, int groups, const flo
                         size_t workspace_bytes, void* stream) {
     return tbl_grouped_forward_rows(views_host, groups, input_dev, 1, output_dev, output_stride, rms_mode,
                                     workspace_dev, workspace_bytes, stream);
+}
+
+size_t tbl_chain_workspace_bytes(const tbl_linear_view* views_host, int count, int rows) {
+    if (!views_host || count <= 0 || count > TBL_MAX_CHAIN || rows <= 0) return 0;
+    size_t lin = 0;
+    for (int i = 0; i < count; ++i) {
+        const size_t b = tbl_linear_workspace_bytes(rows, views_host[i].inputs, views_host[i].outputs);
+        lin = b > lin ? b : lin;
+    }
+    return 1024 + 2 * chain_act_bytes(views_host, count, rows) + lin;
+}
+
+int tbl_chain_forward(const tbl_linear_view* views_host, int count, const int* squared_relu_host,
+                      const float* x_dev, int rows, int rms_mode, float* y_dev, void* workspace_dev,
+                      size_t workspace_bytes, void* stream) {
+    if (!views_host || !x_dev || !y_dev || count <= 0 || count > TBL_MAX_CHAIN || rows <= 0) return TBL_ERR_INVALID_ARG;
+    if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
+    for (int i = 0; i < count; ++i) {
+        const int rc = check_view(views_host[i]);
+        if (rc != TBL_OK) return rc;
+        if (static_cast<int64_t>(rows) * views_host[i].outputs > INT_MAX) return TBL_ERR_SHAPE;
+        if (i > 0 && views_host[i].inputs != views_host[i - 1].outputs) return TBL_ERR_SHAPE;
+    }
+    if (!workspace_dev || workspace_bytes < tbl_chain_workspace_bytes(views_host, count, rows)) return TBL_ERR_WORKSPACE;
+    if (!aligned16(workspace_dev) || !aligned16(x_dev) || !aligned16(y_dev)) return TBL_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ChainLayer layers[TBL_MAX_CHAIN];
+    if (chain_layers(views_host, count, squared_relu_host, rows, rms_mode, layers))
+        return cuda_status(launch_gemv_chain(layers, count, rows, x_dev, y_dev, workspace_dev, st));
+    // layer by layer: same arithmetic, one tbl_linear_forward per layer, activations ping-pong in the workspace
+    uint8_t* ws = static_cast<uint8_t*>(workspace_dev);
+    const size_t act = chain_act_bytes(views_host, count, rows);
+    float* bufs[2] = {reinterpret_cast<float*>(ws + 1024), reinterpret_cast<float*>(ws + 1024 + act)};
+    void* lin_ws = ws + 1024 + 2 * act;
+    const size_t lin_bytes = workspace_bytes - (1024 + 2 * act);
+    const float* in = x_dev;
+    for (int i = 0; i < count; ++i) {
+        const tbl_linear_view& v = views_host[i];
+        float* out = i == count - 1 ? y_dev : bufs[i & 1];
+        const int mode = v.rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
+        const int rc = tbl_linear_forward(in, v.packed, v.strips, rows > 64 ? v.w_i8 : nullptr, v.weight_scale, rows,
+                                          v.inputs, v.outputs, v.activation_bits, mode, v.magnitude, v.bias, out,
+                                          lin_ws, lin_bytes, stream);
+        if (rc != TBL_OK) return rc;
+        if (squared_relu_host && squared_relu_host[i]) {
+            const cudaError_t e = launch_squared_relu(out, static_cast<int64_t>(rows) * v.outputs, st);
+            if (e != cudaSuccess) return TBL_ERR_CUDA;
+        }
+        in = out;
+    }
+    return TBL_OK;
 }
 
 int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, float* weights_dev, void* stream) {

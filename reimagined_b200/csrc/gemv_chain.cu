@@ -1,0 +1,630 @@
+// A stack of ternary linears in ONE persistent launch: y = L_{n-1}( ... L_1( L_0(x) ) ), few activation rows
+// (decode).  Each layer is [RMSNorm] -> per-token absmax quantiser -> 2-bit ternary GEMV -> two-scale epilogue
+// [-> squared ReLU], exactly as the single-layer strip GEMV computes it.
+//
+// Why one launch: a decode GEMV over 64 MiB of weights lasts about as long as the DRAM pipeline needs to ramp
+// up and drain, so a chain of separate launches never reaches the streaming rate.  Here one CTA per SM stays
+// resident for the whole stack.  Its producer warp depends on nothing but the weights, so it keeps the ring of
+// shared-memory stages full across layer boundaries: while the consumer warps of the grid finish layer l, meet
+// at a grid-wide barrier and quantise the new activation row, the first stages of layer l+1 are already
+// landing.  The weight stream of the whole stack is one uninterrupted front-to-back sweep of HBM.
+//
+// Layer boundary (consumer warps only): epilogue writes y_l to global memory and publishes max|y_l| per row
+// with one atomicMax per CTA (max is exact in any order, so the next quantiser's scale is bit-identical to a
+// separate absmax pass) -> arrive on the layer's counter -> bounded spin until all CTAs have arrived -> load
+// the row (L2-resident), quantise it straight into shared memory.  The grid must be co-resident: the kernel is
+// launched cooperatively.  Every wait is bounded; a wait that gives up sets TBL_DEV_WAIT_TIMEOUT and the CTA
+// leaves.
+//
+// Weight layout, stage layout, widening and the MMA are those of gemv_strip.cu (strips of 16 rows, 1 KB
+// blocks, slab-major order, mma.sync.m16n8k32.u8.s8 with the weights as the A operand).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+namespace {
+
+constexpr int kMaxStages = 8;
+constexpr int kSlots = 8;                  // strips a CTA works on concurrently
+constexpr int kWps = 2;                    // warps per strip
+constexpr int kConsumers = kSlots * kWps;  // 16 consumer warps + 1 producer warp
+constexpr int kT = kConsumers * 32;
+constexpr int kMaxRows = 8;
+constexpr int kGroups = 16384 / 16 / kT;   // 16-element groups per thread in the quantiser
+constexpr int kReduceBytes = kSlots * (kWps - 1) * 32 * 4 * 4;
+constexpr int kStateBytes = 1024;
+constexpr uint32_t kGridSpinLimit = 1u << 21;
+
+struct ChainParams {
+    ChainLayer layer[TBL_MAX_CHAIN];
+    int count, rows;
+    const float* x;        // [rows, K_0]
+    float* y;              // [rows, N_last]
+    float* act[2];         // ping-pong activations between layers, [rows, width]
+    unsigned* arrived;     // [count] arrival counters, zero at launch
+    unsigned* amax;        // [count + 1][8] row absmax bit patterns of each layer's input, zero at launch
+    int ks, stage_shift, stages, slots_max, acts_bytes;
+    int* status;
+    unsigned long long* trace;   // profiling aid: [cta][layer][8] nanosecond stamps, or null
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory"); }
+
+// Per-token absmax quantiser of rows*K <= 16384 inputs into the resident interleaved shared-memory copy.
+// Same arithmetic as the stand-alone quantiser.  known_amax != nullptr: the row maxima were published by the
+// producer of x (bit patterns), so the absmax reduction is skipped.
+__device__ __forceinline__ void quantise_resident(const float* __restrict__ x, const int R, const int K,
+                                                  const bool rms_fast, const float q_max,
+                                                  const unsigned* known_amax, const bool first_layer,
+                                                  uint8_t* acts_resident, float* s_scale, int* s_qsum, float* s_red,
+                                                  uint32_t* s_amax) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_groups = R * K / 16;
+    if (threadIdx.x < kMaxRows) {
+        s_qsum[threadIdx.x] = 0;
+        s_amax[threadIdx.x] = 0u;
+    }
+    float4 xv[kGroups][4];
+    int grow[kGroups];
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) {
+        const int Gl = threadIdx.x + i * kT;
+        grow[i] = -1;
+        if (Gl < total_groups) {
+            const int e = Gl * 16;
+            int row = 0;
+#pragma unroll
+            for (int m = 1; m < kMaxRows; ++m) row += e >= m * K ? 1 : 0;
+            grow[i] = row;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = __ldcg(reinterpret_cast<const float4*>(x + e + 4 * q4));
+        } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    // first layer only: the producer warp starts queueing weight copies once these loads are in flight
+    if (first_layer) asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
+    unsigned pub[kMaxRows];
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) pub[m] = (known_amax && m < R) ? __ldcg(known_amax + m) : 0u;
+    bar_consumers();     // s_qsum / s_amax cleared
+    float inv[kMaxRows];
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) inv[m] = 1.0f;
+    if (rms_fast) {
+        float ss[kMaxRows];
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) ss[m] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kGroups; ++i) {
+            float q = 0.0f;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                q += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
+#pragma unroll
+            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) ss[m] += q;
+        }
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) {
+            if (m < R) {
+#pragma unroll
+                for (int o = 16; o; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+                if (lane == 0) s_red[warp * kMaxRows + m] = ss[m];
+            }
+        }
+        bar_consumers();
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) {
+            if (m < R) {
+                float r = s_red[m];
+                for (int w = 1; w < kConsumers; ++w) r += s_red[w * kMaxRows + m];
+                inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(r, static_cast<float>(K)), 1e-6f)));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kGroups; ++i) {
+            float f = 1.0f;
+#pragma unroll
+            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) f = inv[m];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                xv[i][q4].x = __fmul_rn(xv[i][q4].x, f); xv[i][q4].y = __fmul_rn(xv[i][q4].y, f);
+                xv[i][q4].z = __fmul_rn(xv[i][q4].z, f); xv[i][q4].w = __fmul_rn(xv[i][q4].w, f);
+            }
+        }
+    }
+    float amax[kMaxRows];
+    if (known_amax) {
+        // max_k fl(|x_k| * inv) == fl(max_k |x_k| * inv): rounding is monotone
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) amax[m] = __fmul_rn(__uint_as_float(pub[m]), inv[m]);
+    } else {
+        float mx[kMaxRows];
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) mx[m] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kGroups; ++i) {
+            float q = 0.0f;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                q = fmaxf(q, fmaxf(fmaxf(fabsf(xv[i][q4].x), fabsf(xv[i][q4].y)), fmaxf(fabsf(xv[i][q4].z), fabsf(xv[i][q4].w))));
+#pragma unroll
+            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) mx[m] = fmaxf(mx[m], q);
+        }
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) {
+            if (m < R) {
+                const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(mx[m]));
+                if (lane == 0 && wmax != 0u) atomicMax(&s_amax[m], wmax);
+            }
+        }
+        bar_consumers();
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) amax[m] = m < R ? __uint_as_float(s_amax[m]) : 0.0f;
+    }
+    int qsum[kMaxRows];
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) qsum[m] = 0;
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) {
+        if (grow[i] >= 0) {
+            const int m = grow[i];
+            float am = 0.0f;
+#pragma unroll
+            for (int r = 0; r < kMaxRows; ++r) if (m == r) am = amax[r];
+            const float scale = __fdiv_rn(q_max, __fadd_rn(am, 1e-8f));
+            uint32_t wds[4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const uint32_t c0 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].x, scale), 12582912.0f));
+                const uint32_t c1 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].y, scale), 12582912.0f));
+                const uint32_t c2 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].z, scale), 12582912.0f));
+                const uint32_t c3 = __float_as_uint(__fadd_rn(__fmul_rn(xv[i][q4].w, scale), 12582912.0f));
+                wds[q4] = __byte_perm(__byte_perm(c0, c1, 0x0040), __byte_perm(c2, c3, 0x0040), 0x5410);
+                const int s4 = dp4a_ss(static_cast<int>(wds[q4]), 0x01010101, 0);
+#pragma unroll
+                for (int r = 0; r < kMaxRows; ++r) if (m == r) qsum[r] += s4;
+            }
+            const int e = (threadIdx.x + i * kT) * 16;
+            const uint4 codes = transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
+            *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) = codes;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < kMaxRows; ++m) {
+        if (m < R) {
+            const int wsum = __reduce_add_sync(0xffffffffu, qsum[m]);
+            if (lane == 0 && wsum != 0) atomicAdd(&s_qsum[m], wsum);
+        }
+    }
+    if (static_cast<int>(threadIdx.x) < R) {
+        float am = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) if (static_cast<int>(threadIdx.x) == r) am = amax[r];
+        s_scale[threadIdx.x] = __fdiv_rn(__fadd_rn(am, 1e-8f), q_max);
+    }
+    bar_consumers();
+}
+
+__global__ void __launch_bounds__((kConsumers + 1) * 32, 1)
+gemv_chain_kernel(const __grid_constant__ ChainParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk_stage = P.ks >> 8;
+    const int stage_bytes = P.slots_max * nblk_stage * 1024;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kMaxStages;
+    int* reduce_buf = reinterpret_cast<int*>(smem + 128);
+    float* s_scale = reinterpret_cast<float*>(smem + 128 + kReduceBytes);
+    int* s_qsum = reinterpret_cast<int*>(s_scale + 8);
+    float* s_red = s_scale + 16;
+    uint32_t* s_amax = reinterpret_cast<uint32_t*>(s_red + kConsumers * kMaxRows);
+    uint32_t* s_outmax = s_amax + 8;
+    int* s_ok = reinterpret_cast<int*>(s_outmax + 8);
+    uint8_t* acts_resident = smem + 128 + kReduceBytes + kStateBytes;
+    uint8_t* stage_base = acts_resident + P.acts_bytes;
+    const uint32_t stage_base_addr = smem_u32(stage_base);
+    const uint32_t acts_resident_addr = smem_u32(acts_resident);
+    const int nstages = P.stages;
+    const int G = static_cast<int>(gridDim.x), bid = static_cast<int>(blockIdx.x);
+    const int R = P.rows;
+    auto stamp = [&](int l, int slot_id) {
+        if (P.trace) P.trace[(static_cast<size_t>(bid) * P.count + l) * 8 + slot_id] = global_ns();
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumers);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (threadIdx.x < 8) s_outmax[threadIdx.x] = 0u;
+    if (threadIdx.x == 0) *s_ok = 1;
+    __syncthreads();
+
+    const bool producer = warp == kConsumers;
+    const int slot = warp / kWps, part = warp % kWps;
+    const int g = lane >> 2, t = lane & 3;
+    int aoff[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) aoff[x] = g * 256 + ((((x ^ (g & 1)) << 2) + t) << 4);
+
+    // the producer holds its first copies back until the consumers' loads of x are in flight
+    if (producer) asm volatile("bar.sync 11, %0;" ::"r"(kT + 32) : "memory");
+
+    int it = 0;
+    bool alive = true;
+    for (int l = 0; l < P.count && alive; ++l) {
+        const ChainLayer& L = P.layer[l];
+        const int K = L.K, N = L.N;
+        const int nstrips = (N + 15) >> 4;
+        const int share_base = nstrips / G, share_rem = nstrips % G;
+        const int s_begin = bid * share_base + min(bid, share_rem);
+        const int s_end = s_begin + share_base + (bid < share_rem ? 1 : 0);
+        const int share = share_base + (share_rem ? 1 : 0);                 // largest share of any CTA
+        const int passes = (share + kSlots - 1) / kSlots;
+        const int slots = passes ? (share + passes - 1) / passes : 1;
+        const int nblk = K >> 8;
+        const int ksteps = (nblk + nblk_stage - 1) >> P.stage_shift;
+        const bool fast = R == 1 && nblk_stage == 8 && (K & 2047) == 0;
+
+        if (producer) {
+            for (int s = s_begin; s < s_end && alive;) {
+                const int cnt = min(slots, s_end - s);
+                const int local = s;
+                s += cnt;
+                for (int ksi = 0; ksi < ksteps; ++ksi, ++it) {
+                    const int st = it % nstages;
+                    if (it >= nstages) {
+                        alive = mbar_wait_bounded(&empty[st], ((it / nstages) - 1) & 1, P.status);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                    }
+                    const int b0 = ksi * nblk_stage;
+                    const int nb = min(nblk_stage, nblk - b0);
+                    uint8_t* wst = stage_base + static_cast<size_t>(st) * stage_bytes;
+                    if (lane == 0) mbar_arrive_expect_tx(&full[st], static_cast<uint32_t>(cnt) * nb * 1024);
+                    __syncwarp();
+                    // the stage is one or two slabs of cnt adjacent strips: one contiguous copy per slab,
+                    // laid out [slab][strip][block in slab]
+                    const int slab = b0 >> 2;
+                    if (lane < ((nb + 3) >> 2)) {
+                        const int sl = slab + lane;
+                        const int sbs = min(4, nblk - 4 * sl);
+                        bulk_g2s(wst + lane * cnt * 4096,
+                                 L.strips + ((static_cast<size_t>(4) * sl * nstrips + static_cast<size_t>(local) * sbs) << 10),
+                                 cnt * sbs * 1024, &full[st]);
+                    }
+                }
+            }
+            if (lane == 0) stamp(l, 7);
+            continue;
+        }
+
+        // ---------------- consumer warps ----------------
+        const float* xin = l == 0 ? P.x : P.act[(l - 1) & 1];
+        float* yout = l == P.count - 1 ? P.y : P.act[l & 1];
+        const bool has_work = s_begin < s_end;
+        if (threadIdx.x == 0) stamp(l, 0);
+        if (l > 0 && has_work) {
+            // every CTA has written its part of the previous layer's output
+            if (threadIdx.x == 0) {
+                bool ok = false;
+                for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+                    if (ld_acquire_gpu(P.arrived + (l - 1)) >= static_cast<unsigned>(G)) { ok = true; break; }
+                }
+                if (!ok) { atomicOr(P.status, TBL_DEV_WAIT_TIMEOUT); *s_ok = 0; }
+            }
+            bar_consumers();
+            if (*reinterpret_cast<volatile int*>(s_ok) == 0) { alive = false; break; }
+        }
+        if (threadIdx.x == 0) stamp(l, 1);
+        if (has_work)
+            quantise_resident(xin, R, K, L.rms_fast != 0, L.q_max, l > 0 ? P.amax + l * 8 : nullptr, l == 0,
+                              acts_resident, s_scale, s_qsum, s_red, s_amax);
+        else if (l == 0)
+            asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
+        if (threadIdx.x == 0) stamp(l, 2);
+        bool first_stage = true;
+
+        for (int s = s_begin; s < s_end && alive;) {
+            const int cnt = min(slots, s_end - s);
+            const int local = s;
+            s += cnt;
+            const bool active = slot < cnt;
+            int acc[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+
+            for (int ksi = 0; ksi < ksteps; ++ksi, ++it) {
+                const int st = it % nstages;
+                alive = mbar_wait_bounded(&full[st], (it / nstages) & 1, P.status);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                if (first_stage && threadIdx.x == 0) stamp(l, 3);
+                first_stage = false;
+                if (active) {
+                    const int nb = min(nblk_stage, nblk - ksi * nblk_stage);
+                    const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
+                    if (fast) {
+                        // single row, full 2048-deep stage: blocks part, part+2 of both slabs with constant
+                        // offsets; the loads of a block are issued ahead of the MMAs of the block before it
+                        const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
+                        const uint32_t w1 = w0 + cnt * 4096;
+                        const uint32_t a0 = acts_resident_addr + t * 16 + (ksi * 8 + part) * 256;
+                        struct Operands { uint4 lo, hi, b[4]; };
+                        auto load_block = [&](const uint32_t wblk, const uint32_t ablk) {
+                            Operands o;
+                            o.lo = lds128(wblk);
+                            o.hi = lds128(wblk + 512);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + x * 64);
+                            return o;
+                        };
+                        auto mma_block = [&](const Operands& o) {
+                            const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
+                            const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
+#pragma unroll
+                            for (int xp = 0; xp < 2; ++xp) {
+                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
+                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t mk = 0x03030303u << (2 * j);
+                                    mma_u8s8(acc[j], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
+                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                }
+                            }
+                        };
+                        const Operands o0 = load_block(w0, a0);
+                        const Operands o1 = load_block(w0 + 2048, a0 + 512);
+                        mma_block(o0);
+                        const Operands o2 = load_block(w1, a0 + 1024);
+                        mma_block(o1);
+                        const Operands o3 = load_block(w1 + 2048, a0 + 1536);
+                        mma_block(o2);
+                        mma_block(o3);
+                    } else {
+                        // stage layout [slab][strip][block in slab]; this warp takes the blocks of its parity
+                        const uint32_t ast = acts_resident_addr + ksi * nblk_stage * R * 256;
+                        const uint32_t astep = kWps * R * 256;
+                        for (int sl = 0; 4 * sl < nb; ++sl) {
+                            const int sbs = min(4, nb - 4 * sl);
+                            const uint32_t wslab = stage_addr + lane * 16 + sl * cnt * 4096 + (slot * sbs + part) * 1024;
+                            uint32_t ablk = ast + (4 * sl + part) * R * 256;
+#pragma unroll
+                            for (int i = 0; i < 4 / kWps; ++i) {
+                                if (part + i * kWps < sbs) {
+                                    const uint32_t wblk = wslab + i * kWps * 1024;
+                                    const uint4 lo = lds128(wblk);
+                                    const uint4 hi = lds128(wblk + 512);
+                                    const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w};
+                                    const uint32_t hw[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                                    for (int xp = 0; xp < 2; ++xp) {
+                                        const uint4 B0 = lds128(ablk + aoff[2 * xp]);
+                                        const uint4 B1 = lds128(ablk + aoff[2 * xp + 1]);
+                                        const uint32_t b0[4] = {B0.x, B0.y, B0.z, B0.w};
+                                        const uint32_t b1[4] = {B1.x, B1.y, B1.z, B1.w};
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j) {
+                                            const uint32_t mk = 0x03030303u << (2 * j);
+                                            mma_u8s8(acc[j], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
+                                                     hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                        }
+                                    }
+                                }
+                                ablk += astep;
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
+            }
+            if (!alive) break;
+            if (threadIdx.x == 0) stamp(l, 4);
+
+            if (active) {
+                // exact recombination of the 4^j-scaled partial sums, then the two warps of a strip meet
+                int tot[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tot[e] = acc[0][e] + (acc[1][e] >> 2) + (acc[2][e] >> 4) + (acc[3][e] >> 6);
+                int* mine = reduce_buf + (slot * 32 + lane) * 4;
+                if (part > 0) *reinterpret_cast<int4*>(mine) = make_int4(tot[0], tot[1], tot[2], tot[3]);
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * kWps) : "memory");
+                if (part == 0) {
+                    const int4 v = *reinterpret_cast<const int4*>(mine);
+                    tot[0] += v.x; tot[1] += v.y; tot[2] += v.z; tot[3] += v.w;
+                }
+                // the buffer is reused by the next pass: the reader must be done before the writer returns
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * kWps) : "memory");
+                if (part == 0) {
+                    float omax[2] = {0.0f, 0.0f};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int n = (local + slot) * 16 + g + 8 * h;
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int m = 2 * t + c;
+                            if (n < N && m < R) {
+                                const int total = tot[2 * h + c] - s_qsum[m];
+                                float v = epilogue(total, __fmul_rn(s_scale[m], L.weight_scale), L.magnitude, L.bias, n);
+                                if (L.squared_relu) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
+                                yout[static_cast<size_t>(m) * N + n] = v;
+                                omax[c] = fmaxf(omax[c], fabsf(v));
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t u = __float_as_uint(omax[c]);
+                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 4));
+                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 8));
+                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 16));
+                        if (g == 0 && 2 * t + c < R && u != 0u) atomicMax(&s_outmax[2 * t + c], u);
+                    }
+                }
+            }
+        }
+        if (!alive) break;
+
+        // layer boundary: all consumer warps of this CTA have stored their outputs -> publish the row maxima
+        // and arrive on the layer's counter
+        if (threadIdx.x == 0) stamp(l, 5);
+        bar_consumers();
+        if (threadIdx.x == 0) {
+            stamp(l, 6);
+            if (l + 1 < P.count) {
+                for (int m = 0; m < R; ++m) {
+                    const uint32_t u = s_outmax[m];
+                    if (u != 0u) atomicMax(P.amax + (l + 1) * 8 + m, u);
+                    s_outmax[m] = 0u;
+                }
+                __threadfence();
+                atomicAdd(P.arrived + l, 1u);
+            }
+        }
+    }
+}
+
+struct DeviceInfo {
+    bool known;
+    int sms;
+    int cooperative;
+};
+
+DeviceInfo device_info() {
+    static DeviceInfo info[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DeviceInfo{false, 0, 0};
+    if (!info[dev].known) {
+        int sms = 0, coop = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DeviceInfo{false, 0, 0};
+        if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess) return DeviceInfo{false, 0, 0};
+        if (cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return DeviceInfo{false, 0, 0};
+        info[dev] = DeviceInfo{true, sms, coop};
+    }
+    return info[dev];
+}
+
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+unsigned long long* g_chain_trace = nullptr;
+size_t g_chain_trace_bytes = 0;
+
+}  // namespace
+
+void set_chain_trace(void* buffer, size_t bytes) {
+    g_chain_trace = static_cast<unsigned long long*>(buffer);
+    g_chain_trace_bytes = buffer ? bytes : 0;
+}
+
+bool gemv_chain_supported(const ChainLayer* layers, int count, int rows) {
+    if (!layers || count < 1 || count > TBL_MAX_CHAIN || rows < 1 || rows > kMaxRows) return false;
+    for (int l = 0; l < count; ++l) {
+        if (!layers[l].strips || !gemv_strip_supported(layers[l].K) || layers[l].N < 1) return false;
+        if (static_cast<long long>(rows) * layers[l].K > 16384) return false;
+        if (l > 0 && layers[l].K != layers[l - 1].N) return false;
+    }
+    return true;
+}
+
+size_t gemv_chain_workspace_bytes(const ChainLayer* layers, int count, int rows) {
+    size_t width = 0;
+    for (int l = 0; l + 1 < count; ++l) width = layers[l].N > static_cast<int>(width) ? layers[l].N : width;
+    return 1024 + 2 * round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
+}
+
+cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, const float* x, float* y,
+                              void* workspace, cudaStream_t stream) {
+    if (!gemv_chain_supported(layers, count, rows)) return cudaErrorInvalidValue;
+    const DeviceInfo info = device_info();
+    if (!info.known || !info.cooperative || info.sms < 1) return cudaErrorNotSupported;
+    ChainParams P{};
+    P.count = count;
+    P.rows = rows;
+    P.x = x;
+    P.y = y;
+    P.status = device_status_ptr();
+    if (!P.status) return cudaErrorUnknown;
+    int max_k = 0, max_strips = 0;
+    size_t width = 0;
+    for (int l = 0; l < count; ++l) {
+        P.layer[l] = layers[l];
+        max_k = layers[l].K > max_k ? layers[l].K : max_k;
+        const int ns = (layers[l].N + 15) / 16;
+        max_strips = ns > max_strips ? ns : max_strips;
+        if (l + 1 < count && static_cast<size_t>(layers[l].N) > width) width = layers[l].N;
+    }
+    const int grid = max_strips < info.sms ? max_strips : info.sms;
+    P.trace = g_chain_trace_bytes >= static_cast<size_t>(grid) * count * 8 * sizeof(unsigned long long) ? g_chain_trace : nullptr;
+    // one ring geometry for the whole stack: the deepest stage and the widest pass of any layer
+    P.ks = max_k >= 2048 ? 2048 : 1024;
+    P.stage_shift = P.ks == 2048 ? 3 : 2;
+    P.slots_max = 1;
+    for (int l = 0; l < count; ++l) {
+        const int ns = (layers[l].N + 15) / 16;
+        const int share = (ns + grid - 1) / grid;
+        const int passes = (share + kSlots - 1) / kSlots;
+        const int slots = (share + passes - 1) / passes;
+        P.slots_max = slots > P.slots_max ? slots : P.slots_max;
+    }
+    P.acts_bytes = static_cast<int>(round_up(static_cast<size_t>(rows) * max_k, 128));
+    const size_t stage_bytes = static_cast<size_t>(P.slots_max) * (P.ks / 256) * 1024;
+    // slack after the last stage: lanes of activation rows >= rows read (and ignore) stale bytes
+    const size_t fixed = 128 + kReduceBytes + kStateBytes + P.acts_bytes + 2048;
+    const size_t room = 227 * 1024 - fixed;
+    P.stages = static_cast<int>(room / stage_bytes < static_cast<size_t>(kMaxStages) ? room / stage_bytes : kMaxStages);
+    if (P.stages < 2) return cudaErrorInvalidValue;
+    const size_t smem = fixed + P.stages * stage_bytes;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    P.arrived = reinterpret_cast<unsigned*>(ws);
+    P.amax = reinterpret_cast<unsigned*>(ws + 256);
+    const size_t act_bytes = round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
+    P.act[0] = reinterpret_cast<float*>(ws + 1024);
+    P.act[1] = reinterpret_cast<float*>(ws + 1024 + act_bytes);
+    cudaError_t e = cudaMemsetAsync(ws, 0, 1024, stream);      // arrival counters and published maxima
+    if (e != cudaSuccess) return e;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((kConsumers + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1]{};
+    attrs[0].id = cudaLaunchAttributeCooperative;     // CTAs wait on one another: they must be co-resident
+    attrs[0].val.cooperative = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemv_chain_kernel, P);
+    note_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+}  // namespace tbl

@@ -320,4 +320,24 @@ cudaError_t launch_row_norm(const float* value, const float* gate, const float* 
                 : launch_one<false>(value, gate, weight, rows, dim, eps, q_max, out, q, act_scales, q_sums, stream);
 }
 
+namespace {
+// max(x,0)^2 in place (Tensor::squared_relu); the product is rounded on its own like the host form.
+__global__ void __launch_bounds__(256) squared_relu_kernel(float* __restrict__ x, int64_t n) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = fmaxf(x[i], 0.0f);
+        x[i] = __fmul_rn(v, v);
+    }
+}
+}  // namespace
+
+cudaError_t launch_squared_relu(float* x, int64_t n, cudaStream_t stream) {
+    if (n < 1) return cudaErrorInvalidValue;
+    const int64_t want = (n + 255) / 256;
+    const int grid = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+    squared_relu_kernel<<<grid, 256, 0, stream>>>(x, n);
+    note_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace tbl

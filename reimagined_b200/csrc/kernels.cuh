@@ -103,6 +103,24 @@ cudaError_t launch_relayout_strips(const uint32_t* words, int N, int K, void* st
 cudaError_t launch_gemv_strip(StripProblem* problems, int count, cudaStream_t stream);
 cudaError_t launch_permute_q(const int8_t* q, int M, int K, int8_t* qp, int32_t* q_sums, cudaStream_t stream);
 
+// gemv_chain.cu -- a stack of ternary linears (each layer's output is the next one's input) for <= 8 rows in one
+// persistent cooperative launch; layers need strip-major weights, K % 256 == 0 and rows*K <= 16384.
+struct ChainLayer {
+    const uint8_t* strips;
+    const float* magnitude;
+    const float* bias;
+    float weight_scale;
+    float q_max;
+    int N, K;
+    int rms_fast;        // input RMSNorm (parallel sum) before the quantiser
+    int squared_relu;    // max(y,0)^2 after the epilogue
+};
+bool gemv_chain_supported(const ChainLayer* layers, int count, int rows);
+size_t gemv_chain_workspace_bytes(const ChainLayer* layers, int count, int rows);
+void set_chain_trace(void* buffer, size_t bytes);
+cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, const float* x, float* y,
+                              void* workspace, cudaStream_t stream);
+
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8,
                                 float weight_scale, const float* magnitude, const float* bias,
@@ -132,6 +150,8 @@ constexpr int kRowNormMaxDim = 49152;
 cudaError_t launch_row_norm(const float* value, const float* gate, const float* weight, int rows, int dim, float eps,
                             int bits, float* out, int8_t* q, float* act_scales, int32_t* q_sums,
                             cudaStream_t stream);
+// max(x,0)^2 in place over n floats (OXN/nsos/src/tensor.cpp:3209-3226).
+cudaError_t launch_squared_relu(float* x, int64_t n, cudaStream_t stream);
 cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,
                              int experts, int dim, float* out, cudaStream_t stream);
 

@@ -139,3 +139,19 @@ def moe_forward(views, routing, x, hidden_dim, max_routes, rms_mode=2, tie_mode=
     capi.check(L.tbl_moe_forward(arr, ptr(routing), ptr(x), rows, dim, hidden_dim, E, max_routes, rms_mode,
                                  tie_mode, ptr(out), ptr(ws), nbytes, stream_ptr()), "tbl_moe_forward")
     return out
+
+
+def chain_forward(views, x, squared_relu=None, rms_mode=0):
+    """x [rows, views[0].inputs] through the stack of linears; returns [rows, views[-1].outputs]."""
+    L = capi.lib()
+    n = len(views)
+    rows = x.shape[0]
+    arr = (capi.LinearView * n)(*views)
+    flags = None if squared_relu is None else (C.c_int * n)(*[int(bool(f)) for f in squared_relu])
+    y = torch.empty((rows, views[-1].outputs), dtype=torch.float32, device="cuda")
+    nbytes = L.tbl_chain_workspace_bytes(arr, n, rows)
+    assert nbytes > 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    capi.check(L.tbl_chain_forward(arr, n, flags, ptr(x), rows, rms_mode, ptr(y), ptr(ws), nbytes, stream_ptr()),
+               "tbl_chain_forward")
+    return y

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(tbl):
     for n in names:
         assert hasattr(tbl, n), f"{n} declared in include/ternary_b200.h but not exported"
     assert set(names) == set(capi.EXPORTED_SYMBOLS), "capi.py bindings out of sync with the header"
-    assert tbl.tbl_abi_version() == 2
+    assert tbl.tbl_abi_version() == 3
     assert tbl.tbl_status_string(0) == b"ok"
 
 
