@@ -78,6 +78,10 @@ class _Port:
         L.tor_router_topk.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p]
         pp_u32 = C.POINTER(_u32p)
         pp_f32 = C.POINTER(_f32p)
+        L.tor_mamba_conv_step.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
+        L.tor_mamba_ssd_step.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
+        L.tor_attention_decode.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_int, _i32p, _f32p, _f32p, C.c_int, C.c_int,
+                                           C.c_int, C.c_int, C.c_int, _f32p]
         L.tor_moe_forward.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p,
                                       pp_u32, _f32p, pp_f32, pp_f32,
                                       pp_u32, _f32p, pp_f32, pp_f32,
@@ -156,6 +160,37 @@ class _Port:
         self.lib.tor_linear_forward_i8_mt(_ptr(x, _f32p), M, K, N, _ptr(t, _i8p), float(weight_scale),
                                           int(rms_input), bits, 0, None, None, _ptr(y, _f32p), threads)
         return y
+
+    # -- decode glue (all update their state arrays in place) -----------------------------
+    def mamba_conv_step(self, xv, Bv, Cv, conv_w, conv_b, ring, K):
+        """xv [R,d_inner], Bv/Cv [R,GS], ring [R,K-1,conv_dim] (updated) -> xBC [R,conv_dim]."""
+        R, d_inner = xv.shape
+        GS = Bv.shape[1]
+        xBC = np.zeros((R, d_inner + 2 * GS), np.float32)
+        self.lib.tor_mamba_conv_step(_ptr(_f32(xv), _f32p), _ptr(_f32(Bv), _f32p), _ptr(_f32(Cv), _f32p),
+                                     _ptr(_f32(conv_w), _f32p), _ptr(_f32(conv_b), _f32p), _ptr(ring, _f32p),
+                                     R, d_inner, GS, K, _ptr(xBC, _f32p))
+        return xBC
+
+    def mamba_ssd_step(self, xBC, dt, A_log, D, state, n_heads, d_head, N, n_groups):
+        """state [R,d_inner,N] (updated) -> y [R,d_inner]."""
+        R = xBC.shape[0]
+        y = np.zeros((R, n_heads * d_head), np.float32)
+        self.lib.tor_mamba_ssd_step(_ptr(_f32(xBC), _f32p), _ptr(_f32(dt), _f32p), _ptr(_f32(A_log), _f32p),
+                                    _ptr(_f32(D), _f32p), _ptr(state, _f32p), R, n_heads, d_head, N, n_groups,
+                                    _ptr(y, _f32p))
+        return y
+
+    def attention_decode(self, q, kv, k_cache, v_cache, tokens, cos_t, sin_t, n_heads, n_kv_heads, head_dim,
+                         sliding_window):
+        """caches [R,capacity,kv_dim] and tokens int32 [R] are updated -> out [R, n_heads*head_dim]."""
+        R = q.shape[0]
+        out = np.zeros((R, n_heads * head_dim), np.float32)
+        self.lib.tor_attention_decode(_ptr(_f32(q), _f32p), _ptr(_f32(kv), _f32p), _ptr(k_cache, _f32p),
+                                      _ptr(v_cache, _f32p), k_cache.shape[1], _ptr(tokens, _i32p),
+                                      _ptr(_f32(cos_t), _f32p), _ptr(_f32(sin_t), _f32p), R, n_heads, n_kv_heads,
+                                      head_dim, sliding_window, _ptr(out, _f32p))
+        return out
 
     def squared_relu(self, x):
         x = _f32(x)
@@ -315,3 +350,111 @@ def ref() -> _Ref:
     if _ref is None:
         _ref = _Ref()
     return _ref
+
+
+# ---- model-level checker: the reference's whole core library behind ref_model_shim.cpp ----------------
+MODEL_REF_SO = os.path.join(_HERE, "_ref", "libnsos_model_ref.so")
+_EMIT = C.CFUNCTYPE(None, C.c_char_p, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p)
+MODEL_CFG_FIELDS = ("num_layers", "d_model", "vocab_size", "n_heads", "n_kv_heads", "mamba_d_state", "mamba_expand",
+                    "mamba_conv_kernel", "mamba_head_dim", "mamba_n_groups", "attention_period", "attention_slot")
+
+
+class RefModel:
+    """An nsos::JambaModel of the reference (CPU, packed ternary path, streaming decode), seeded weights."""
+
+    def __init__(self, lib, cfg: dict, seed: int):
+        self.lib, self.cfg = lib, dict(cfg)
+        arr = (C.c_int * len(MODEL_CFG_FIELDS))(*[int(cfg[k]) for k in MODEL_CFG_FIELDS])
+        self.handle = lib.refm_create(arr, seed)
+        if not self.handle:
+            raise RuntimeError("reference JambaModel construction raised")
+
+    def close(self):
+        if self.handle:
+            self.lib.refm_destroy(self.handle)
+            self.handle = None
+
+    def reset(self):
+        if self.lib.refm_reset(self.handle) != 0:
+            raise RuntimeError("reset_session raised")
+
+    def step(self, token: int) -> np.ndarray:
+        """JambaModel::forward_ids_last({token}) in streaming mode: logits fp32 [vocab]."""
+        logits = np.zeros(self.cfg["vocab_size"], np.float32)
+        if self.lib.refm_step(self.handle, int(token), _ptr(logits, _f32p)) != logits.size:
+            raise RuntimeError("forward_ids_last raised")
+        return logits
+
+    def step_trace(self, token: int):
+        """The same step block by block: (hidden fp32 [layers + 1, d_model], logits)."""
+        hidden = np.zeros((self.cfg["num_layers"] + 1, self.cfg["d_model"]), np.float32)
+        logits = np.zeros(self.cfg["vocab_size"], np.float32)
+        if self.lib.refm_step_trace(self.handle, int(token), _ptr(hidden, _f32p), _ptr(logits, _f32p)) != logits.size:
+            raise RuntimeError("block-by-block step raised")
+        return hidden, logits
+
+    def export(self) -> dict:
+        """Every parameter of the decode step as named numpy arrays (see ref_model_shim.cpp::refm_export)."""
+        out = {}
+
+        def cb(name, dtype, data, count, user):
+            dt = (np.float32, np.uint32, np.int32)[dtype]
+            if count:
+                raw = C.string_at(data, count * 4)
+                out[name.decode()] = np.frombuffer(raw, dtype=dt).copy()
+            else:
+                out[name.decode()] = np.zeros(0, dt)
+
+        if self.lib.refm_export(self.handle, _EMIT(cb), None) != 0:
+            raise RuntimeError("export raised")
+        return out
+
+    def save_edge_pack(self, path: str):
+        if self.lib.refm_save_edge_pack(self.handle, path.encode()) != 0:
+            raise RuntimeError("save_edge_linear_pack raised")
+
+
+class _ModelRef:
+    def __init__(self):
+        if not os.path.exists(MODEL_REF_SO):
+            raise FileNotFoundError(MODEL_REF_SO)
+        self.lib = L = C.CDLL(MODEL_REF_SO)
+        L.refm_create.restype = C.c_void_p
+        L.refm_create.argtypes = [C.POINTER(C.c_int), C.c_uint]
+        L.refm_destroy.argtypes = [C.c_void_p]
+        L.refm_reset.argtypes = [C.c_void_p]
+        L.refm_step.argtypes = [C.c_void_p, C.c_int, _f32p]
+        L.refm_step_trace.argtypes = [C.c_void_p, C.c_int, _f32p, _f32p]
+        L.refm_export.argtypes = [C.c_void_p, _EMIT, C.c_void_p]
+        L.refm_save_edge_pack.argtypes = [C.c_void_p, C.c_char_p]
+        L.refm_router.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p]
+
+    def model(self, cfg: dict, seed: int = 1) -> RefModel:
+        return RefModel(self.lib, cfg, seed)
+
+    def router(self, x, gate_w, top_k):
+        """MoERouter::forward: (logits, routing weights), both [rows, experts]."""
+        x = _f32(x)
+        gate_w = _f32(gate_w)
+        rows, D = x.shape
+        E = gate_w.shape[0]
+        logits = np.zeros((rows, E), np.float32)
+        weights = np.zeros((rows, E), np.float32)
+        if self.lib.refm_router(_ptr(x, _f32p), rows, D, E, top_k, _ptr(gate_w, _f32p), _ptr(logits, _f32p),
+                                _ptr(weights, _f32p)) != 0:
+            raise RuntimeError("MoERouter::forward raised")
+        return logits, weights
+
+
+_model_ref = None
+
+
+def model_ref_available() -> bool:
+    return os.path.exists(MODEL_REF_SO)
+
+
+def model_ref() -> _ModelRef:
+    global _model_ref
+    if _model_ref is None:
+        _model_ref = _ModelRef()
+    return _model_ref

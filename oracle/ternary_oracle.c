@@ -336,6 +336,159 @@ void tor_row_norm(const float* value, const float* gate, const float* weight, in
     }
 }
 
+/* ---- F1: decode-step glue of the hybrid -----------------------------------------------
+ * Streaming single-token forms, restated from the reference's host branches.  Every product and
+ * sum is rounded on its own, in the reference's order (the file is compiled with contraction off,
+ * like the reference objects it is pinned against). */
+
+/* OXN/nsos/src/mamba2.cpp:727-739 (sigmoid_stable / silu_stable). */
+static float tor_silu_stable(float x) {
+    float sig;
+    if (x >= 0.0f) {
+        const float z = expf(-x);
+        sig = 1.0f / (1.0f + z);
+    } else {
+        const float z = expf(x);
+        sig = z / (1.0f + z);
+    }
+    return x * sig;
+}
+
+/* Causal depthwise conv step + SiLU over the concatenated [x | B | C] channels, then the ring shift.
+ * OXN/nsos/src/mamba2.cpp:4062-4094 (Mamba2SSD::forward_faithful_step, host branch); the device form is
+ * mamba2_faithful_conv_step_kernel, OXN/nsos/src/cuda/mamba_kernels.cu:3332-3359.
+ * ring [R][K-1][conv_dim] (oldest tap first), conv_w [conv_dim][K], xBC [R][conv_dim]. */
+void tor_mamba_conv_step(const float* xv, const float* Bv, const float* Cv, const float* conv_w,
+                         const float* conv_b, float* ring, int R, int d_inner, int GS, int K, float* xBC) {
+    const int conv_dim = d_inner + 2 * GS;
+    const int taps = K - 1 > 0 ? K - 1 : 0;
+    for (int r = 0; r < R; ++r) {
+        float* rr = ring + (int64_t)r * taps * conv_dim;
+        for (int c = 0; c < conv_dim; ++c) {
+            const float current = c < d_inner ? xv[(int64_t)r * d_inner + c]
+                                              : (c < d_inner + GS ? Bv[(int64_t)r * GS + c - d_inner]
+                                                                  : Cv[(int64_t)r * GS + c - d_inner - GS]);
+            float value = conv_b[c];
+            for (int j = 0; j < K; ++j)
+                value += conv_w[(int64_t)c * K + j] * (j < taps ? rr[(int64_t)j * conv_dim + c] : current);
+            xBC[(int64_t)r * conv_dim + c] = tor_silu_stable(value);
+            if (taps > 0) {
+                for (int s = 0; s + 1 < taps; ++s) rr[(int64_t)s * conv_dim + c] = rr[(int64_t)(s + 1) * conv_dim + c];
+                rr[(int64_t)(taps - 1) * conv_dim + c] = current;
+            }
+        }
+    }
+}
+
+/* delta = softplus(dt), decay = exp(-delta * exp(A_log)) evaluated in double.
+ * OXN/nsos/src/mamba2.cpp:443-473 (mamba_decay_terms; the gradient terms are not needed here). */
+static void tor_decay_terms(float dt_raw, float a_log, float* delta_out, float* decay_out) {
+    const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
+    *delta_out = delta;
+    if (!isfinite(dt_raw) || !isfinite(a_log)) { *decay_out = NAN; return; }
+    const double log_delta = dt_raw < -20.0f ? (double)dt_raw : log((double)delta);
+    const double log_q = log_delta + (double)a_log;
+    if (log_q > 50.0) { *decay_out = 0.0f; return; }
+    *decay_out = (float)exp(-exp(log_q));
+}
+
+/* One SSD recurrence step: h = decay*h + delta*B*x ; y = D*x + sum_n h*C.
+ * OXN/nsos/src/mamba2.cpp:4096-4118; device form mamba2_faithful_step_kernel,
+ * OXN/nsos/src/cuda/mamba_kernels.cu:3376-3405.  xBC [R][d_inner + 2*G*N], dt [R][H],
+ * state [R][d_inner][N], y [R][d_inner]. */
+void tor_mamba_ssd_step(const float* xBC, const float* dt, const float* A_log, const float* D, float* state,
+                        int R, int n_heads, int d_head, int N, int n_groups, float* y) {
+    const int d_inner = n_heads * d_head, GS = n_groups * N, conv_dim = d_inner + 2 * GS;
+    for (int r = 0; r < R; ++r) {
+        const float* row = xBC + (int64_t)r * conv_dim;
+        float* st = state + (int64_t)r * d_inner * N;
+        for (int h = 0; h < n_heads; ++h) {
+            const int group = (h * n_groups) / n_heads;
+            float delta, decay;
+            tor_decay_terms(dt[(int64_t)r * n_heads + h], A_log[h], &delta, &decay);
+            for (int p = 0; p < d_head; ++p) {
+                const int chan = h * d_head + p;
+                const float input = row[chan];
+                float out = D[h] * input;
+                for (int n = 0; n < N; ++n) {
+                    const int64_t si = (int64_t)chan * N + n;
+                    const float Bvalue = row[d_inner + group * N + n];
+                    const float Cvalue = row[d_inner + GS + group * N + n];
+                    st[si] = decay * st[si] + delta * Bvalue * input;
+                    out += st[si] * Cvalue;
+                }
+                y[(int64_t)r * d_inner + chan] = out;
+            }
+        }
+    }
+}
+
+/* Single-token attention over the KV cache: RoPE on q and k at the row's position, append k/v, per-head
+ * softmax(q.k * scale) over the window, weighted sum of v.
+ * OXN/nsos/src/jamba.cpp:5140-5190 (apply_rope: halves i / i + head_dim/2), :6520-6542 (k | v split, append),
+ * :6604-6638 (scores, softmax with 1/max(sum,1e-9), accumulation in token order); device form
+ * gqa_cached_attention_decode, OXN/nsos/src/cuda/kernels.cu:2853-2990.
+ * q [R][H*hd], kv [R][2*KV*hd] (k then v), caches [R][capacity][KV*hd], tokens[r] = entries already cached
+ * (advanced here), cos/sin [positions][hd/2], out [R][H*hd]. */
+void tor_attention_decode(const float* q, const float* kv, float* k_cache, float* v_cache, int capacity,
+                          int* tokens, const float* cos_t, const float* sin_t, int R, int n_heads,
+                          int n_kv_heads, int head_dim, int sliding_window, float* out) {
+    const int kv_dim = n_kv_heads * head_dim, half = head_dim / 2, d_model = n_heads * head_dim;
+    const int group = n_heads / n_kv_heads > 0 ? n_heads / n_kv_heads : 1;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    float* qr = (float*)malloc(sizeof(float) * d_model);
+    float* scores = (float*)malloc(sizeof(float) * (capacity + 1));
+    for (int r = 0; r < R; ++r) {
+        const int pos = tokens[r];
+        const float* c = cos_t + (int64_t)pos * half;
+        const float* s = sin_t + (int64_t)pos * half;
+        for (int h = 0; h < n_heads; ++h)
+            for (int i = 0; i < half; ++i) {
+                const float q0 = q[(int64_t)r * d_model + h * head_dim + i];
+                const float q1 = q[(int64_t)r * d_model + h * head_dim + i + half];
+                qr[h * head_dim + i] = q0 * c[i] - q1 * s[i];
+                qr[h * head_dim + i + half] = q0 * s[i] + q1 * c[i];
+            }
+        float* kc = k_cache + ((int64_t)r * capacity + pos) * kv_dim;
+        float* vc = v_cache + ((int64_t)r * capacity + pos) * kv_dim;
+        for (int h = 0; h < n_kv_heads; ++h)
+            for (int i = 0; i < half; ++i) {
+                const float k0 = kv[(int64_t)r * 2 * kv_dim + h * head_dim + i];
+                const float k1 = kv[(int64_t)r * 2 * kv_dim + h * head_dim + i + half];
+                kc[h * head_dim + i] = k0 * c[i] - k1 * s[i];
+                kc[h * head_dim + i + half] = k0 * s[i] + k1 * c[i];
+            }
+        memcpy(vc, kv + (int64_t)r * 2 * kv_dim + kv_dim, sizeof(float) * kv_dim);
+        const int cached = pos + 1;
+        tokens[r] = cached;
+        const int first = cached - sliding_window > 0 ? cached - sliding_window : 0;
+        for (int h = 0; h < n_heads; ++h) {
+            int kvh = h / group;
+            if (kvh > n_kv_heads - 1) kvh = n_kv_heads - 1;
+            float max_s = -1e30f;
+            for (int t = first; t < cached; ++t) {
+                const float* key = k_cache + ((int64_t)r * capacity + t) * kv_dim + kvh * head_dim;
+                float dot = 0.0f;
+                for (int d = 0; d < head_dim; ++d) dot += qr[h * head_dim + d] * key[d];
+                scores[t] = dot * scale;
+                if (scores[t] > max_s) max_s = scores[t];
+            }
+            float sum_exp = 0.0f;
+            for (int t = first; t < cached; ++t) { scores[t] = expf(scores[t] - max_s); sum_exp += scores[t]; }
+            const float inv_sum = 1.0f / (sum_exp > 1e-9f ? sum_exp : 1e-9f);
+            for (int t = first; t < cached; ++t) scores[t] *= inv_sum;
+            float* oh = out + (int64_t)r * d_model + h * head_dim;
+            for (int d = 0; d < head_dim; ++d) oh[d] = 0.0f;
+            for (int t = first; t < cached; ++t) {
+                const float* val = v_cache + ((int64_t)r * capacity + t) * kv_dim + kvh * head_dim;
+                for (int d = 0; d < head_dim; ++d) oh[d] += scores[t] * val[d];
+            }
+        }
+    }
+    free(qr);
+    free(scores);
+}
+
 /* Multi-threaded wrapper for the CPU-baseline timing legs: rows are sharded over
  * `threads` OpenMP workers (the reference's GEMM itself is single-threaded,
  * OXN/nsos/src/bitnet_adapter_avx2.cpp has no OpenMP; sharding rows is the fair

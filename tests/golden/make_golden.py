@@ -80,8 +80,55 @@ ROW_NORM_CASES = [
 ]
 
 
+TINY_MODEL = dict(num_layers=2, d_model=64, vocab_size=96, n_heads=1, n_kv_heads=1, mamba_d_state=16, mamba_expand=2,
+                  mamba_conv_kernel=4, mamba_head_dim=64, mamba_n_groups=1, attention_period=2, attention_slot=1)
+TINY_TOKENS = [5, 90, 17, 17, 0, 63, 41, 8]
+
+
+def model_fixtures(only):
+    """From the reference's whole model (oracle/_ref/libnsos_model_ref.so): a two-block hybrid (one Mamba-2 block,
+    one Mamba-2 + attention + FFN block) stepped token by token through JambaModel::forward_ids_last, with its
+    parameters, the residual stream after every block, its own edge-linear pack, and MoERouter::forward."""
+    if not oracle.model_ref_available():
+        print("model reference library not built: decode / edge-pack / router fixtures skipped")
+        return
+    MR = oracle.model_ref()
+    if "decode_tiny".startswith(only) or "edge_pack_tiny".startswith(only):
+        m = MR.model(TINY_MODEL, seed=11)
+        params = m.export()
+        twin = MR.model(TINY_MODEL, seed=11)
+        logits, hidden = [], []
+        for tok in TINY_TOKENS:
+            lg = m.step(tok)                       # public API
+            hd, lg2 = twin.step_trace(tok)         # block by block on a twin with the same seed
+            assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32))
+            logits.append(lg)
+            hidden.append(hd)
+        rec = {"param:" + k: v for k, v in params.items()}
+        rec.update(tokens=np.asarray(TINY_TOKENS, np.int32), logits=np.stack(logits), hidden=np.stack(hidden),
+                   cfg=np.asarray([TINY_MODEL[k] for k in oracle.MODEL_CFG_FIELDS], np.int32))
+        np.savez_compressed(os.path.join(OUT, "decode_tiny.npz"), **rec)
+        print("decode_tiny logits[0,:3]", logits[0][:3], "logits[-1,:3]", logits[-1][:3])
+        path = os.path.join(OUT, "edge_pack_tiny.bin")
+        m.save_edge_pack(path)
+        print("edge_pack_tiny.bin", os.path.getsize(path), "bytes")
+        m.close()
+        twin.close()
+    if "router_".startswith(only[:7]) or not only:
+        for name, seed, rows, D, E, k in [("router_40x64_e8_top2", 41, 40, 64, 8, 2), ("router_9x32_e4_top1", 42, 9, 32, 4, 1)]:
+            rng = np.random.default_rng(seed)
+            x = rng.standard_normal((rows, D)).astype(np.float32)
+            x[1] = x[0]                                       # two identical rows
+            gate = (rng.standard_normal((E, D)) * 0.02).astype(np.float32)
+            gate[1] = gate[0]                                 # a tie between experts 0 and 1 on every row
+            lg, w = MR.router(x, gate, k)
+            np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, gate=gate, top_k=k, logits=lg, weights=w)
+            print(name, "weights[0]", w[0])
+
+
 def main():
     only = sys.argv[1] if len(sys.argv) > 1 else ""
+    model_fixtures(only)
     R = oracle.ref()
     row_norm_fixtures(R, only)
     for name, seed, N, K, M, exact, affine, bits, store in LINEAR_CASES:
