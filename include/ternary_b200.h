@@ -259,6 +259,12 @@ int tbl_chain_forward(const tbl_linear_view* views_host, int count, const int* s
                       const float* x_dev, int rows, int rms_mode, float* y_dev, void* workspace_dev,
                       size_t workspace_bytes, void* stream);
 
+/* Column-split layers (one rank per block of output columns, see tbl_linear_forward: each rank writes its
+ * [rows, cols] block straight into its slot of the all-gather buffer): gathered_dev fp32 [parts, rows, cols] as the
+ * all-gather leaves it -> out_dev fp32 [rows, parts*cols].  Local memory only.  No counterpart in the reference,
+ * which has no multi-GPU inference (its optional host-staged MPI layer is OXN/nsos/src/fabric_v2.cpp:192-258). */
+int tbl_retile_columns(const float* gathered_dev, int parts, int rows, int cols, float* out_dev, void* stream);
+
 /* Router post-processing on the device: logits fp32 [rows, experts] (the gate's output) -> routing weights
  * [rows, experts] as tbl_moe_forward takes them: softmax, keep the top_k largest per row (ties -> lower
  * index), renormalise, zero the rest; top_k == 0 or >= experts leaves the softmax.  May run in place.
@@ -287,6 +293,122 @@ int tbl_router_topk(const float* logits_dev, int rows, int experts, int top_k, f
 int tbl_row_norm(const float* value_dev, const float* gate_dev, const float* weight_dev, int rows, int dim,
                  float eps, float* out_dev, int bits, int8_t* q_dev, float* act_scales_dev,
                  int32_t* q_sums_dev, void* stream);
+
+/* ---- one decode step of the Mamba-2 / attention hybrid ----------------------------------------- */
+
+/* The streaming single-token step of the reference's model (JambaModel::forward_ids_last on one token per
+ * sequence in streaming mode, OXN/nsos/src/jamba.cpp:851-992, 1963-1980; its graph form
+ * JambaModel::forward_ids_decode_graph, :2074-2376) for a batch of independent sequences:
+ *   embedding gather (OXN/nsos/src/embedding.cpp:618) -> per block { RMSNorm x weight; Mamba-2 branch: x / z / B / C / dt
+ *   projections, causal-conv step + SiLU, SSD recurrence step, SiLU-gated RMSNorm, out projection
+ *   (Mamba2SSD::forward_faithful_step, OXN/nsos/src/mamba2.cpp:3947-4125; device forms
+ *   OXN/nsos/src/cuda/mamba_kernels.cu:3332-3405); hybrid blocks add, in parallel on their own norm of the same
+ *   residual stream, attention over the KV cache with RoPE (OXN/nsos/src/jamba.cpp:6291-6295, 6500-6640;
+ *   OXN/nsos/src/cuda/kernels.cu:2853-2990), the per-channel gates (OXN/nsos/src/jamba.cpp:3195-3230) and the FFN
+ *   up -> squared ReLU -> down (OXN/nsos/src/jamba.cpp:3286-3367) } -> final RMSNorm x weight -> LM head.
+ * Every projection is a ternary linear described by a tbl_linear_view (packed mode; `strips` where inputs % 256 == 0
+ * gives the fast path).  All pointers are device pointers except `blocks`, which is a host array. */
+#define TBL_MAX_DECODE_BLOCKS 128
+
+typedef struct tbl_mamba_block {
+    tbl_linear_view x, z;          /* d_model -> d_inner                                   */
+    tbl_linear_view B, C;          /* d_model -> n_groups * d_state                        */
+    tbl_linear_view dt;            /* d_model -> n_heads (its bias is the dt bias)         */
+    tbl_linear_view out;           /* d_inner -> d_model                                   */
+    const float* A_log;            /* [n_heads]                                            */
+    const float* D;                /* [n_heads]                                            */
+    const float* conv_w;           /* [d_inner + 2*n_groups*d_state, conv_kernel]          */
+    const float* conv_b;           /* [d_inner + 2*n_groups*d_state]                       */
+    const float* norm_w;           /* [d_inner], weight of the gated norm                  */
+    int d_inner, n_heads, d_head, n_groups, d_state, conv_kernel;
+    float norm_eps;
+} tbl_mamba_block;
+
+typedef struct tbl_attention_block {
+    tbl_linear_view q;             /* d_model -> n_heads * head_dim                        */
+    tbl_linear_view kv;            /* d_model -> 2 * n_kv_heads * head_dim (k then v)      */
+    tbl_linear_view out;           /* d_model -> d_model                                   */
+    const float* rope_cos;         /* [rope_positions, head_dim / 2]                       */
+    const float* rope_sin;
+    int n_heads, n_kv_heads, head_dim, sliding_window, rope_positions;
+} tbl_attention_block;
+
+typedef struct tbl_decode_block {
+    int hybrid;                    /* 0: x + mamba(norm(x)); 1: gated mamba + attention, then the gated FFN */
+    const float* core_norm_w;      /* [d_model] or NULL                                    */
+    float core_norm_eps;
+    tbl_mamba_block mamba;
+    /* hybrid blocks only */
+    const float* attn_norm_w;      /* [d_model] or NULL                                    */
+    const float* ff_norm_w;        /* [d_model] or NULL                                    */
+    const float* mamba_gate;       /* [d_model]                                            */
+    const float* attn_gate;        /* [d_model]                                            */
+    const float* ffn_gate;         /* [d_model]                                            */
+    tbl_attention_block attn;
+    tbl_linear_view ffn_up, ffn_down;
+} tbl_decode_block;
+
+typedef struct tbl_decode_model {
+    int d_model, vocab, n_blocks;
+    const float* embedding;        /* [vocab, d_model]                                     */
+    const tbl_decode_block* blocks;/* HOST array of n_blocks entries                       */
+    const float* final_norm_w;     /* [d_model] or NULL                                    */
+    float final_norm_eps;
+    tbl_linear_view head;          /* d_model -> vocab                                     */
+} tbl_decode_model;
+
+/* The glue kernels of the step, one entry point each (all enqueue on `stream`, fp32, row-major).
+ *
+ * tbl_embedding_gather: out[i,:] = table[ids[i],:], a zero row for an id outside [0, vocab).
+ *   Replaces: launch_embedding_gather_kernel (OXN/nsos/src/cuda/kernels.cu:639), Embedding::forward
+ *   (OXN/nsos/src/embedding.cpp:618).
+ * tbl_mamba_conv_step: causal depthwise conv over the concatenated channels [x | B | C] with the window kept in
+ *   ring_dev [rows, conv_kernel-1, d_inner + 2*group_state] (oldest tap first; shifted here), bias, SiLU.
+ *   Replaces: launch_mamba2_faithful_conv_step (OXN/nsos/src/cuda/mamba_kernels.cu:3332-3359),
+ *   host form OXN/nsos/src/mamba2.cpp:4062-4094.
+ * tbl_mamba_ssd_step: h = decay*h + delta*B*x, y = D*x + sum_n h*C with delta = softplus(dt),
+ *   decay = exp(-delta*exp(A_log)) (in double); state_dev [rows, n_heads*d_head, d_state] is updated.
+ *   Replaces: launch_mamba2_faithful_step (OXN/nsos/src/cuda/mamba_kernels.cu:3376-3405), host form
+ *   OXN/nsos/src/mamba2.cpp:443-473, 4096-4118.
+ * tbl_attention_decode: one new token per row: RoPE (halves i / i + head_dim/2) on q and k at positions_dev[row],
+ *   k | v appended to the caches [rows, capacity, n_kv_heads*head_dim], softmax(q.k / sqrt(head_dim)) over the last
+ *   sliding_window tokens, weighted sum of v -> out [rows, n_heads*head_dim].  positions_dev is NOT advanced.
+ *   Replaces: launch_gqa_append_kv_cache_kernel + launch_gqa_cached_attention_decode_kernel
+ *   (OXN/nsos/src/cuda/kernels.cu:2853-2990), host form OXN/nsos/src/jamba.cpp:5140-5190, 6520-6640.
+ * tbl_gated_residual: out = x + (a*gate_a [+ b*gate_b]) with per-channel gates [dim]; gate_a NULL: out = x + a.
+ *   Replaces: the Tensor mul/add chains of JambaBlock::forward (OXN/nsos/src/jamba.cpp:3224-3251, 3367-3371). */
+int tbl_embedding_gather(const int32_t* ids_dev, int count, const float* table_dev, int vocab, int dim, float* out_dev,
+                         void* stream);
+int tbl_mamba_conv_step(const float* x_dev, const float* B_dev, const float* C_dev, const float* conv_w_dev,
+                        const float* conv_b_dev, float* ring_dev, float* xbc_dev, int d_inner, int group_state,
+                        int conv_kernel, int rows, void* stream);
+int tbl_mamba_ssd_step(const float* xbc_dev, const float* dt_dev, const float* A_log_dev, const float* D_dev,
+                       float* state_dev, float* y_dev, int n_heads, int d_head, int d_state, int n_groups, int rows,
+                       void* stream);
+int tbl_attention_decode(const float* q_dev, const float* kv_dev, float* k_cache_dev, float* v_cache_dev, int capacity,
+                         const int32_t* positions_dev, const float* rope_cos_dev, const float* rope_sin_dev,
+                         int rope_positions, int n_heads, int n_kv_heads, int head_dim, int sliding_window, int rows,
+                         float* out_dev, void* stream);
+int tbl_gated_residual(const float* x_dev, const float* a_dev, const float* gate_a_dev, const float* b_dev,
+                       const float* gate_b_dev, int rows, int dim, float* out_dev, void* stream);
+
+/* Device state of `batch` sequences with room for `capacity` cached tokens each (positions, conv windows, SSM
+ * states, KV caches): size, and reset to the empty session (JambaModel::reset_session + reserve_kv_cache). */
+size_t tbl_decode_state_bytes(const tbl_decode_model* model, int batch, int capacity);
+int tbl_decode_state_reset(const tbl_decode_model* model, int batch, int capacity, void* state_dev, size_t state_bytes,
+                           void* stream);
+size_t tbl_decode_workspace_bytes(const tbl_decode_model* model, int batch);
+
+/* Enqueues one step: token_ids_dev int32 [batch] -> logits_dev fp32 [batch, vocab]; the state advances by one
+ * token per sequence (positions live on the device, so a captured step can be replayed).  hidden_trace_dev
+ * (may be NULL) receives the residual stream fp32 [n_blocks + 1, batch, d_model]: the embedding rows, then the
+ * stream after every block.  state_dev and workspace_dev must be 256-byte aligned.  A sequence whose cache is
+ * full is reported through the device status (TBL_DEV_CACHE_FULL).  fp32 results agree with the reference's CPU
+ * path to ~1e-5 relative per operation (device expf / exp / log, tree-shaped norm and softmax sums), not bit for
+ * bit; the ternary linears themselves are bit-exact on identical inputs. */
+int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void* state_dev,
+                    const int32_t* token_ids_dev, float* logits_dev, float* hidden_trace_dev, void* workspace_dev,
+                    size_t workspace_bytes, void* stream);
 
 /* Bytes of scratch for tbl_moe_forward. */
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row);
@@ -351,6 +473,7 @@ void tbl_sha256_hex(const void* data, size_t bytes, char out[65]);
 #define TBL_DEV_OK 0
 #define TBL_DEV_WAIT_TIMEOUT 1     /* a bounded mbarrier / TMA wait gave up                */
 #define TBL_DEV_ROUTE_OVERFLOW 2   /* a row had more routes than max_routes_per_row        */
+#define TBL_DEV_CACHE_FULL 4       /* decode step: a sequence's KV cache or rotary table is full */
 
 /* Synchronises `stream`, returns the sticky device status word of the current device and
  * clears it.  Negative on a CUDA error. */

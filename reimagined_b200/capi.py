@@ -47,6 +47,41 @@ class EdgeLayerSrc(C.Structure):
                 ("flat_alpha", C.c_void_p), ("flat_beta", C.c_void_p), ("weight", C.c_void_p)]
 
 
+class MambaBlock(C.Structure):
+    """tbl_mamba_block."""
+
+    _fields_ = [("x", LinearView), ("z", LinearView), ("B", LinearView), ("C", LinearView), ("dt", LinearView),
+                ("out", LinearView), ("A_log", C.c_void_p), ("D", C.c_void_p), ("conv_w", C.c_void_p),
+                ("conv_b", C.c_void_p), ("norm_w", C.c_void_p), ("d_inner", C.c_int), ("n_heads", C.c_int),
+                ("d_head", C.c_int), ("n_groups", C.c_int), ("d_state", C.c_int), ("conv_kernel", C.c_int),
+                ("norm_eps", C.c_float)]
+
+
+class AttentionBlock(C.Structure):
+    """tbl_attention_block."""
+
+    _fields_ = [("q", LinearView), ("kv", LinearView), ("out", LinearView), ("rope_cos", C.c_void_p),
+                ("rope_sin", C.c_void_p), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int),
+                ("sliding_window", C.c_int), ("rope_positions", C.c_int)]
+
+
+class DecodeBlock(C.Structure):
+    """tbl_decode_block."""
+
+    _fields_ = [("hybrid", C.c_int), ("core_norm_w", C.c_void_p), ("core_norm_eps", C.c_float), ("mamba", MambaBlock),
+                ("attn_norm_w", C.c_void_p), ("ff_norm_w", C.c_void_p), ("mamba_gate", C.c_void_p),
+                ("attn_gate", C.c_void_p), ("ffn_gate", C.c_void_p), ("attn", AttentionBlock), ("ffn_up", LinearView),
+                ("ffn_down", LinearView)]
+
+
+class DecodeModel(C.Structure):
+    """tbl_decode_model."""
+
+    _fields_ = [("d_model", C.c_int), ("vocab", C.c_int), ("n_blocks", C.c_int), ("embedding", C.c_void_p),
+                ("blocks", C.POINTER(DecodeBlock)), ("final_norm_w", C.c_void_p), ("final_norm_eps", C.c_float),
+                ("head", LinearView)]
+
+
 _vp = C.c_void_p
 _SIGNATURES = {
     # name: (restype, argtypes)
@@ -78,6 +113,17 @@ _SIGNATURES = {
     "tbl_chain_workspace_bytes": (C.c_size_t, [C.POINTER(LinearView), C.c_int, C.c_int]),
     "tbl_chain_forward": (C.c_int, [C.POINTER(LinearView), C.c_int, C.POINTER(C.c_int), _vp, C.c_int, C.c_int, _vp, _vp,
                                     C.c_size_t, _vp]),
+    "tbl_embedding_gather": (C.c_int, [_vp, C.c_int, _vp, C.c_int, C.c_int, _vp, _vp]),
+    "tbl_mamba_conv_step": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "tbl_mamba_ssd_step": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "tbl_attention_decode": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, C.c_int, _vp, _vp]),
+    "tbl_gated_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, _vp, _vp]),
+    "tbl_decode_state_bytes": (C.c_size_t, [C.POINTER(DecodeModel), C.c_int, C.c_int]),
+    "tbl_decode_state_reset": (C.c_int, [C.POINTER(DecodeModel), C.c_int, C.c_int, _vp, C.c_size_t, _vp]),
+    "tbl_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeModel), C.c_int]),
+    "tbl_decode_step": (C.c_int, [C.POINTER(DecodeModel), C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "tbl_retile_columns": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "tbl_router_topk": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "tbl_row_norm": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_float, _vp, C.c_int, _vp, _vp, _vp, _vp]),
     "tbl_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),

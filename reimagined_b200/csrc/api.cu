@@ -472,7 +472,13 @@ size_t tbl_chain_workspace_bytes(const tbl_linear_view* views_host, int count, i
         const size_t b = tbl_linear_workspace_bytes(rows, views_host[i].inputs, views_host[i].outputs);
         lin = b > lin ? b : lin;
     }
-    return 1024 + 2 * chain_act_bytes(views_host, count, rows) + lin;
+    // the persistent kernel's scratch (barrier words, strip flags, activations) or the layer-by-layer route's
+    // (activations + one layer's quantiser scratch), whichever is larger
+    ChainLayer layers[TBL_MAX_CHAIN];
+    for (int i = 0; i < count; ++i) { layers[i] = ChainLayer{}; layers[i].N = views_host[i].outputs; layers[i].K = views_host[i].inputs; }
+    const size_t persistent = gemv_chain_workspace_bytes(layers, count, rows);
+    const size_t stepwise = 1024 + 2 * chain_act_bytes(views_host, count, rows) + lin;
+    return persistent > stepwise ? persistent : stepwise;
 }
 
 int tbl_chain_forward(const tbl_linear_view* views_host, int count, const int* squared_relu_host,
@@ -536,6 +542,11 @@ int tbl_row_norm(const float* value_dev, const float* gate_dev, const float* wei
     }
     return cuda_status(launch_row_norm(value_dev, gate_dev, weight_dev, rows, dim, eps, bits, out_dev, q_dev,
                                        act_scales_dev, q_sums_dev, static_cast<cudaStream_t>(stream)));
+}
+
+int tbl_retile_columns(const float* gathered_dev, int parts, int rows, int cols, float* out_dev, void* stream) {
+    if (!gathered_dev || !out_dev || parts <= 0 || rows <= 0 || cols <= 0 || gathered_dev == out_dev) return TBL_ERR_INVALID_ARG;
+    return cuda_status(launch_retile_columns(gathered_dev, parts, rows, cols, out_dev, static_cast<cudaStream_t>(stream)));
 }
 
 size_t tbl_moe_workspace_bytes(int rows, int dim, int hidden_dim, int experts, int max_routes_per_row) {

@@ -1,0 +1,565 @@
+// One streaming decode step of the Mamba-2 / attention hybrid whose every projection is a ternary linear:
+// the glue kernels between the linears (embedding gather, causal-conv step, SSD recurrence step, single-token
+// attention over the KV cache with RoPE, gated residual adds) and the host routine that enqueues the whole
+// step on one stream -- no allocation, no synchronisation, positions kept on the device -- so a caller can
+// capture it once in a CUDA graph and replay it per token.
+//
+// The arithmetic follows the reference's host branches operation by operation (separately rounded products
+// and sums, the same summation orders) so that results differ from them only through the device's expf / exp /
+// log and the tree-shaped sums of the norms and the softmax denominator.
+#include <cmath>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tbl {
+namespace {
+
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- embedding gather: out[b,:] = table[ids[b],:]; an id outside [0, vocab) gives a zero row ----------------
+__global__ void __launch_bounds__(256) embedding_gather_kernel(const int32_t* __restrict__ ids,
+                                                               const float* __restrict__ table, int vocab, int D,
+                                                               float* __restrict__ out, float* __restrict__ trace) {
+    const int b = blockIdx.x;
+    const int id = __ldg(ids + b);
+    const bool ok = id >= 0 && id < vocab;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = ok ? __ldg(table + static_cast<size_t>(id) * D + d) : 0.0f;
+        out[static_cast<size_t>(b) * D + d] = v;
+        if (trace) trace[static_cast<size_t>(b) * D + d] = v;
+    }
+}
+
+__device__ __forceinline__ float silu_stable(float x) {
+    float sig;
+    if (x >= 0.0f) {
+        const float z = expf(-x);
+        sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, z));
+    } else {
+        const float z = expf(x);
+        sig = __fdiv_rn(z, __fadd_rn(1.0f, z));
+    }
+    return __fmul_rn(x, sig);
+}
+
+// ---- Mamba-2 causal depthwise conv step + SiLU over [x | B | C], then the ring shift ------------------------
+// One thread per (row, channel).  ring [R][K-1][conv_dim], oldest tap first.
+__global__ void __launch_bounds__(256) mamba_conv_step_kernel(const float* __restrict__ xv, const float* __restrict__ Bv,
+                                                              const float* __restrict__ Cv,
+                                                              const float* __restrict__ conv_w,
+                                                              const float* __restrict__ conv_b, float* __restrict__ ring,
+                                                              int d_inner, int GS, int K, float* __restrict__ xBC) {
+    const int conv_dim = d_inner + 2 * GS;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= conv_dim) return;
+    const int taps = K - 1;
+    float* rr = ring + static_cast<size_t>(r) * taps * conv_dim;
+    const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
+                                      : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
+                                                          : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
+    float value = __ldg(conv_b + c);
+    for (int j = 0; j < K; ++j) {
+        const float tap = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
+        value = __fadd_rn(value, __fmul_rn(__ldg(conv_w + static_cast<size_t>(c) * K + j), tap));
+    }
+    xBC[static_cast<size_t>(r) * conv_dim + c] = silu_stable(value);
+    for (int s = 0; s + 1 < taps; ++s) rr[static_cast<size_t>(s) * conv_dim + c] = rr[static_cast<size_t>(s + 1) * conv_dim + c];
+    if (taps > 0) rr[static_cast<size_t>(taps - 1) * conv_dim + c] = current;
+}
+
+// ---- SSD recurrence step: h = decay*h + delta*B*x ; y = D*x + sum_n h*C -------------------------------------
+// One thread per (row, channel); delta = softplus(dt), decay = exp(-delta*exp(A_log)) in double.
+__global__ void __launch_bounds__(128) mamba_ssd_step_kernel(const float* __restrict__ xBC, const float* __restrict__ dt,
+                                                             const float* __restrict__ A_log, const float* __restrict__ Dp,
+                                                             float* __restrict__ state, int n_heads, int d_head, int N,
+                                                             int n_groups, float* __restrict__ y) {
+    const int d_inner = n_heads * d_head, GS = n_groups * N, conv_dim = d_inner + 2 * GS;
+    const int chan = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (chan >= d_inner) return;
+    const int h = chan / d_head;
+    const int group = (h * n_groups) / n_heads;
+    const float dt_raw = dt[static_cast<size_t>(r) * n_heads + h];
+    const float a_log = __ldg(A_log + h);
+    const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
+    float decay;
+    if (!isfinite(dt_raw) || !isfinite(a_log)) {
+        decay = nanf("");
+    } else {
+        const double log_delta = dt_raw < -20.0f ? static_cast<double>(dt_raw) : log(static_cast<double>(delta));
+        const double log_q = log_delta + static_cast<double>(a_log);
+        decay = log_q > 50.0 ? 0.0f : static_cast<float>(exp(-exp(log_q)));
+    }
+    const float* row = xBC + static_cast<size_t>(r) * conv_dim;
+    const float input = row[chan];
+    float out = __fmul_rn(__ldg(Dp + h), input);
+    float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
+    for (int n = 0; n < N; ++n) {
+        const float Bvalue = row[d_inner + group * N + n];
+        const float Cvalue = row[d_inner + GS + group * N + n];
+        const float hv = __fadd_rn(__fmul_rn(decay, st[n]), __fmul_rn(__fmul_rn(delta, Bvalue), input));
+        st[n] = hv;
+        out = __fadd_rn(out, __fmul_rn(hv, Cvalue));
+    }
+    y[static_cast<size_t>(r) * d_inner + chan] = out;
+}
+
+// ---- single-token attention over the KV cache ----------------------------------------------------------------
+// One CTA per (query head, row).  RoPE on q and on the new key at the row's position; the first head of a
+// KV group appends the rotated key and the value to the cache; every CTA keeps the new key / value of its group
+// in shared memory, so no CTA reads what another one writes in this launch.
+constexpr int kAttnThreads = 128;
+__global__ void __launch_bounds__(kAttnThreads)
+attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ kv, float* __restrict__ k_cache,
+                        float* __restrict__ v_cache, int capacity, const int32_t* __restrict__ positions,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rope_positions,
+                        int n_heads, int n_kv_heads, int head_dim, int sliding_window, float* __restrict__ out,
+                        int* status) {
+    extern __shared__ float sm[];
+    float* qr = sm;                       // [head_dim]
+    float* knew = qr + head_dim;          // [head_dim]
+    float* vnew = knew + head_dim;        // [head_dim]
+    float* red = vnew + head_dim;         // [kAttnThreads]
+    float* scores = red + kAttnThreads;   // [capacity]
+    const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+    const int kv_dim = n_kv_heads * head_dim, half = head_dim / 2, d_model = n_heads * head_dim;
+    const int group = n_heads / n_kv_heads > 0 ? n_heads / n_kv_heads : 1;
+    const int kvh = min(h / group, n_kv_heads - 1);
+    const int pos = __ldg(positions + r);
+    if (pos < 0 || pos >= capacity || pos >= rope_positions) {
+        // the cache (or the rotary table) is full: report it and leave this row's output at zero
+        if (tid == 0) atomicOr(status, TBL_DEV_CACHE_FULL);
+        for (int d = tid; d < head_dim; d += kAttnThreads) out[static_cast<size_t>(r) * d_model + h * head_dim + d] = 0.0f;
+        return;
+    }
+    const float* c = cos_t + static_cast<size_t>(pos) * half;
+    const float* s = sin_t + static_cast<size_t>(pos) * half;
+    const float* qh = q + static_cast<size_t>(r) * d_model + h * head_dim;
+    const float* kh = kv + static_cast<size_t>(r) * 2 * kv_dim + kvh * head_dim;
+    for (int i = tid; i < half; i += kAttnThreads) {
+        const float cv = __ldg(c + i), sv = __ldg(s + i);
+        const float q0 = qh[i], q1 = qh[i + half];
+        qr[i] = __fsub_rn(__fmul_rn(q0, cv), __fmul_rn(q1, sv));
+        qr[i + half] = __fadd_rn(__fmul_rn(q0, sv), __fmul_rn(q1, cv));
+        const float k0 = kh[i], k1 = kh[i + half];
+        knew[i] = __fsub_rn(__fmul_rn(k0, cv), __fmul_rn(k1, sv));
+        knew[i + half] = __fadd_rn(__fmul_rn(k0, sv), __fmul_rn(k1, cv));
+        vnew[i] = kh[kv_dim + i];
+        vnew[i + half] = kh[kv_dim + i + half];
+    }
+    __syncthreads();
+    if (h == kvh * group) {
+        float* kc = k_cache + (static_cast<size_t>(r) * capacity + pos) * kv_dim + kvh * head_dim;
+        float* vc = v_cache + (static_cast<size_t>(r) * capacity + pos) * kv_dim + kvh * head_dim;
+        for (int d = tid; d < head_dim; d += kAttnThreads) { kc[d] = knew[d]; vc[d] = vnew[d]; }
+    }
+    const int cached = pos + 1;
+    const int first = max(0, cached - sliding_window);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(head_dim)));
+    // scores: one token per thread, the dot product in dimension order
+    float local_max = -1e30f;
+    for (int t = first + tid; t < cached; t += kAttnThreads) {
+        float dot = 0.0f;
+        if (t == pos) {
+            for (int d = 0; d < head_dim; ++d) dot = __fadd_rn(dot, __fmul_rn(qr[d], knew[d]));
+        } else {
+            const float4* key = reinterpret_cast<const float4*>(k_cache + (static_cast<size_t>(r) * capacity + t) * kv_dim + kvh * head_dim);
+            for (int d4 = 0; d4 < head_dim / 4; ++d4) {
+                const float4 k4 = key[d4];
+                dot = __fadd_rn(dot, __fmul_rn(qr[4 * d4], k4.x));
+                dot = __fadd_rn(dot, __fmul_rn(qr[4 * d4 + 1], k4.y));
+                dot = __fadd_rn(dot, __fmul_rn(qr[4 * d4 + 2], k4.z));
+                dot = __fadd_rn(dot, __fmul_rn(qr[4 * d4 + 3], k4.w));
+            }
+        }
+        const float sc = __fmul_rn(dot, scale);
+        scores[t - first] = sc;
+        local_max = fmaxf(local_max, sc);
+    }
+    red[tid] = local_max;
+    __syncthreads();
+    for (int o = kAttnThreads / 2; o; o >>= 1) {
+        if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
+        __syncthreads();
+    }
+    const float max_s = red[0];
+    __syncthreads();
+    float local_sum = 0.0f;
+    for (int t = first + tid; t < cached; t += kAttnThreads) {
+        const float e = expf(__fsub_rn(scores[t - first], max_s));
+        scores[t - first] = e;
+        local_sum += e;
+    }
+    red[tid] = local_sum;
+    __syncthreads();
+    for (int o = kAttnThreads / 2; o; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+    }
+    const float inv_sum = __fdiv_rn(1.0f, fmaxf(red[0], 1e-9f));
+    // weighted sum of the values: one dimension per thread, tokens in order
+    for (int d = tid; d < head_dim; d += kAttnThreads) {
+        float acc = 0.0f;
+        const float* vbase = v_cache + static_cast<size_t>(r) * capacity * kv_dim + kvh * head_dim + d;
+        for (int t = first; t < cached; ++t) {
+            const float v = t == pos ? vnew[d] : vbase[static_cast<size_t>(t) * kv_dim];
+            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(scores[t - first], inv_sum), v));
+        }
+        out[static_cast<size_t>(r) * d_model + h * head_dim + d] = acc;
+    }
+}
+
+// ---- out = x + (a * ga [+ b * gb]); ga == null: out = x + a ----------------------------------------------------
+__global__ void __launch_bounds__(256) gated_residual_kernel(const float* __restrict__ x, const float* __restrict__ a,
+                                                             const float* __restrict__ ga, const float* __restrict__ b,
+                                                             const float* __restrict__ gb, int rows, int D,
+                                                             float* __restrict__ out, float* __restrict__ trace) {
+    const int64_t n = static_cast<int64_t>(rows) * D;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int d = static_cast<int>(i % D);
+        float contrib = ga ? __fmul_rn(a[i], __ldg(ga + d)) : a[i];
+        if (b) contrib = __fadd_rn(contrib, __fmul_rn(b[i], __ldg(gb + d)));
+        const float v = __fadd_rn(x[i], contrib);
+        out[i] = v;
+        if (trace) trace[i] = v;
+    }
+}
+
+__global__ void advance_positions_kernel(int32_t* positions, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < rows) positions[r] += 1;
+}
+
+// ---- state layout ----------------------------------------------------------------------------------------------
+struct BlockState {
+    float* ring;
+    float* ssm;
+    float* k_cache;
+    float* v_cache;
+};
+
+struct StateLayout {
+    int32_t* positions;
+    BlockState block[TBL_MAX_DECODE_BLOCKS];
+    size_t bytes;
+};
+
+StateLayout carve_state(const tbl_decode_model& m, int batch, int capacity, void* base) {
+    StateLayout L{};
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { uint8_t* r = p + off; off += round_up(bytes, 256); return r; };
+    L.positions = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * batch));
+    for (int i = 0; i < m.n_blocks; ++i) {
+        const tbl_decode_block& b = m.blocks[i];
+        const int conv_dim = b.mamba.d_inner + 2 * b.mamba.n_groups * b.mamba.d_state;
+        const int taps = b.mamba.conv_kernel > 1 ? b.mamba.conv_kernel - 1 : 0;
+        L.block[i].ring = reinterpret_cast<float*>(take(sizeof(float) * batch * (taps ? taps : 1) * conv_dim));
+        L.block[i].ssm = reinterpret_cast<float*>(take(sizeof(float) * batch * static_cast<size_t>(b.mamba.d_inner) * b.mamba.d_state));
+        if (b.hybrid) {
+            const size_t kv = sizeof(float) * batch * static_cast<size_t>(capacity) * b.attn.n_kv_heads * b.attn.head_dim;
+            L.block[i].k_cache = reinterpret_cast<float*>(take(kv));
+            L.block[i].v_cache = reinterpret_cast<float*>(take(kv));
+        }
+    }
+    L.bytes = off;
+    return L;
+}
+
+int check_model(const tbl_decode_model* m, int batch, int capacity) {
+    if (!m || !m->blocks || !m->embedding || batch <= 0 || capacity <= 0) return TBL_ERR_INVALID_ARG;
+    if (m->n_blocks <= 0 || m->n_blocks > TBL_MAX_DECODE_BLOCKS || m->d_model <= 0 || m->vocab <= 0) return TBL_ERR_INVALID_ARG;
+    for (int i = 0; i < m->n_blocks; ++i) {
+        const tbl_decode_block& b = m->blocks[i];
+        const tbl_mamba_block& mm = b.mamba;
+        if (mm.d_inner <= 0 || mm.n_heads <= 0 || mm.d_head <= 0 || mm.n_groups <= 0 || mm.d_state <= 0 ||
+            mm.conv_kernel < 1 || mm.n_heads * mm.d_head != mm.d_inner || mm.n_heads % mm.n_groups)
+            return TBL_ERR_SHAPE;
+        if (!mm.A_log || !mm.D || !mm.conv_w || !mm.conv_b) return TBL_ERR_INVALID_ARG;
+        const int GS = mm.n_groups * mm.d_state;
+        if (mm.x.inputs != m->d_model || mm.x.outputs != mm.d_inner || mm.z.outputs != mm.d_inner || mm.B.outputs != GS ||
+            mm.C.outputs != GS || mm.dt.outputs != mm.n_heads || mm.out.inputs != mm.d_inner || mm.out.outputs != m->d_model)
+            return TBL_ERR_SHAPE;
+        if (b.hybrid) {
+            const tbl_attention_block& a = b.attn;
+            if (a.n_heads <= 0 || a.n_kv_heads <= 0 || a.head_dim <= 0 || a.head_dim % 4 || a.n_heads * a.head_dim != m->d_model ||
+                a.sliding_window <= 0 || !a.rope_cos || !a.rope_sin || a.rope_positions <= 0)
+                return TBL_ERR_SHAPE;
+            if (a.q.outputs != m->d_model || a.kv.outputs != 2 * a.n_kv_heads * a.head_dim || a.out.inputs != m->d_model)
+                return TBL_ERR_SHAPE;
+            if (!b.mamba_gate || !b.attn_gate || !b.ffn_gate) return TBL_ERR_INVALID_ARG;
+            if (b.ffn_up.inputs != m->d_model || b.ffn_down.inputs != b.ffn_up.outputs || b.ffn_down.outputs != m->d_model)
+                return TBL_ERR_SHAPE;
+        }
+    }
+    if (m->head.inputs != m->d_model || m->head.outputs != m->vocab) return TBL_ERR_SHAPE;
+    return TBL_OK;
+}
+
+struct Scratch {
+    float *hidden[2], *core, *attn_in, *proj, *xbc, *y, *gated, *mamba_out, *qkv, *heads, *attn_out, *res, *ffn_in, *ffn_out;
+    void* lin;
+    size_t lin_bytes, proj_stride, qkv_stride, bytes;
+};
+
+Scratch carve_scratch(const tbl_decode_model& m, int batch, void* base) {
+    Scratch S{};
+    uint8_t* p = static_cast<uint8_t*>(base);
+    size_t off = 0;
+    auto take = [&](size_t floats) { float* r = reinterpret_cast<float*>(p + off); off += round_up(floats * sizeof(float), 256); return r; };
+    int max_inner = 1, max_conv = 1, max_kvout = 1, max_ffn = 1;
+    size_t lin = 0;
+    auto want = [&](size_t b) { lin = b > lin ? b : lin; };
+    const int D = m.d_model;
+    for (int i = 0; i < m.n_blocks; ++i) {
+        const tbl_decode_block& b = m.blocks[i];
+        max_inner = b.mamba.d_inner > max_inner ? b.mamba.d_inner : max_inner;
+        const int conv_dim = b.mamba.d_inner + 2 * b.mamba.n_groups * b.mamba.d_state;
+        max_conv = conv_dim > max_conv ? conv_dim : max_conv;
+        want(tbl_grouped_rows_workspace_bytes(5, batch < 64 ? batch : 64, D));
+        want(tbl_linear_workspace_bytes(batch, D, b.mamba.d_inner));
+        want(tbl_linear_workspace_bytes(batch, b.mamba.d_inner, D));
+        if (b.hybrid) {
+            max_kvout = b.attn.kv.outputs > max_kvout ? b.attn.kv.outputs : max_kvout;
+            max_kvout = D > max_kvout ? D : max_kvout;
+            max_ffn = b.ffn_up.outputs > max_ffn ? b.ffn_up.outputs : max_ffn;
+            tbl_linear_view pair[2] = {b.ffn_up, b.ffn_down};
+            want(tbl_chain_workspace_bytes(pair, 2, batch));
+            want(tbl_linear_workspace_bytes(batch, D, D));
+        }
+    }
+    want(tbl_linear_workspace_bytes(batch, D, m.vocab));
+    const size_t BD = static_cast<size_t>(batch) * D;
+    S.hidden[0] = take(BD); S.hidden[1] = take(BD);
+    S.core = take(BD); S.attn_in = take(BD);
+    S.proj_stride = static_cast<size_t>(batch) * max_inner;
+    S.proj = take(5 * S.proj_stride);
+    S.xbc = take(static_cast<size_t>(batch) * max_conv);
+    S.y = take(static_cast<size_t>(batch) * max_inner);
+    S.gated = take(static_cast<size_t>(batch) * max_inner);
+    S.mamba_out = take(BD);
+    S.qkv_stride = static_cast<size_t>(batch) * max_kvout;
+    S.qkv = take(2 * S.qkv_stride);
+    S.heads = take(BD); S.attn_out = take(BD); S.res = take(BD); S.ffn_in = take(BD); S.ffn_out = take(BD);
+    (void)max_ffn;
+    S.lin = p + off;
+    S.lin_bytes = round_up(lin, 256);
+    off += S.lin_bytes;
+    S.bytes = off;
+    return S;
+}
+
+}  // namespace
+}  // namespace tbl
+
+using namespace tbl;
+
+extern "C" {
+
+int tbl_embedding_gather(const int32_t* ids_dev, int count, const float* table_dev, int vocab, int dim, float* out_dev,
+                         void* stream) {
+    if (!ids_dev || !table_dev || !out_dev || count <= 0 || vocab <= 0 || dim <= 0) return TBL_ERR_INVALID_ARG;
+    embedding_gather_kernel<<<count, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids_dev, table_dev, vocab, dim, out_dev, nullptr);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+int tbl_mamba_conv_step(const float* x_dev, const float* B_dev, const float* C_dev, const float* conv_w_dev,
+                        const float* conv_b_dev, float* ring_dev, float* xbc_dev, int d_inner, int group_state,
+                        int conv_kernel, int rows, void* stream) {
+    if (!x_dev || !B_dev || !C_dev || !conv_w_dev || !conv_b_dev || !ring_dev || !xbc_dev) return TBL_ERR_INVALID_ARG;
+    if (d_inner <= 0 || group_state <= 0 || conv_kernel < 1 || rows <= 0) return TBL_ERR_INVALID_ARG;
+    const int conv_dim = d_inner + 2 * group_state;
+    mamba_conv_step_kernel<<<dim3((conv_dim + 255) / 256, rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x_dev, B_dev, C_dev, conv_w_dev, conv_b_dev, ring_dev, d_inner, group_state, conv_kernel, xbc_dev);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+int tbl_mamba_ssd_step(const float* xbc_dev, const float* dt_dev, const float* A_log_dev, const float* D_dev,
+                       float* state_dev, float* y_dev, int n_heads, int d_head, int d_state, int n_groups, int rows,
+                       void* stream) {
+    if (!xbc_dev || !dt_dev || !A_log_dev || !D_dev || !state_dev || !y_dev) return TBL_ERR_INVALID_ARG;
+    if (n_heads <= 0 || d_head <= 0 || d_state <= 0 || n_groups <= 0 || n_heads % n_groups || rows <= 0) return TBL_ERR_INVALID_ARG;
+    mamba_ssd_step_kernel<<<dim3((n_heads * d_head + 127) / 128, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        xbc_dev, dt_dev, A_log_dev, D_dev, state_dev, n_heads, d_head, d_state, n_groups, y_dev);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+int tbl_attention_decode(const float* q_dev, const float* kv_dev, float* k_cache_dev, float* v_cache_dev, int capacity,
+                         const int32_t* positions_dev, const float* rope_cos_dev, const float* rope_sin_dev,
+                         int rope_positions, int n_heads, int n_kv_heads, int head_dim, int sliding_window, int rows,
+                         float* out_dev, void* stream) {
+    if (!q_dev || !kv_dev || !k_cache_dev || !v_cache_dev || !positions_dev || !rope_cos_dev || !rope_sin_dev || !out_dev)
+        return TBL_ERR_INVALID_ARG;
+    if (capacity <= 0 || rope_positions <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || head_dim % 4 ||
+        sliding_window <= 0 || rows <= 0)
+        return TBL_ERR_INVALID_ARG;
+    const size_t smem = sizeof(float) * (3 * head_dim + kAttnThreads + capacity);
+    if (smem > 200 * 1024) return TBL_ERR_SHAPE;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return TBL_ERR_CUDA;
+    int* status = device_status_ptr();
+    if (!status) return TBL_ERR_CUDA;
+    attention_decode_kernel<<<dim3(n_heads, rows), kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        q_dev, kv_dev, k_cache_dev, v_cache_dev, capacity, positions_dev, rope_cos_dev, rope_sin_dev, rope_positions, n_heads,
+        n_kv_heads, head_dim, sliding_window, out_dev, status);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+int tbl_gated_residual(const float* x_dev, const float* a_dev, const float* gate_a_dev, const float* b_dev,
+                       const float* gate_b_dev, int rows, int dim, float* out_dev, void* stream) {
+    if (!x_dev || !a_dev || !out_dev || rows <= 0 || dim <= 0 || (b_dev && !gate_b_dev)) return TBL_ERR_INVALID_ARG;
+    const int64_t n = static_cast<int64_t>(rows) * dim;
+    const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    gated_residual_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x_dev, a_dev, gate_a_dev, b_dev, gate_b_dev, rows,
+                                                                               dim, out_dev, nullptr);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+size_t tbl_decode_state_bytes(const tbl_decode_model* model, int batch, int capacity) {
+    if (check_model(model, batch, capacity) != TBL_OK) return 0;
+    return carve_state(*model, batch, capacity, nullptr).bytes;
+}
+
+int tbl_decode_state_reset(const tbl_decode_model* model, int batch, int capacity, void* state_dev, size_t state_bytes,
+                           void* stream) {
+    const int rc = check_model(model, batch, capacity);
+    if (rc != TBL_OK) return rc;
+    if (!state_dev || state_bytes < tbl_decode_state_bytes(model, batch, capacity)) return TBL_ERR_WORKSPACE;
+    const StateLayout L = carve_state(*model, batch, capacity, state_dev);
+    // positions, conv rings and SSM states start at zero; the KV caches are only read below the positions
+    const size_t head = reinterpret_cast<uint8_t*>(L.block[0].ring) - static_cast<uint8_t*>(state_dev);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(state_dev, 0, head, st) != cudaSuccess) return TBL_ERR_CUDA;
+    for (int i = 0; i < model->n_blocks; ++i) {
+        const tbl_mamba_block& mm = model->blocks[i].mamba;
+        const int conv_dim = mm.d_inner + 2 * mm.n_groups * mm.d_state;
+        const int taps = mm.conv_kernel > 1 ? mm.conv_kernel - 1 : 1;
+        if (cudaMemsetAsync(L.block[i].ring, 0, sizeof(float) * batch * taps * conv_dim, st) != cudaSuccess) return TBL_ERR_CUDA;
+        if (cudaMemsetAsync(L.block[i].ssm, 0, sizeof(float) * batch * static_cast<size_t>(mm.d_inner) * mm.d_state, st) != cudaSuccess)
+            return TBL_ERR_CUDA;
+    }
+    return TBL_OK;
+}
+
+size_t tbl_decode_workspace_bytes(const tbl_decode_model* model, int batch) {
+    if (check_model(model, batch, 1) != TBL_OK) return 0;
+    return carve_scratch(*model, batch, nullptr).bytes;
+}
+
+int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void* state_dev, const int32_t* token_ids_dev,
+                    float* logits_dev, float* hidden_trace_dev, void* workspace_dev, size_t workspace_bytes, void* stream) {
+    int rc = check_model(model, batch, capacity);
+    if (rc != TBL_OK) return rc;
+    if (!state_dev || !token_ids_dev || !logits_dev) return TBL_ERR_INVALID_ARG;
+    if (!workspace_dev || workspace_bytes < tbl_decode_workspace_bytes(model, batch)) return TBL_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace_dev) & 255) || (reinterpret_cast<uintptr_t>(state_dev) & 255)) return TBL_ERR_ALIGNMENT;
+    const tbl_decode_model& m = *model;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const StateLayout state = carve_state(m, batch, capacity, state_dev);
+    const Scratch S = carve_scratch(m, batch, workspace_dev);
+    int* status = device_status_ptr();
+    if (!status) return TBL_ERR_CUDA;
+    const int D = m.d_model, B = batch;
+    const size_t BD = static_cast<size_t>(B) * D;
+    auto launched = [&]() { note_launch(); return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA; };
+    auto linear = [&](const tbl_linear_view& v, const float* x, float* y) {
+        return tbl_linear_forward(x, v.packed, v.strips, B > 64 ? v.w_i8 : nullptr, v.weight_scale, B, v.inputs, v.outputs,
+                                  v.activation_bits, v.rms_input ? TBL_RMS_FAST : TBL_RMS_NONE, v.magnitude, v.bias, y,
+                                  S.lin, S.lin_bytes, stream);
+    };
+    auto group = [&](const tbl_linear_view* views, int count, const float* x, float* out, size_t stride) {
+        if (B <= 64) return tbl_grouped_forward_rows(views, count, x, B, out, static_cast<long long>(stride), TBL_RMS_NONE,
+                                                      S.lin, S.lin_bytes, stream);
+        for (int g = 0; g < count; ++g) {
+            const int r = linear(views[g], x, out + g * stride);
+            if (r != TBL_OK) return r;
+        }
+        return TBL_OK;
+    };
+    auto norm = [&](const float* x, const float* w, float eps, float* out) {
+        return tbl_row_norm(x, nullptr, w, B, D, eps, out, 8, nullptr, nullptr, nullptr, stream);
+    };
+    auto residual = [&](const float* x, const float* a, const float* ga, const float* b, const float* gb, float* out, float* trace) {
+        const int64_t n = static_cast<int64_t>(BD);
+        const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+        gated_residual_kernel<<<grid, 256, 0, st>>>(x, a, ga, b, gb, B, D, out, trace);
+        return launched();
+    };
+
+    embedding_gather_kernel<<<B, 256, 0, st>>>(token_ids_dev, m.embedding, m.vocab, D, S.hidden[0], hidden_trace_dev);
+    if ((rc = launched()) != TBL_OK) return rc;
+    int cur = 0;
+    for (int i = 0; i < m.n_blocks; ++i) {
+        const tbl_decode_block& b = m.blocks[i];
+        const tbl_mamba_block& mm = b.mamba;
+        const float* h = S.hidden[cur];
+        float* trace = hidden_trace_dev ? hidden_trace_dev + (static_cast<size_t>(i) + 1) * BD : nullptr;
+        if ((rc = norm(h, b.core_norm_w, b.core_norm_eps, S.core)) != TBL_OK) return rc;
+        // Mamba-2 branch: five projections of the normalised row, conv step, SSD step, gated norm, out projection
+        const tbl_linear_view proj[5] = {mm.x, mm.z, mm.B, mm.C, mm.dt};
+        if ((rc = group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK) return rc;
+        const int GS = mm.n_groups * mm.d_state, conv_dim = mm.d_inner + 2 * GS;
+        mamba_conv_step_kernel<<<dim3((conv_dim + 255) / 256, B), 256, 0, st>>>(
+            S.proj, S.proj + 2 * S.proj_stride, S.proj + 3 * S.proj_stride, mm.conv_w, mm.conv_b, state.block[i].ring,
+            mm.d_inner, GS, mm.conv_kernel, S.xbc);
+        if ((rc = launched()) != TBL_OK) return rc;
+        mamba_ssd_step_kernel<<<dim3((mm.d_inner + 127) / 128, B), 128, 0, st>>>(
+            S.xbc, S.proj + 4 * S.proj_stride, mm.A_log, mm.D, state.block[i].ssm, mm.n_heads, mm.d_head, mm.d_state,
+            mm.n_groups, S.y);
+        if ((rc = launched()) != TBL_OK) return rc;
+        rc = tbl_row_norm(S.y, S.proj + S.proj_stride, mm.norm_w, B, mm.d_inner, mm.norm_eps, S.gated, 8, nullptr, nullptr,
+                          nullptr, stream);
+        if (rc != TBL_OK) return rc;
+        if ((rc = linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
+        if (!b.hybrid) {
+            if ((rc = residual(h, S.mamba_out, nullptr, nullptr, nullptr, S.hidden[cur ^ 1], trace)) != TBL_OK) return rc;
+            cur ^= 1;
+            continue;
+        }
+        // attention branch on its own norm of the same residual stream
+        const tbl_attention_block& a = b.attn;
+        if ((rc = norm(h, b.attn_norm_w, b.core_norm_eps, S.attn_in)) != TBL_OK) return rc;
+        const tbl_linear_view qkv[2] = {a.q, a.kv};
+        if ((rc = group(qkv, 2, S.attn_in, S.qkv, S.qkv_stride)) != TBL_OK) return rc;
+        const size_t attn_smem = sizeof(float) * (3 * a.head_dim + kAttnThreads + capacity);
+        if (attn_smem > 200 * 1024) return TBL_ERR_SHAPE;
+        if (attn_smem > 48 * 1024) {
+            static bool configured[64] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev < 0 || dev >= 64 || !configured[dev]) {
+                if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+                    return TBL_ERR_CUDA;
+                if (dev >= 0 && dev < 64) configured[dev] = true;
+            }
+        }
+        attention_decode_kernel<<<dim3(a.n_heads, B), kAttnThreads, attn_smem, st>>>(
+            S.qkv, S.qkv + S.qkv_stride, state.block[i].k_cache, state.block[i].v_cache, capacity, state.positions,
+            a.rope_cos, a.rope_sin, a.rope_positions, a.n_heads, a.n_kv_heads, a.head_dim, a.sliding_window, S.heads, status);
+        if ((rc = launched()) != TBL_OK) return rc;
+        if ((rc = linear(a.out, S.heads, S.attn_out)) != TBL_OK) return rc;
+        if ((rc = residual(h, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, S.res, nullptr)) != TBL_OK) return rc;
+        // FFN: norm -> up -> squared ReLU -> down, as one stack
+        if ((rc = norm(S.res, b.ff_norm_w, 1e-5f, S.ffn_in)) != TBL_OK) return rc;
+        const tbl_linear_view ffn[2] = {b.ffn_up, b.ffn_down};
+        const int relu[2] = {1, 0};
+        if ((rc = tbl_chain_forward(ffn, 2, relu, S.ffn_in, B, TBL_RMS_FAST, S.ffn_out, S.lin, S.lin_bytes, stream)) != TBL_OK) return rc;
+        if ((rc = residual(S.res, S.ffn_out, b.ffn_gate, nullptr, nullptr, S.hidden[cur ^ 1], trace)) != TBL_OK) return rc;
+        cur ^= 1;
+    }
+    if ((rc = norm(S.hidden[cur], m.final_norm_w, m.final_norm_eps, S.core)) != TBL_OK) return rc;
+    if ((rc = linear(m.head, S.core, logits_dev)) != TBL_OK) return rc;
+    advance_positions_kernel<<<(B + 127) / 128, 128, 0, st>>>(state.positions, B);
+    return launched();
+}
+
+}  // extern "C"

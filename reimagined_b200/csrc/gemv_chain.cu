@@ -9,12 +9,13 @@
 // at a grid-wide barrier and quantise the new activation row, the first stages of layer l+1 are already
 // landing.  The weight stream of the whole stack is one uninterrupted front-to-back sweep of HBM.
 //
-// Layer boundary (consumer warps only): epilogue writes y_l to global memory and publishes max|y_l| per row
-// with one atomicMax per CTA (max is exact in any order, so the next quantiser's scale is bit-identical to a
-// separate absmax pass) -> arrive on the layer's counter -> bounded spin until all CTAs have arrived -> load
-// the row (L2-resident), quantise it straight into shared memory.  The grid must be co-resident: the kernel is
-// launched cooperatively.  Every wait is bounded; a wait that gives up sets TBL_DEV_WAIT_TIMEOUT and the CTA
-// leaves.
+// Layer boundary (consumer warps only).  The epilogue warp of each strip stores its 16 outputs per row,
+// publishes their maxima with atomicMax (max is exact in any order, so the next quantiser's scale is bit-identical
+// to a separate absmax pass), fences and counts its strip as arrived -- per warp, with no CTA-wide barrier, so
+// the round trips of the seven strips of a CTA overlap.  The quantiser of the next layer polls the counter
+// (bounded) until all strips have arrived, reads the row (L2-resident) and quantises it straight into shared
+// memory.  The grid must be co-resident: the kernel is launched cooperatively.  Every wait is bounded; a wait
+// that gives up sets TBL_DEV_WAIT_TIMEOUT and the CTA leaves.
 //
 // Weight layout, stage layout, widening and the MMA are those of gemv_strip.cu (strips of 16 rows, 1 KB
 // blocks, slab-major order, mma.sync.m16n8k32.u8.s8 with the weights as the A operand).
@@ -41,8 +42,8 @@ struct ChainParams {
     const float* x;        // [rows, K_0]
     float* y;              // [rows, N_last]
     float* act[2];         // ping-pong activations between layers, [rows, width]
-    unsigned* arrived;     // [count] arrival counters, zero at launch
-    unsigned* amax;        // [count + 1][8] row absmax bit patterns of each layer's input, zero at launch
+    unsigned* sync;        // [count][16]: word 0 = strips of the layer that have arrived, words 1..8 = bit patterns of
+                           // the row maxima of the layer's output; zero at launch
     int ks, stage_shift, stages, slots_max, acts_bytes;
     int* status;
     unsigned long long* trace;   // profiling aid: [cta][layer][8] nanosecond stamps, or null
@@ -68,22 +69,59 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     return v;
 }
 
+__device__ __forceinline__ uint2 ld_acquire_gpu_v2(const unsigned* p) {
+    uint2 v;
+    asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory"); }
 
-// Per-token absmax quantiser of rows*K <= 16384 inputs into the resident interleaved shared-memory copy.
-// Same arithmetic as the stand-alone quantiser.  known_amax != nullptr: the row maxima were published by the
-// producer of x (bit patterns), so the absmax reduction is skipped.
-__device__ __forceinline__ void quantise_resident(const float* __restrict__ x, const int R, const int K,
-                                                  const bool rms_fast, const float q_max,
-                                                  const unsigned* known_amax, const bool first_layer,
-                                                  uint8_t* acts_resident, float* s_scale, int* s_qsum, float* s_red,
-                                                  uint32_t* s_amax) {
+// Shared-memory state of the consumer warps.  The per-row scale and code sum are double-buffered by layer parity:
+// the epilogue warps of layer l may still read theirs while the quantiser of layer l+1 fills the other copy.
+struct ConsumerState {
+    float scale[2][kMaxRows];
+    int qsum[2][kMaxRows];
+    float red[kConsumers * kMaxRows];
+    uint32_t amax[kMaxRows];      // local absmax reduction (first layer)
+    uint32_t pub[kMaxRows];       // row maxima published by the previous layer's epilogue warps
+    int ok;
+};
+static_assert(sizeof(ConsumerState) <= kStateBytes, "consumer state must fit its slot");
+
+// Per-token absmax quantiser of rows*K <= 16384 inputs into the resident interleaved shared-memory copy; same
+// arithmetic as the stand-alone quantiser.  `sync` != null: x is the previous layer's output; it is complete when
+// that layer's arrival counter reaches `target`, and its row maxima are final then, so no absmax pass is needed.
+// Returns false when a bounded wait gave up (status word set).
+template <bool SINGLE>
+__device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, const int R, const int K,
+                                                  const bool rms_fast, const float q_max, const unsigned* sync,
+                                                  const unsigned target, const bool first_layer, const int par,
+                                                  uint8_t* acts_resident, ConsumerState* cs, int* status,
+                                                  unsigned long long* trace) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_groups = R * K / 16;
+    constexpr int kRows = SINGLE ? 1 : kMaxRows;
     if (threadIdx.x < kMaxRows) {
-        s_qsum[threadIdx.x] = 0;
-        s_amax[threadIdx.x] = 0u;
+        cs->qsum[par][threadIdx.x] = 0;
+        cs->amax[threadIdx.x] = 0u;
     }
+    if (sync) {
+        if (static_cast<int>(threadIdx.x) < R) {
+            bool ok = false;
+            unsigned value = 0u;
+            for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+                const uint2 v = ld_acquire_gpu_v2(sync);
+                if (v.x >= target) { ok = true; value = v.y; break; }
+            }
+            if (ok && threadIdx.x > 0) value = ld_acquire_gpu(sync + 1 + threadIdx.x);
+            if (!ok) { atomicOr(status, TBL_DEV_WAIT_TIMEOUT); cs->ok = 0; }
+            cs->pub[threadIdx.x] = value;
+        }
+        bar_consumers();     // every consumer warp has left the previous layer; maxima and zeroed sums visible
+        if (*reinterpret_cast<volatile int*>(&cs->ok) == 0) return false;
+    }
+    if (trace && threadIdx.x == 0) trace[1] = global_ns();
     float4 xv[kGroups][4];
     int grow[kGroups];
 #pragma unroll
@@ -93,8 +131,10 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
         if (Gl < total_groups) {
             const int e = Gl * 16;
             int row = 0;
+            if (!SINGLE) {
 #pragma unroll
-            for (int m = 1; m < kMaxRows; ++m) row += e >= m * K ? 1 : 0;
+                for (int m = 1; m < kMaxRows; ++m) row += e >= m * K ? 1 : 0;
+            }
             grow[i] = row;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = __ldcg(reinterpret_cast<const float4*>(x + e + 4 * q4));
@@ -105,17 +145,18 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
     }
     // first layer only: the producer warp starts queueing weight copies once these loads are in flight
     if (first_layer) asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
-    unsigned pub[kMaxRows];
+    if (!sync) bar_consumers();     // zeroed sums visible (later layers passed a barrier above)
+    if (trace && threadIdx.x == 0) {
+        asm volatile("" ::"f"(xv[kGroups - 1][3].w), "f"(xv[0][0].x));
+        trace[7] = global_ns();
+    }
+    float inv[kRows];
 #pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) pub[m] = (known_amax && m < R) ? __ldcg(known_amax + m) : 0u;
-    bar_consumers();     // s_qsum / s_amax cleared
-    float inv[kMaxRows];
-#pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) inv[m] = 1.0f;
+    for (int m = 0; m < kRows; ++m) inv[m] = 1.0f;
     if (rms_fast) {
-        float ss[kMaxRows];
+        float ss[kRows];
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) ss[m] = 0.0f;
+        for (int m = 0; m < kRows; ++m) ss[m] = 0.0f;
 #pragma unroll
         for (int i = 0; i < kGroups; ++i) {
             float q = 0.0f;
@@ -123,22 +164,22 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
             for (int q4 = 0; q4 < 4; ++q4)
                 q += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
 #pragma unroll
-            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) ss[m] += q;
+            for (int m = 0; m < kRows; ++m) if (grow[i] == m) ss[m] += q;
         }
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) {
+        for (int m = 0; m < kRows; ++m) {
             if (m < R) {
 #pragma unroll
                 for (int o = 16; o; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
-                if (lane == 0) s_red[warp * kMaxRows + m] = ss[m];
+                if (lane == 0) cs->red[warp * kMaxRows + m] = ss[m];
             }
         }
         bar_consumers();
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) {
+        for (int m = 0; m < kRows; ++m) {
             if (m < R) {
-                float r = s_red[m];
-                for (int w = 1; w < kConsumers; ++w) r += s_red[w * kMaxRows + m];
+                float r = cs->red[m];
+                for (int w = 1; w < kConsumers; ++w) r += cs->red[w * kMaxRows + m];
                 inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(r, static_cast<float>(K)), 1e-6f)));
             }
         }
@@ -146,7 +187,7 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
         for (int i = 0; i < kGroups; ++i) {
             float f = 1.0f;
 #pragma unroll
-            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) f = inv[m];
+            for (int m = 0; m < kRows; ++m) if (grow[i] == m) f = inv[m];
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
                 xv[i][q4].x = __fmul_rn(xv[i][q4].x, f); xv[i][q4].y = __fmul_rn(xv[i][q4].y, f);
@@ -154,15 +195,15 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
             }
         }
     }
-    float amax[kMaxRows];
-    if (known_amax) {
+    float amax[kRows];
+    if (sync) {
         // max_k fl(|x_k| * inv) == fl(max_k |x_k| * inv): rounding is monotone
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) amax[m] = __fmul_rn(__uint_as_float(pub[m]), inv[m]);
+        for (int m = 0; m < kRows; ++m) amax[m] = m < R ? __fmul_rn(__uint_as_float(cs->pub[m]), inv[m]) : 0.0f;
     } else {
-        float mx[kMaxRows];
+        float mx[kRows];
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) mx[m] = 0.0f;
+        for (int m = 0; m < kRows; ++m) mx[m] = 0.0f;
 #pragma unroll
         for (int i = 0; i < kGroups; ++i) {
             float q = 0.0f;
@@ -170,29 +211,29 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
             for (int q4 = 0; q4 < 4; ++q4)
                 q = fmaxf(q, fmaxf(fmaxf(fabsf(xv[i][q4].x), fabsf(xv[i][q4].y)), fmaxf(fabsf(xv[i][q4].z), fabsf(xv[i][q4].w))));
 #pragma unroll
-            for (int m = 0; m < kMaxRows; ++m) if (grow[i] == m) mx[m] = fmaxf(mx[m], q);
+            for (int m = 0; m < kRows; ++m) if (grow[i] == m) mx[m] = fmaxf(mx[m], q);
         }
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) {
+        for (int m = 0; m < kRows; ++m) {
             if (m < R) {
                 const uint32_t wmax = __reduce_max_sync(0xffffffffu, __float_as_uint(mx[m]));
-                if (lane == 0 && wmax != 0u) atomicMax(&s_amax[m], wmax);
+                if (lane == 0 && wmax != 0u) atomicMax(&cs->amax[m], wmax);
             }
         }
         bar_consumers();
 #pragma unroll
-        for (int m = 0; m < kMaxRows; ++m) amax[m] = m < R ? __uint_as_float(s_amax[m]) : 0.0f;
+        for (int m = 0; m < kRows; ++m) amax[m] = m < R ? __uint_as_float(cs->amax[m]) : 0.0f;
     }
-    int qsum[kMaxRows];
+    int qsum[kRows];
 #pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) qsum[m] = 0;
+    for (int m = 0; m < kRows; ++m) qsum[m] = 0;
 #pragma unroll
     for (int i = 0; i < kGroups; ++i) {
         if (grow[i] >= 0) {
             const int m = grow[i];
-            float am = 0.0f;
+            float am = amax[0];
 #pragma unroll
-            for (int r = 0; r < kMaxRows; ++r) if (m == r) am = amax[r];
+            for (int r = 1; r < kRows; ++r) if (m == r) am = amax[r];
             const float scale = __fdiv_rn(q_max, __fadd_rn(am, 1e-8f));
             uint32_t wds[4];
 #pragma unroll
@@ -204,7 +245,7 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
                 wds[q4] = __byte_perm(__byte_perm(c0, c1, 0x0040), __byte_perm(c2, c3, 0x0040), 0x5410);
                 const int s4 = dp4a_ss(static_cast<int>(wds[q4]), 0x01010101, 0);
 #pragma unroll
-                for (int r = 0; r < kMaxRows; ++r) if (m == r) qsum[r] += s4;
+                for (int r = 0; r < kRows; ++r) if (m == r) qsum[r] += s4;
             }
             const int e = (threadIdx.x + i * kT) * 16;
             const uint4 codes = transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
@@ -212,19 +253,20 @@ __device__ __forceinline__ void quantise_resident(const float* __restrict__ x, c
         }
     }
 #pragma unroll
-    for (int m = 0; m < kMaxRows; ++m) {
+    for (int m = 0; m < kRows; ++m) {
         if (m < R) {
             const int wsum = __reduce_add_sync(0xffffffffu, qsum[m]);
-            if (lane == 0 && wsum != 0) atomicAdd(&s_qsum[m], wsum);
+            if (lane == 0 && wsum != 0) atomicAdd(&cs->qsum[par][m], wsum);
         }
     }
     if (static_cast<int>(threadIdx.x) < R) {
-        float am = 0.0f;
+        float am = amax[0];
 #pragma unroll
-        for (int r = 0; r < kMaxRows; ++r) if (static_cast<int>(threadIdx.x) == r) am = amax[r];
-        s_scale[threadIdx.x] = __fdiv_rn(__fadd_rn(am, 1e-8f), q_max);
+        for (int r = 1; r < kRows; ++r) if (static_cast<int>(threadIdx.x) == r) am = amax[r];
+        cs->scale[par][threadIdx.x] = __fdiv_rn(__fadd_rn(am, 1e-8f), q_max);
     }
     bar_consumers();
+    return true;
 }
 
 __global__ void __launch_bounds__((kConsumers + 1) * 32, 1)
@@ -236,12 +278,7 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
     int* reduce_buf = reinterpret_cast<int*>(smem + 128);
-    float* s_scale = reinterpret_cast<float*>(smem + 128 + kReduceBytes);
-    int* s_qsum = reinterpret_cast<int*>(s_scale + 8);
-    float* s_red = s_scale + 16;
-    uint32_t* s_amax = reinterpret_cast<uint32_t*>(s_red + kConsumers * kMaxRows);
-    uint32_t* s_outmax = s_amax + 8;
-    int* s_ok = reinterpret_cast<int*>(s_outmax + 8);
+    ConsumerState* cs = reinterpret_cast<ConsumerState*>(smem + 128 + kReduceBytes);
     uint8_t* acts_resident = smem + 128 + kReduceBytes + kStateBytes;
     uint8_t* stage_base = acts_resident + P.acts_bytes;
     const uint32_t stage_base_addr = smem_u32(stage_base);
@@ -260,9 +297,8 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
         }
         fence_mbar_init();
         fence_proxy_async();
+        cs->ok = 1;
     }
-    if (threadIdx.x < 8) s_outmax[threadIdx.x] = 0u;
-    if (threadIdx.x == 0) *s_ok = 1;
     __syncthreads();
 
     const bool producer = warp == kConsumers;
@@ -290,6 +326,7 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
         const int nblk = K >> 8;
         const int ksteps = (nblk + nblk_stage - 1) >> P.stage_shift;
         const bool fast = R == 1 && nblk_stage == 8 && (K & 2047) == 0;
+        const int par = l & 1;
 
         if (producer) {
             for (int s = s_begin; s < s_end && alive;) {
@@ -320,7 +357,6 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                     }
                 }
             }
-            if (lane == 0) stamp(l, 7);
             continue;
         }
 
@@ -329,24 +365,19 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
         float* yout = l == P.count - 1 ? P.y : P.act[l & 1];
         const bool has_work = s_begin < s_end;
         if (threadIdx.x == 0) stamp(l, 0);
-        if (l > 0 && has_work) {
-            // every CTA has written its part of the previous layer's output
-            if (threadIdx.x == 0) {
-                bool ok = false;
-                for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
-                    if (ld_acquire_gpu(P.arrived + (l - 1)) >= static_cast<unsigned>(G)) { ok = true; break; }
-                }
-                if (!ok) { atomicOr(P.status, TBL_DEV_WAIT_TIMEOUT); *s_ok = 0; }
-            }
-            bar_consumers();
-            if (*reinterpret_cast<volatile int*>(s_ok) == 0) { alive = false; break; }
-        }
-        if (threadIdx.x == 0) stamp(l, 1);
-        if (has_work)
-            quantise_resident(xin, R, K, L.rms_fast != 0, L.q_max, l > 0 ? P.amax + l * 8 : nullptr, l == 0,
-                              acts_resident, s_scale, s_qsum, s_red, s_amax);
-        else if (l == 0)
+        if (has_work) {
+            unsigned long long* tr = P.trace ? P.trace + (static_cast<size_t>(bid) * P.count + l) * 8 : nullptr;
+            const unsigned* sync = l > 0 ? P.sync + (l - 1) * 16 : nullptr;
+            const unsigned target = l > 0 ? static_cast<unsigned>((P.layer[l - 1].N + 15) >> 4) : 0u;
+            const bool ok = R == 1
+                ? quantise_resident<true>(xin, R, K, L.rms_fast != 0, L.q_max, sync, target, l == 0, par, acts_resident,
+                                          cs, P.status, tr)
+                : quantise_resident<false>(xin, R, K, L.rms_fast != 0, L.q_max, sync, target, l == 0, par, acts_resident,
+                                           cs, P.status, tr);
+            if (!ok) { alive = false; break; }
+        } else if (l == 0) {
             asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
+        }
         if (threadIdx.x == 0) stamp(l, 2);
         bool first_stage = true;
 
@@ -471,43 +502,37 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                         for (int c = 0; c < 2; ++c) {
                             const int m = 2 * t + c;
                             if (n < N && m < R) {
-                                const int total = tot[2 * h + c] - s_qsum[m];
-                                float v = epilogue(total, __fmul_rn(s_scale[m], L.weight_scale), L.magnitude, L.bias, n);
+                                const int total = tot[2 * h + c] - cs->qsum[par][m];
+                                float v = epilogue(total, __fmul_rn(cs->scale[par][m], L.weight_scale), L.magnitude, L.bias, n);
                                 if (L.squared_relu) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
                                 yout[static_cast<size_t>(m) * N + n] = v;
                                 omax[c] = fmaxf(omax[c], fabsf(v));
                             }
                         }
                     }
+                    if (l + 1 < P.count) {
+                        // layer boundary, per strip: publish this strip's row maxima, make the stores visible and
+                        // count the strip as arrived
+                        unsigned* sync = P.sync + l * 16;
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t u = __float_as_uint(omax[c]);
-                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 4));
-                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 8));
-                        u = max(u, __shfl_xor_sync(0xffffffffu, u, 16));
-                        if (g == 0 && 2 * t + c < R && u != 0u) atomicMax(&s_outmax[2 * t + c], u);
+                        for (int c = 0; c < 2; ++c) {
+                            uint32_t u = __float_as_uint(omax[c]);
+                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 4));
+                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 8));
+                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 16));
+                            if (g == 0 && 2 * t + c < R && u != 0u) atomicMax(sync + 1 + 2 * t + c, u);
+                        }
+                        __syncwarp();
+                        if (lane == 0) {
+                            __threadfence();
+                            atomicAdd(sync, 1u);
+                        }
                     }
                 }
             }
         }
         if (!alive) break;
-
-        // layer boundary: all consumer warps of this CTA have stored their outputs -> publish the row maxima
-        // and arrive on the layer's counter
         if (threadIdx.x == 0) stamp(l, 5);
-        bar_consumers();
-        if (threadIdx.x == 0) {
-            stamp(l, 6);
-            if (l + 1 < P.count) {
-                for (int m = 0; m < R; ++m) {
-                    const uint32_t u = s_outmax[m];
-                    if (u != 0u) atomicMax(P.amax + (l + 1) * 8 + m, u);
-                    s_outmax[m] = 0u;
-                }
-                __threadfence();
-                atomicAdd(P.arrived + l, 1u);
-            }
-        }
     }
 }
 
@@ -554,10 +579,24 @@ bool gemv_chain_supported(const ChainLayer* layers, int count, int rows) {
     return true;
 }
 
-size_t gemv_chain_workspace_bytes(const ChainLayer* layers, int count, int rows) {
+namespace {
+// [sync words | two activation buffers]
+struct ChainScratch {
+    size_t sync_bytes, act_bytes, total;
+};
+ChainScratch chain_scratch(const ChainLayer* layers, int count, int rows) {
     size_t width = 0;
-    for (int l = 0; l + 1 < count; ++l) width = layers[l].N > static_cast<int>(width) ? layers[l].N : width;
-    return 1024 + 2 * round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
+    for (int l = 0; l + 1 < count; ++l) width = static_cast<size_t>(layers[l].N) > width ? layers[l].N : width;
+    ChainScratch c{};
+    c.sync_bytes = round_up(static_cast<size_t>(count) * 16 * sizeof(unsigned), 256);
+    c.act_bytes = round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
+    c.total = c.sync_bytes + 2 * c.act_bytes;
+    return c;
+}
+}  // namespace
+
+size_t gemv_chain_workspace_bytes(const ChainLayer* layers, int count, int rows) {
+    return chain_scratch(layers, count, rows).total;
 }
 
 cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, const float* x, float* y,
@@ -573,13 +612,11 @@ cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, con
     P.status = device_status_ptr();
     if (!P.status) return cudaErrorUnknown;
     int max_k = 0, max_strips = 0;
-    size_t width = 0;
     for (int l = 0; l < count; ++l) {
         P.layer[l] = layers[l];
         max_k = layers[l].K > max_k ? layers[l].K : max_k;
         const int ns = (layers[l].N + 15) / 16;
         max_strips = ns > max_strips ? ns : max_strips;
-        if (l + 1 < count && static_cast<size_t>(layers[l].N) > width) width = layers[l].N;
     }
     const int grid = max_strips < info.sms ? max_strips : info.sms;
     P.trace = g_chain_trace_bytes >= static_cast<size_t>(grid) * count * 8 * sizeof(unsigned long long) ? g_chain_trace : nullptr;
@@ -604,12 +641,12 @@ cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, con
     const size_t smem = fixed + P.stages * stage_bytes;
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    P.arrived = reinterpret_cast<unsigned*>(ws);
-    P.amax = reinterpret_cast<unsigned*>(ws + 256);
-    const size_t act_bytes = round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
-    P.act[0] = reinterpret_cast<float*>(ws + 1024);
-    P.act[1] = reinterpret_cast<float*>(ws + 1024 + act_bytes);
-    cudaError_t e = cudaMemsetAsync(ws, 0, 1024, stream);      // arrival counters and published maxima
+    const ChainScratch sc = chain_scratch(layers, count, rows);
+    P.sync = reinterpret_cast<unsigned*>(ws);
+    P.act[0] = reinterpret_cast<float*>(ws + sc.sync_bytes);
+    P.act[1] = reinterpret_cast<float*>(ws + sc.sync_bytes + sc.act_bytes);
+    // arrival counters and published maxima start at zero
+    cudaError_t e = cudaMemsetAsync(ws, 0, sc.sync_bytes, stream);
     if (e != cudaSuccess) return e;
 
     cudaLaunchConfig_t cfg{};

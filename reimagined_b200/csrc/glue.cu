@@ -331,6 +331,38 @@ __global__ void __launch_bounds__(256) squared_relu_kernel(float* __restrict__ x
 }
 }  // namespace
 
+namespace {
+// gathered [parts][rows][cols] -> out [rows][parts*cols]; 128-bit accesses when cols % 4 == 0.
+template <typename V>
+__global__ void __launch_bounds__(256) retile_columns_kernel(const V* __restrict__ src, int parts, int rows, int cols,
+                                                             V* __restrict__ dst) {
+    const int64_t n = static_cast<int64_t>(parts) * rows * cols;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += stride) {
+        const int c = static_cast<int>(o % cols);
+        const int64_t rp = o / cols;
+        const int p = static_cast<int>(rp % parts);
+        const int64_t r = rp / parts;
+        dst[o] = src[(static_cast<int64_t>(p) * rows + r) * cols + c];
+    }
+}
+}  // namespace
+
+cudaError_t launch_retile_columns(const float* gathered, int parts, int rows, int cols, float* out, cudaStream_t stream) {
+    if (parts < 1 || rows < 1 || cols < 1) return cudaErrorInvalidValue;
+    const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(gathered) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const int64_t n = static_cast<int64_t>(parts) * rows * (vec ? cols / 4 : cols);
+    const int64_t want = (n + 255) / 256;
+    const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+    if (vec)
+        retile_columns_kernel<float4><<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(gathered), parts, rows, cols / 4,
+                                                               reinterpret_cast<float4*>(out));
+    else
+        retile_columns_kernel<float><<<grid, 256, 0, stream>>>(gathered, parts, rows, cols, out);
+    note_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_squared_relu(float* x, int64_t n, cudaStream_t stream) {
     if (n < 1) return cudaErrorInvalidValue;
     const int64_t want = (n + 255) / 256;

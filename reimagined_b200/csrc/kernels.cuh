@@ -150,6 +150,8 @@ constexpr int kRowNormMaxDim = 49152;
 cudaError_t launch_row_norm(const float* value, const float* gate, const float* weight, int rows, int dim, float eps,
                             int bits, float* out, int8_t* q, float* act_scales, int32_t* q_sums,
                             cudaStream_t stream);
+// column-split outputs after an all-gather, [parts][rows][cols] -> [rows][parts*cols]
+cudaError_t launch_retile_columns(const float* gathered, int parts, int rows, int cols, float* out, cudaStream_t stream);
 // max(x,0)^2 in place over n floats (OXN/nsos/src/tensor.cpp:3209-3226).
 cudaError_t launch_squared_relu(float* x, int64_t n, cudaStream_t stream);
 cudaError_t launch_moe_merge(const float* routing, const float* contrib, const int32_t* slot_of, int rows,

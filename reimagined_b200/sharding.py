@@ -43,16 +43,51 @@ def column_shard_words(words: np.ndarray, out_features: int, in_features: int, w
     return np.ascontiguousarray(words.reshape(out_features, wpr)[lo:hi]).reshape(-1)
 
 
-def gather_columns(y_local, world: int, group=None):
-    """All-gathers per-rank [M, N/world] blocks into [M, N] (torch tensors, any backend).  The gathered
-    data lands in local memory first and is re-tiled there; no peer loads are involved."""
+def gather_buffer(rows: int, n_local: int, world: int, device="cuda"):
+    """The all-gather buffer [world, rows, n_local]: rank r's linear writes its block into slot r of it (no copy
+    before the collective), the all-gather fills the other slots in place."""
     import torch
+    return torch.empty((world, rows, n_local), dtype=torch.float32, device=device)
+
+
+def gather_columns_inplace(stacked, rank: int, group=None):
+    """In-place all-gather of a buffer whose slot `rank` already holds this rank's block.  NCCL sees
+    sendbuff == recvbuff + rank * count and moves nothing locally; data from the other ranks lands in local
+    memory (no peer loads afterwards)."""
     import torch.distributed as dist
+    world = stacked.shape[0]
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(stacked.view(-1), stacked[rank].reshape(-1), group=group)
+    else:   # gloo (CPU tests): list form, the views alias `stacked`
+        dist.all_gather([stacked[r] for r in range(world)], stacked[rank].clone(), group=group)
+    return stacked
+
+
+def retile(stacked, out=None):
+    """[world, rows, n_local] -> [rows, world*n_local].  On CUDA: the library's re-tile kernel (tbl_retile_columns);
+    on the CPU (gloo tests) the same index map in torch."""
+    import torch
+    world, rows, n_local = stacked.shape
+    if out is None:
+        out = torch.empty((rows, world * n_local), dtype=stacked.dtype, device=stacked.device)
+    if stacked.is_cuda:
+        from . import capi
+        capi.check(capi.lib().tbl_retile_columns(stacked.data_ptr(), world, rows, n_local, out.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream), "tbl_retile_columns")
+    else:
+        out.copy_(stacked.permute(1, 0, 2).reshape(rows, world * n_local))
+    return out
+
+
+def gather_columns(y_local, world: int, group=None, rank=None):
+    """All-gathers per-rank [M, N/world] blocks into [M, N] (a copy into the gather buffer first: prefer
+    ColumnParallelBitLinear.forward, whose linear writes into the buffer directly)."""
+    import torch.distributed as dist
+    rank = dist.get_rank(group) if rank is None else rank
     m, n_local = y_local.shape
-    stacked = torch.empty((world, m, n_local), dtype=y_local.dtype, device=y_local.device)
-    # list form of all_gather: supported by NCCL and gloo alike; the views alias `stacked`
-    dist.all_gather([stacked[r] for r in range(world)], y_local.contiguous(), group=group)
-    return stacked.permute(1, 0, 2).reshape(m, world * n_local).contiguous()
+    stacked = gather_buffer(m, n_local, world, y_local.device)
+    stacked[rank].copy_(y_local)
+    return retile(gather_columns_inplace(stacked, rank, group))
 
 
 class ColumnParallelBitLinear:
@@ -77,5 +112,12 @@ class ColumnParallelBitLinear:
         self.shard.to(device)
         return self
 
-    def forward(self, x, group=None):
-        return gather_columns(self.shard.forward(x), self.world, group)
+    def forward(self, x, group=None, stacked=None, out=None):
+        """x [M, K] (replicated) -> y [M, N]: the shard's epilogue writes its [M, N/world] block into slot `rank`
+        of the gather buffer, one in-place all-gather, one re-tile pass over local memory."""
+        m = x.numel() // self.shard.in_features
+        if stacked is None:
+            stacked = gather_buffer(m, self.shard.out_features, self.world, x.device)
+        self.shard.forward(x, out=stacked[self.rank])
+        gather_columns_inplace(stacked, self.rank, group)
+        return retile(stacked, out)

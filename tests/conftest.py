@@ -51,10 +51,11 @@ def cuda():
 
 
 def golden_cases(prefix=""):
-    """Fixture paths; without a prefix, the linear / MoE fixtures only (the row-norm ones are asked for by name)."""
+    """Fixture paths; without a prefix, the linear / MoE fixtures only (row-norm, decode and router fixtures are
+    asked for by name)."""
     paths = sorted(p for p in glob.glob(os.path.join(GOLDEN_DIR, prefix + "*.npz")))
     if not prefix:
-        paths = [p for p in paths if not os.path.basename(p).startswith("rownorm_")]
+        paths = [p for p in paths if not os.path.basename(p).startswith(("rownorm_", "decode_", "router_"))]
     return paths
 
 
