@@ -87,6 +87,11 @@ int tbl_validate_packed(const uint32_t* words_host, int64_t n_words, int N, int 
 
 /* ---- device: weight layouts derived from the canonical words ------------------------------ */
 
+/* The device entry points below take words that passed tbl_validate_packed (or came out of tbl_pack_weights /
+ * tbl_edge_pack_open): they do not look for the reserved code 0b11.  The host decoder maps that code to 0
+ * (like the reference's CPU decoders); the device kernels compute code - 1 and would read it as +2 (like the
+ * reference's GPU kernels, OXN/nsos/src/cuda/kernels.cu:991,1043).  Validate before uploading. */
+
 /* Bytes of the strip-major copy of an [N,K] matrix (K % 256 == 0; rows padded to a multiple of 16). */
 size_t tbl_strip_bytes(int N, int K);
 
@@ -459,8 +464,13 @@ typedef struct tbl_edge_layer_src {
  * last layer, version-3 trailer length and SHA-256) and reports version (2 or 3) and layer count.
  * Replaces: the parsing and validation half of load_edge_linear_pack (jamba.cpp:1451-1616). */
 int tbl_edge_pack_open(const void* data, size_t bytes, int* version_out, int* layers_out);
-/* Layer `index` of a pack (validated up to and including that layer). */
+/* Layer `index` of a pack that tbl_edge_pack_open accepted: walks the record headers up to it and scans only that
+ * layer's payload; the digest is not recomputed. */
 int tbl_edge_pack_layer(const void* data, size_t bytes, int index, tbl_edge_layer* out);
+/* Everything in one pass: digest, full validation and every layer record (`capacity` entries; TBL_ERR_WORKSPACE
+ * with *layers_out set when there are more).  Loading a pack costs one hash and one scan of the file. */
+int tbl_edge_pack_layers(const void* data, size_t bytes, tbl_edge_layer* out, int capacity, int* version_out,
+                         int* layers_out);
 /* Size of, and writer for, a version-3 pack.  Replaces: save_edge_linear_pack's serialisation
  * (jamba.cpp:1345-1439); the caller does the atomic temp-file replace. */
 size_t tbl_edge_pack_bytes(const tbl_edge_layer_src* layers, int count);

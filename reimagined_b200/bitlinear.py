@@ -31,6 +31,9 @@ class BitLinearPackedState:
     packed_weights: np.ndarray = field(default_factory=lambda: np.zeros(0, np.uint32))
     magnitude: np.ndarray = field(default_factory=lambda: np.zeros(0, np.float32))
     bias: np.ndarray = field(default_factory=lambda: np.zeros(0, np.float32))
+    # per-input affine of the reference's Hadamard/"flat" option, carried for interchange (ones / zeros when unused)
+    flat_alpha: np.ndarray = field(default_factory=lambda: np.zeros(0, np.float32))
+    flat_beta: np.ndarray = field(default_factory=lambda: np.zeros(0, np.float32))
 
 
 class BitLinear:
@@ -50,6 +53,8 @@ class BitLinear:
         self.packed_weights = np.zeros(0, np.uint32)
         self.magnitude = np.ones(out_features, np.float32)
         self.bias = np.zeros(out_features if bias else 0, np.float32)
+        self.flat_alpha = np.ones(in_features, np.float32)
+        self.flat_beta = np.zeros(in_features, np.float32)
         self._dev = None                       # device buffers after to("cuda")
         self._ws = None
 
@@ -79,7 +84,8 @@ class BitLinear:
 
     def export_packed_state(self) -> BitLinearPackedState:
         return BitLinearPackedState(self.in_features, self.out_features, self.use_bias, self.weight_scale,
-                                    self.packed_weights.copy(), self.magnitude.copy(), self.bias.copy())
+                                    self.packed_weights.copy(), self.magnitude.copy(), self.bias.copy(),
+                                    self.flat_alpha.copy(), self.flat_beta.copy())
 
     def import_packed_state(self, state: BitLinearPackedState) -> None:
         """Validate first, install afterwards (a rejected state leaves the layer untouched)."""
@@ -88,13 +94,19 @@ class BitLinear:
         words = np.ascontiguousarray(state.packed_weights, np.uint32)
         mag = np.ascontiguousarray(state.magnitude, np.float32)
         bias = np.ascontiguousarray(state.bias, np.float32)
-        if mag.size != self.out_features or bias.size != (self.out_features if self.use_bias else 0):
+        alpha = np.ascontiguousarray(state.flat_alpha, np.float32) if state.flat_alpha.size else np.ones(self.in_features, np.float32)
+        beta = np.ascontiguousarray(state.flat_beta, np.float32) if state.flat_beta.size else np.zeros(self.in_features, np.float32)
+        if mag.size != self.out_features or bias.size != (self.out_features if self.use_bias else 0) or \
+                alpha.size != self.in_features or beta.size != self.in_features:
             raise RuntimeError("BitLinear packed state buffer length mismatch")
+        if not (np.isfinite(alpha).all() and np.isfinite(beta).all()):
+            raise RuntimeError("BitLinear packed state contains non-finite values")
         rc = capi.lib().tbl_validate_packed(words.ctypes.data, words.size, self.out_features, self.in_features,
                                             float(state.weight_scale), mag.ctypes.data,
                                             bias.ctypes.data if bias.size else None)
         capi.check(rc, "tbl_validate_packed")
         self.packed_weights, self.weight_scale, self.magnitude, self.bias = words, float(state.weight_scale), mag, bias
+        self.flat_alpha, self.flat_beta = alpha, beta
         if self._dev is not None:
             self.to("cuda")
 

@@ -131,6 +131,8 @@ _SIGNATURES = {
                                   C.c_int, C.c_int, C.c_int, _vp, _vp, C.c_size_t, _vp]),
     "tbl_edge_pack_open": (C.c_int, [_vp, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "tbl_edge_pack_layer": (C.c_int, [_vp, C.c_size_t, C.c_int, C.POINTER(EdgeLayer)]),
+    "tbl_edge_pack_layers": (C.c_int, [_vp, C.c_size_t, C.POINTER(EdgeLayer), C.c_int, C.POINTER(C.c_int),
+                                       C.POINTER(C.c_int)]),
     "tbl_edge_pack_bytes": (C.c_size_t, [C.POINTER(EdgeLayerSrc), C.c_int]),
     "tbl_edge_pack_write": (C.c_int, [C.POINTER(EdgeLayerSrc), C.c_int, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
     "tbl_sha256_hex": (None, [_vp, C.c_size_t, C.c_char_p]),

@@ -257,6 +257,30 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
 
 }  // extern "C"
 
+namespace tbl {
+
+// tbl_linear_forward on a view, optionally followed by max(y,0)^2: fused into the strip GEMV's epilogue where that
+// kernel serves the shape (one launch), a separate elementwise pass otherwise.
+int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
+                        void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int mode = v.rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
+    if (squared_relu && v.strips && aligned16(v.strips) && gemv_strip_supported(v.inputs) && mode != TBL_RMS_REFERENCE_ORDER &&
+        rows <= gemv_strip_fused_rows(v.inputs)) {
+        StripProblem pr{};
+        pr.strips = static_cast<const uint8_t*>(v.strips); pr.x = x; pr.q_max = qmax_for_bits(v.activation_bits);
+        pr.rms_fast = mode == TBL_RMS_FAST; pr.magnitude = v.magnitude; pr.bias = v.bias; pr.y = y;
+        pr.weight_scale = v.weight_scale; pr.rows = rows; pr.N = v.outputs; pr.K = v.inputs; pr.ldy = v.outputs;
+        pr.squared_relu = 1;
+        return cuda_status(launch_gemv_strip(&pr, 1, st));
+    }
+    const int rc = tbl_linear_forward(x, v.packed, v.strips, rows > 64 ? v.w_i8 : nullptr, v.weight_scale, rows, v.inputs,
+                                      v.outputs, v.activation_bits, mode, v.magnitude, v.bias, y, workspace, workspace_bytes, st);
+    if (rc != TBL_OK || !squared_relu) return rc;
+    return cuda_status(launch_squared_relu(y, static_cast<int64_t>(rows) * v.outputs, st));
+}
+
+}  // namespace tbl
+
 // ---- grouped variant ---------------------------------------------------------------------------
 
 namespace {
@@ -508,15 +532,9 @@ int tbl_chain_forward(const tbl_linear_view* views_host, int count, const int* s
     for (int i = 0; i < count; ++i) {
         const tbl_linear_view& v = views_host[i];
         float* out = i == count - 1 ? y_dev : bufs[i & 1];
-        const int mode = v.rms_input ? (rms_mode == TBL_RMS_NONE ? TBL_RMS_FAST : rms_mode) : TBL_RMS_NONE;
-        const int rc = tbl_linear_forward(in, v.packed, v.strips, rows > 64 ? v.w_i8 : nullptr, v.weight_scale, rows,
-                                          v.inputs, v.outputs, v.activation_bits, mode, v.magnitude, v.bias, out,
-                                          lin_ws, lin_bytes, stream);
+        const int rc = linear_view_forward(v, in, rows, rms_mode, squared_relu_host && squared_relu_host[i], out, lin_ws,
+                                           lin_bytes, st);
         if (rc != TBL_OK) return rc;
-        if (squared_relu_host && squared_relu_host[i]) {
-            const cudaError_t e = launch_squared_relu(out, static_cast<int64_t>(rows) * v.outputs, st);
-            if (e != cudaSuccess) return TBL_ERR_CUDA;
-        }
         in = out;
     }
     return TBL_OK;

@@ -300,7 +300,7 @@ int check_model(const tbl_decode_model* m, int batch, int capacity) {
 }
 
 struct Scratch {
-    float *hidden[2], *core, *attn_in, *proj, *xbc, *y, *gated, *mamba_out, *qkv, *heads, *attn_out, *res, *ffn_in, *ffn_out;
+    float *hidden[2], *core, *attn_in, *proj, *xbc, *y, *gated, *mamba_out, *qkv, *heads, *attn_out, *res, *ffn_in, *ffn_mid, *ffn_out;
     void* lin;
     size_t lin_bytes, proj_stride, qkv_stride, bytes;
 };
@@ -326,8 +326,8 @@ Scratch carve_scratch(const tbl_decode_model& m, int batch, void* base) {
             max_kvout = b.attn.kv.outputs > max_kvout ? b.attn.kv.outputs : max_kvout;
             max_kvout = D > max_kvout ? D : max_kvout;
             max_ffn = b.ffn_up.outputs > max_ffn ? b.ffn_up.outputs : max_ffn;
-            tbl_linear_view pair[2] = {b.ffn_up, b.ffn_down};
-            want(tbl_chain_workspace_bytes(pair, 2, batch));
+            want(tbl_linear_workspace_bytes(batch, D, b.ffn_up.outputs));
+            want(tbl_linear_workspace_bytes(batch, b.ffn_up.outputs, D));
             want(tbl_linear_workspace_bytes(batch, D, D));
         }
     }
@@ -344,7 +344,7 @@ Scratch carve_scratch(const tbl_decode_model& m, int batch, void* base) {
     S.qkv_stride = static_cast<size_t>(batch) * max_kvout;
     S.qkv = take(2 * S.qkv_stride);
     S.heads = take(BD); S.attn_out = take(BD); S.res = take(BD); S.ffn_in = take(BD); S.ffn_out = take(BD);
-    (void)max_ffn;
+    S.ffn_mid = take(static_cast<size_t>(batch) * max_ffn);
     S.lin = p + off;
     S.lin_bytes = round_up(lin, 256);
     off += S.lin_bytes;
@@ -550,9 +550,10 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         if ((rc = residual(h, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, S.res, nullptr)) != TBL_OK) return rc;
         // FFN: norm -> up -> squared ReLU -> down, as one stack
         if ((rc = norm(S.res, b.ff_norm_w, 1e-5f, S.ffn_in)) != TBL_OK) return rc;
-        const tbl_linear_view ffn[2] = {b.ffn_up, b.ffn_down};
-        const int relu[2] = {1, 0};
-        if ((rc = tbl_chain_forward(ffn, 2, relu, S.ffn_in, B, TBL_RMS_FAST, S.ffn_out, S.lin, S.lin_bytes, stream)) != TBL_OK) return rc;
+        // (two launches with the squared ReLU in the first one's epilogue: at this width a launch boundary is cheaper
+        // than the persistent stack's grid-wide layer boundary)
+        if ((rc = linear_view_forward(b.ffn_up, S.ffn_in, B, TBL_RMS_FAST, true, S.ffn_mid, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
+        if ((rc = linear_view_forward(b.ffn_down, S.ffn_mid, B, TBL_RMS_FAST, false, S.ffn_out, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
         if ((rc = residual(S.res, S.ffn_out, b.ffn_gate, nullptr, nullptr, S.hidden[cur ^ 1], trace)) != TBL_OK) return rc;
         cur ^= 1;
     }

@@ -136,8 +136,12 @@ bool all_finite(const uint8_t* base, uint64_t offset, uint64_t count) {
     return true;
 }
 
-// Parses layer records up to and including `stop_at` (or all when stop_at < 0), validating each.
-int walk(const uint8_t* data, uint64_t payload, int stop_at, uint32_t* layers_out, tbl_edge_layer* out) {
+// Parses layer records up to and including `stop_at` (or all when stop_at < 0).  Structure (flags, sizes, vector
+// lengths, truncation) is always checked; the payload scans -- finite values, reserved codes -- run for every layer
+// when validating the whole pack and only for the requested layer otherwise.  `all_out` (may be null, `capacity`
+// entries) receives every record.
+int walk(const uint8_t* data, uint64_t payload, int stop_at, uint32_t* layers_out, tbl_edge_layer* out,
+         tbl_edge_layer* all_out = nullptr, int capacity = 0) {
     Cursor c{data, payload, 8, true};
     const uint32_t layers = c.pod<uint32_t>();
     if (!c.ok) return TBL_ERR_FORMAT;
@@ -164,11 +168,13 @@ int walk(const uint8_t* data, uint64_t payload, int stop_at, uint32_t* layers_ou
         if (sensitive) { L.weight_offset = c.vec(total, 4, &length_ok); L.weight_count = total; }
         if (!c.ok) return length_ok ? TBL_ERR_FORMAT : TBL_ERR_SHAPE;
         if (!std::isfinite(L.weight_scale) || L.weight_scale <= 0.0f) return TBL_ERR_SCALE;
-        if (!all_finite(data, L.magnitude_offset, outf) || !all_finite(data, L.bias_offset, use_bias ? outf : 0) ||
+        if (all_out && static_cast<int>(index) < capacity) all_out[index] = L;
+        const bool scan = stop_at < 0 || static_cast<int>(index) == stop_at;
+        if (scan && (!all_finite(data, L.magnitude_offset, outf) || !all_finite(data, L.bias_offset, use_bias ? outf : 0) ||
             !all_finite(data, L.flat_alpha_offset, in) || !all_finite(data, L.flat_beta_offset, in) ||
-            !all_finite(data, L.weight_offset, L.weight_count))
+            !all_finite(data, L.weight_offset, L.weight_count)))
             return TBL_ERR_FORMAT;
-        for (uint64_t w = 0; w < L.packed_words; ++w) {
+        for (uint64_t w = 0; scan && w < L.packed_words; ++w) {
             uint32_t word;
             std::memcpy(&word, data + L.packed_offset + 4 * w, 4);
             // a field is reserved when both of its bits are set; fields past the last weight are not checked
@@ -183,7 +189,7 @@ int walk(const uint8_t* data, uint64_t payload, int stop_at, uint32_t* layers_ou
 }
 
 // Header and (version 3) trailer checks; returns the payload length.
-int open_pack(const uint8_t* data, size_t bytes, uint32_t* version_out, uint64_t* payload_out) {
+int open_pack(const uint8_t* data, size_t bytes, uint32_t* version_out, uint64_t* payload_out, bool verify_digest = true) {
     if (!data || bytes < 12) return TBL_ERR_FORMAT;
     uint32_t magic, version;
     std::memcpy(&magic, data, 4);
@@ -198,12 +204,14 @@ int open_pack(const uint8_t* data, size_t bytes, uint32_t* version_out, uint64_t
         std::memcpy(&tmagic, data + payload, 4);
         std::memcpy(&tbytes, data + payload + 4, 8);
         if (tmagic != kTrailerMagic || tbytes != payload) return TBL_ERR_INTEGRITY;
-        Sha256 c;
-        sha_init(c);
-        sha_update(c, data, payload);
-        char hex[65];
-        sha_hex(c, hex);
-        if (std::memcmp(hex, data + payload + 12, 64) != 0) return TBL_ERR_INTEGRITY;
+        if (verify_digest) {
+            Sha256 c;
+            sha_init(c);
+            sha_update(c, data, payload);
+            char hex[65];
+            sha_hex(c, hex);
+            if (std::memcmp(hex, data + payload + 12, 64) != 0) return TBL_ERR_INTEGRITY;
+        }
     }
     *version_out = version;
     *payload_out = payload;
@@ -237,9 +245,24 @@ int tbl_edge_pack_layer(const void* data, size_t bytes, int index, tbl_edge_laye
     if (!out || index < 0) return TBL_ERR_INVALID_ARG;
     uint32_t version = 0;
     uint64_t payload = 0;
-    const int rc = open_pack(static_cast<const uint8_t*>(data), bytes, &version, &payload);
+    // header and trailer framing only: the digest was checked by tbl_edge_pack_open
+    const int rc = open_pack(static_cast<const uint8_t*>(data), bytes, &version, &payload, /*verify_digest=*/false);
     if (rc != TBL_OK) return rc;
     return walk(static_cast<const uint8_t*>(data), payload, index, nullptr, out);
+}
+
+int tbl_edge_pack_layers(const void* data, size_t bytes, tbl_edge_layer* out, int capacity, int* version_out,
+                         int* layers_out) {
+    if (!out || capacity < 0) return TBL_ERR_INVALID_ARG;
+    uint32_t version = 0, layers = 0;
+    uint64_t payload = 0;
+    int rc = open_pack(static_cast<const uint8_t*>(data), bytes, &version, &payload, true);
+    if (rc != TBL_OK) return rc;
+    rc = walk(static_cast<const uint8_t*>(data), payload, -1, &layers, nullptr, out, capacity);
+    if (rc != TBL_OK) return rc;
+    if (version_out) *version_out = static_cast<int>(version);
+    if (layers_out) *layers_out = static_cast<int>(layers);
+    return static_cast<int>(layers) <= capacity ? TBL_OK : TBL_ERR_WORKSPACE;
 }
 
 }  // extern "C"

@@ -283,12 +283,17 @@ cudaError_t launch_one(const float* value, const float* gate, const float* weigh
         return launch_warp_rows<GATED, 16>(value, gate, weight, rows, dim, eps, q_max, out, q, act_scales, q_sums, stream);
     }
     const size_t smem = static_cast<size_t>(dim) * sizeof(float);
-    static size_t configured = 0;      // one per instantiation
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(row_norm_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kRowNormMaxDim * sizeof(float)));
-        if (e != cudaSuccess) return e;
-        configured = kRowNormMaxDim * sizeof(float);
+    if (smem > 48 * 1024) {
+        // the opt-in is a per-device attribute of the kernel: remember it per device (one flag set per instantiation)
+        static bool configured[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(row_norm_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kRowNormMaxDim * sizeof(float)));
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) configured[dev] = true;
+        }
     }
     // Few rows (decode): one CTA per row, as many threads as the row has 4-element groups, up to 1024, so the
     // row is one load per thread.  Many rows: 256 threads, several CTAs per SM, a grid-stride over rows.

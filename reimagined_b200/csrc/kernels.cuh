@@ -121,6 +121,10 @@ void set_chain_trace(void* buffer, size_t bytes);
 cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, const float* x, float* y,
                               void* workspace, cudaStream_t stream);
 
+// api.cu -- one view's forward with an optional squared ReLU (fused into the GEMV epilogue where possible)
+int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
+                        void* workspace, size_t workspace_bytes, cudaStream_t st);
+
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8,
                                 float weight_scale, const float* magnitude, const float* bias,

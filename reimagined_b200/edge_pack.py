@@ -27,11 +27,14 @@ def loads(image: bytes) -> List[Dict]:
     """Parse and validate a pack held in memory; raises capi.TernaryB200Error with the library's status."""
     L = capi.lib()
     version, layers = C.c_int(0), C.c_int(0)
-    capi.check(L.tbl_edge_pack_open(image, len(image), C.byref(version), C.byref(layers)), "tbl_edge_pack_open")
+    # the layer count sits in the header; one pass then hashes, validates and returns every record
+    count = int.from_bytes(image[8:12], "little") if len(image) >= 12 else 0
+    records = (capi.EdgeLayer * max(count, 1))()
+    capi.check(L.tbl_edge_pack_layers(image, len(image), records, count, C.byref(version), C.byref(layers)),
+               "tbl_edge_pack_layers")
     out = []
     for index in range(layers.value):
-        rec = capi.EdgeLayer()
-        capi.check(L.tbl_edge_pack_layer(image, len(image), index, C.byref(rec)), "tbl_edge_pack_layer")
+        rec = records[index]
         n, k = rec.out_features, rec.in_features
         out.append({
             "sensitive": bool(rec.sensitive), "in_features": k, "out_features": n, "use_bias": bool(rec.use_bias),
@@ -120,5 +123,13 @@ def to_bitlinear(layer: Dict):
     lin.import_packed_state(BitLinearPackedState(
         in_features=layer["in_features"], out_features=layer["out_features"], use_bias=layer["use_bias"],
         weight_scale=float(layer["weight_scale"]), packed_weights=layer["packed_weights"],
-        magnitude=layer["magnitude"], bias=layer["bias"]))
+        magnitude=layer["magnitude"], bias=layer["bias"], flat_alpha=layer["flat_alpha"], flat_beta=layer["flat_beta"]))
     return lin
+
+
+def from_bitlinear(lin) -> Dict:
+    """The pack record of a `BitLinear` (the inverse of `to_bitlinear`)."""
+    st = lin.export_packed_state()
+    return {"sensitive": False, "in_features": st.in_features, "out_features": st.out_features, "use_bias": st.use_bias,
+            "weight_scale": np.float32(st.weight_scale), "packed_weights": st.packed_weights, "magnitude": st.magnitude,
+            "bias": st.bias, "flat_alpha": st.flat_alpha, "flat_beta": st.flat_beta, "weight": None}

@@ -109,3 +109,12 @@ def test_router_matches_moe_router_forward(port, name):
     assert np.array_equal(got != 0, g["weights"] != 0), "different experts kept (ties go to the lower index)"
     assert bits_equal(got, g["weights"])
     assert (g["weights"] != 0).sum(axis=1).tolist() == [int(g["top_k"])] * g["weights"].shape[0]
+
+
+def test_pack_to_layers_and_back_is_byte_identical(tbl):
+    """edge pack -> BitLinear mirror objects -> exported states -> edge pack: nothing is lost on the way."""
+    from reimagined_b200 import edge_pack
+    with open(os.path.join(GOLDEN_DIR, "edge_pack_tiny.bin"), "rb") as f:
+        image = f.read()
+    layers = [edge_pack.to_bitlinear(rec) for rec in edge_pack.loads(image)]
+    assert edge_pack.dumps([edge_pack.from_bitlinear(lin) for lin in layers]) == image

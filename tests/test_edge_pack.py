@@ -172,3 +172,32 @@ def test_writer_refuses_what_would_not_load(tbl, port):
     layers[0]["magnitude"][3] = np.inf
     with pytest.raises(capi.TernaryB200Error):
         edge_pack.dumps(layers)
+
+
+def test_loading_a_pack_of_many_layers_hashes_it_once(tbl, port):
+    """120 layers: one digest and one scan of the file, not one per layer."""
+    import time
+    from reimagined_b200 import edge_pack
+    rng = np.random.default_rng(5)
+    layers = []
+    for i in range(120):
+        n, k = 256, 512
+        words = rng.integers(0, 3, (n * k,), dtype=np.uint32).reshape(-1, 16)
+        packed = (words << (2 * np.arange(16, dtype=np.uint32))).sum(axis=1).astype(np.uint32)
+        layers.append({"sensitive": False, "in_features": k, "out_features": n, "use_bias": False,
+                       "weight_scale": np.float32(0.016), "packed_weights": packed, "magnitude": np.ones(n, np.float32),
+                       "bias": np.zeros(0, np.float32), "flat_alpha": np.ones(k, np.float32),
+                       "flat_beta": np.zeros(k, np.float32), "weight": None})
+    image = edge_pack.dumps(layers)
+    t0 = time.perf_counter()
+    back = edge_pack.loads(image)
+    one_pass = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    edge_pack.sha256_hex(image)
+    one_hash = time.perf_counter() - t0
+    assert len(back) == 120 and np.array_equal(back[77]["packed_weights"], layers[77]["packed_weights"])
+    assert one_pass < 6 * one_hash + 0.5, f"loading took {one_pass:.2f}s for a file that hashes in {one_hash:.2f}s"
+    # the per-layer call still works and agrees
+    rec = __import__("reimagined_b200.capi", fromlist=["EdgeLayer"]).EdgeLayer()
+    assert tbl.tbl_edge_pack_layer(image, len(image), 119, C.byref(rec)) == 0 and rec.packed_words == 256 * 512 // 16
+    assert tbl.tbl_edge_pack_layer(image, len(image), 120, C.byref(rec)) == -1
