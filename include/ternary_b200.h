@@ -489,6 +489,12 @@ void tbl_sha256_hex(const void* data, size_t bytes, char out[65]);
  * clears it.  Negative on a CUDA error. */
 int tbl_device_status(void* stream);
 
+/* Self-test of the give-up path of the device-side waits: launches one CTA that waits, with a limit of 4096 polls,
+ * on a barrier nobody arrives on.  The kernel must return on its own (within milliseconds), write 1 to *gave_up_dev
+ * and leave TBL_DEV_WAIT_TIMEOUT in the device status word; the context stays usable.  No counterpart in the
+ * reference, whose kernels have no inter-thread waits. */
+int tbl_selftest_bounded_wait(int* gave_up_dev, void* stream);
+
 /* Profiling aid: while set (non-NULL cudaEvent_t handles), every launch of the decode GEMV kernel
  * records `start_event` just before and `stop_event` just after it on its stream, so a harness can
  * time that kernel alone with cudaEventElapsedTime.  Pass NULLs to switch it off.  Process-wide.

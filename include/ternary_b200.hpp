@@ -11,8 +11,12 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstring>
+#include <functional>
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 
 extern "C" {
 #include "ternary_b200.h"
@@ -87,6 +91,195 @@ inline void rmsnorm_weight(const float* x, const float* weight, float* output, i
     throw_on_status(tbl_row_norm(x, nullptr, weight, rows, dim, eps, output, 8, nullptr, nullptr, nullptr, stream),
                     "rmsnorm");
 }
+
+// ---- the layer object ------------------------------------------------------------------------------------------
+
+// nsos::BitLinearPackedState (OXN/nsos/include/bitlinear.h:37-47), field for field: the interchange form of a layer.
+struct PackedState {
+    int in_features = 0;
+    int out_features = 0;
+    bool use_bias = true;
+    float weight_scale = 1.0f;
+    std::vector<std::uint32_t> packed_weights;
+    std::vector<float> magnitude;
+    std::vector<float> bias;
+    std::vector<float> flat_alpha;
+    std::vector<float> flat_beta;
+};
+
+// How the host runtime hands out device memory.  The C ABI never allocates; the layer object asks its owner.
+// (The reference draws from its tensor pool, OXN/nsos/include/tensor.h:89-152.)  `upload` enqueues a host-to-device
+// copy on `stream`; the source stays alive until the caller has synchronised.
+struct DeviceMemory {
+    std::function<void*(std::size_t bytes)> allocate;
+    std::function<void(void* ptr)> release;
+    std::function<void(void* dst, const void* src, std::size_t bytes, void* stream)> upload;
+};
+
+// The packed-inference surface of nsos::BitLinear (OXN/nsos/include/bitlinear.h:77-212) over the C ABI:
+// import_packed_state / export_packed_state / forward / prepare_gpu_decode_view, with the reference's transactional
+// import -- prepare_packed_state validates and fills freshly allocated buffers and may throw without touching the
+// layer, commit_prepared_packed_state only swaps owned buffers (OXN/nsos/src/bitlinear.cpp:834-1028).
+class TernaryLinear {
+public:
+    TernaryLinear(int in_features, int out_features, bool bias, DeviceMemory memory)
+        : in_(in_features), out_(out_features), use_bias_(bias), mem_(std::move(memory)) {
+        if (in_features <= 0 || out_features <= 0) throw std::invalid_argument("BitLinear feature counts must be positive");
+        if (!mem_.allocate || !mem_.release || !mem_.upload) throw std::invalid_argument("DeviceMemory callbacks are required");
+    }
+    TernaryLinear(const TernaryLinear&) = delete;
+    TernaryLinear& operator=(const TernaryLinear&) = delete;
+    ~TernaryLinear() { release(live_); }
+
+    // Device buffers of one validated state, owned until committed or destroyed.
+    class Prepared {
+    public:
+        Prepared(Prepared&& o) noexcept : owner_(o.owner_), dev_(o.dev_), host_(std::move(o.host_)) { o.dev_ = Buffers{}; }
+        Prepared& operator=(Prepared&&) = delete;
+        Prepared(const Prepared&) = delete;
+        ~Prepared() { if (owner_) owner_->release(dev_); }
+    private:
+        friend class TernaryLinear;
+        struct Buffers { void *words = nullptr, *strips = nullptr, *w_i8 = nullptr, *magnitude = nullptr, *bias = nullptr; };
+        Prepared(const TernaryLinear* owner, PackedState host) : owner_(owner), host_(std::move(host)) {}
+        const TernaryLinear* owner_;
+        Buffers dev_;
+        PackedState host_;
+    };
+
+    // Validation (shape, lengths, finite positive scale, no reserved code, finite affine; with `retained_fp32` the
+    // codes and the scale must equal a fresh packing of those weights, OXN/nsos/src/bitlinear.cpp:957-973), then
+    // upload into new buffers and derivation of the device layouts.  Throws std::runtime_error like the reference;
+    // the live layer is untouched.  `with_int8` also keeps the int8 expansion the prefill GEMM (M > 64) reads.
+    Prepared prepare_packed_state(const PackedState& state, void* stream, bool with_int8 = true,
+                                  const float* retained_fp32 = nullptr) const {
+        if (state.in_features != in_ || state.out_features != out_ || state.use_bias != use_bias_)
+            throw std::runtime_error("BitLinear packed state shape mismatch");
+        const std::size_t total = static_cast<std::size_t>(out_) * static_cast<std::size_t>(in_);
+        if (state.packed_weights.size() != (total + 15) / 16 || state.magnitude.size() != static_cast<std::size_t>(out_) ||
+            state.bias.size() != (use_bias_ ? static_cast<std::size_t>(out_) : 0u) ||
+            state.flat_alpha.size() != static_cast<std::size_t>(in_) || state.flat_beta.size() != static_cast<std::size_t>(in_))
+            throw std::runtime_error("BitLinear packed state buffer length mismatch");
+        const int rc = tbl_validate_packed(state.packed_weights.data(), static_cast<long long>(state.packed_weights.size()), out_,
+                                           in_, state.weight_scale, state.magnitude.data(), use_bias_ ? state.bias.data() : nullptr);
+        if (rc != TBL_OK) throw std::runtime_error(std::string("BitLinear packed state rejected: ") + tbl_status_string(rc));
+        for (const std::vector<float>* v : {&state.flat_alpha, &state.flat_beta})
+            for (float f : *v)
+                if (!(f - f == 0.0f)) throw std::runtime_error("BitLinear packed state contains non-finite values");
+        if (retained_fp32) {
+            std::vector<std::uint32_t> words(state.packed_weights.size());
+            float scale = 0.0f;
+            throw_on_status(tbl_pack_weights(retained_fp32, out_, in_, words.data(), &scale), "prepare_packed_state");
+            if (std::memcmp(&scale, &state.weight_scale, sizeof(float)) != 0 || words != state.packed_weights)
+                throw std::runtime_error("BitLinear packed state does not match the retained full-precision weights");
+        }
+        Prepared p(this, state);
+        const std::size_t word_bytes = state.packed_weights.size() * sizeof(std::uint32_t);
+        p.dev_.words = take(word_bytes);
+        mem_.upload(p.dev_.words, p.host_.packed_weights.data(), word_bytes, stream);
+        p.dev_.magnitude = take(sizeof(float) * out_);
+        mem_.upload(p.dev_.magnitude, p.host_.magnitude.data(), sizeof(float) * out_, stream);
+        if (use_bias_) {
+            p.dev_.bias = take(sizeof(float) * out_);
+            mem_.upload(p.dev_.bias, p.host_.bias.data(), sizeof(float) * out_, stream);
+        }
+        if (in_ % 16 == 0) {
+            const std::size_t strip_bytes = tbl_strip_bytes(out_, in_);
+            if (strip_bytes) {
+                p.dev_.strips = take(strip_bytes);
+                throw_on_status(tbl_relayout_strips(static_cast<const std::uint32_t*>(p.dev_.words), out_, in_, p.dev_.strips, stream),
+                                "prepare_packed_state");
+            }
+            if (with_int8) {
+                p.dev_.w_i8 = take(total);
+                throw_on_status(tbl_expand_weights_i8(static_cast<const std::uint32_t*>(p.dev_.words), out_, in_,
+                                                      static_cast<std::int8_t*>(p.dev_.w_i8), stream),
+                                "prepare_packed_state");
+            }
+        }
+        return p;
+    }
+
+    // Installs a prepared state: swaps owned pointers, frees the previous buffers, cannot fail.
+    void commit_prepared_packed_state(Prepared&& p) noexcept {
+        std::swap(live_, p.dev_);
+        std::swap(host_, p.host_);
+        loaded_ = true;
+    }
+
+    void import_packed_state(const PackedState& state, void* stream, bool with_int8 = true) {
+        commit_prepared_packed_state(prepare_packed_state(state, stream, with_int8));
+    }
+
+    // BitLinear::export_packed_state (OXN/nsos/src/bitlinear.cpp:764-799).
+    PackedState export_packed_state() const {
+        if (!loaded_) throw std::runtime_error("BitLinear has no packed state to export");
+        return host_;
+    }
+
+    void set_exact_linear_mode(bool enabled) { exact_ = enabled; }    // no input RMSNorm, no magnitude (bitlinear.h:99-108)
+    bool exact_linear_mode() const { return exact_; }
+    void set_precision_mode(int bits) {
+        if (bits < 2 || bits > 8) throw std::invalid_argument("activation bits must be in [2,8]");
+        bits_ = bits;
+    }
+    int input_features() const { return in_; }
+    int output_features() const { return out_; }
+    bool uses_bias() const { return use_bias_; }
+
+    std::size_t workspace_bytes(int rows) const { return tbl_linear_workspace_bytes(rows, in_, out_); }
+
+    // BitLinear::forward, packed branch: x fp32 [rows, in] -> y fp32 [rows, out], enqueued on `stream`.
+    // rms_mode applies in default mode only: TBL_RMS_FAST, or TBL_RMS_REFERENCE_ORDER for the CPU path's sum order.
+    void forward(const float* x_dev, int rows, float* y_dev, void* scratch, std::size_t scratch_bytes, void* stream,
+                 int rms_mode = TBL_RMS_FAST) const {
+        if (!loaded_) throw std::runtime_error("BitLinear::forward before import_packed_state");
+        throw_on_status(tbl_linear_forward(x_dev, static_cast<const std::uint32_t*>(live_.words), live_.strips,
+                                           static_cast<const std::int8_t*>(live_.w_i8), host_.weight_scale, rows, in_, out_,
+                                           bits_, exact_ ? TBL_RMS_NONE : rms_mode,
+                                           exact_ ? nullptr : static_cast<const float*>(live_.magnitude),
+                                           static_cast<const float*>(live_.bias), y_dev, scratch, scratch_bytes, stream),
+                        "BitLinear::forward");
+    }
+
+    // BitLinear::prepare_gpu_decode_view (OXN/nsos/src/bitlinear.cpp:335-389): a borrowed descriptor for the grouped
+    // entry points; false when the layer has nothing packed to show.
+    bool prepare_gpu_decode_view(tbl_linear_view& view) const {
+        if (!loaded_ || in_ % 16 != 0) return false;
+        view = tbl_linear_view{};
+        view.packed = static_cast<const std::uint32_t*>(live_.words);
+        view.magnitude = exact_ ? nullptr : static_cast<const float*>(live_.magnitude);
+        view.bias = static_cast<const float*>(live_.bias);
+        view.inputs = in_;
+        view.outputs = out_;
+        view.activation_bits = bits_;
+        view.rms_input = exact_ ? 0 : 1;
+        view.weight_scale = host_.weight_scale;
+        view.strips = live_.strips;
+        view.w_i8 = static_cast<const std::int8_t*>(live_.w_i8);
+        return true;
+    }
+
+private:
+    void* take(std::size_t bytes) const {
+        void* p = mem_.allocate(bytes ? bytes : 16);
+        if (!p) throw std::runtime_error("BitLinear: device allocation failed");
+        return p;
+    }
+    void release(Prepared::Buffers& b) const {
+        for (void** p : {&b.words, &b.strips, &b.w_i8, &b.magnitude, &b.bias}) {
+            if (*p) mem_.release(*p);
+            *p = nullptr;
+        }
+    }
+    int in_, out_;
+    bool use_bias_;
+    bool exact_ = false, loaded_ = false;
+    int bits_ = 8;
+    DeviceMemory mem_;
+    mutable Prepared::Buffers live_;
+    PackedState host_;
+};
 
 // Sticky device status (bounded waits that gave up, MoE route overflow); synchronises the stream.
 inline void check_device(void* stream) {

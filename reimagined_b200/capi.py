@@ -136,6 +136,7 @@ _SIGNATURES = {
     "tbl_edge_pack_bytes": (C.c_size_t, [C.POINTER(EdgeLayerSrc), C.c_int]),
     "tbl_edge_pack_write": (C.c_int, [C.POINTER(EdgeLayerSrc), C.c_int, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
     "tbl_sha256_hex": (None, [_vp, C.c_size_t, C.c_char_p]),
+    "tbl_selftest_bounded_wait": (C.c_int, [_vp, _vp]),
     "tbl_device_status": (C.c_int, [_vp]),
     "tbl_set_kernel_events": (None, [_vp, _vp]),
     "tbl_set_chain_trace": (None, [_vp, C.c_size_t]),

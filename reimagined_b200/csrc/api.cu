@@ -81,6 +81,24 @@ int run_gemv(const int8_t* q, const int8_t* qp, const float* act_scales, const i
 }  // namespace
 }  // namespace tbl
 
+namespace tbl {
+namespace {
+// One CTA waits, with a limit of a few thousand polls, on an mbarrier nobody arrives on: the wait runs out, the
+// kernel records it and returns.  Exercises the give-up path every pipelined kernel of the library shares.
+__global__ void bounded_wait_selftest_kernel(int* status, int* gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_bounded(&bar, 0, status, 4096);
+    if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+}  // namespace
+}  // namespace tbl
+
+
 using namespace tbl;
 
 extern "C" {
@@ -113,6 +131,15 @@ void tbl_set_kernel_events(void* start_event, void* stop_event) {
 }
 
 void tbl_set_chain_trace(void* buffer_dev, size_t bytes) { set_chain_trace(buffer_dev, bytes); }
+
+int tbl_selftest_bounded_wait(int* gave_up_dev, void* stream) {
+    if (!gave_up_dev) return TBL_ERR_INVALID_ARG;
+    int* status = device_status_ptr();
+    if (!status) return TBL_ERR_CUDA;
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, gave_up_dev);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
 
 int tbl_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

@@ -64,8 +64,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait on an mbarrier phase.  Returns false (after recording the timeout in the
 // device status word) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
-    for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status,
+                                                  uint32_t limit = kWaitSpinLimit) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     atomicOr(status, TBL_DEV_WAIT_TIMEOUT);

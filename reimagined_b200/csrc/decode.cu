@@ -211,6 +211,144 @@ attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k
     }
 }
 
+
+// ---- fused glue of the step (one CTA per sequence) -------------------------------------------------------------
+constexpr int kFusedThreads = 512;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nw; ++w) t += scratch[w];     // fixed order: the same result in every thread
+    return t;
+}
+
+// hidden_out = x + (a*ga [+ b*gb]) (or x itself when a == null; x = table[ids[row]] when ids != null), and up to two
+// RMSNorm x weight views of it (eps shared): out1 = rmsnorm(h)*w1, out2 = rmsnorm(h)*w2.  Replaces the residual
+// add that closes one block and the norm(s) that open the next (OXN/nsos/src/jamba.cpp:3175-3179, 3195-3251).
+__global__ void __launch_bounds__(kFusedThreads)
+residual_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ ids, const float* __restrict__ table,
+                     int vocab, const float* __restrict__ a, const float* __restrict__ ga, const float* __restrict__ b,
+                     const float* __restrict__ gb, int D, float eps, const float* __restrict__ w1,
+                     const float* __restrict__ w2, float* __restrict__ hidden_out, float* __restrict__ trace,
+                     float* __restrict__ out1, float* __restrict__ out2) {
+    extern __shared__ float sm[];
+    float* row = sm;                 // [D]
+    float* scratch = sm + D;         // [32]
+    const int r = blockIdx.x;
+    const float* src = x ? x + static_cast<size_t>(r) * D : nullptr;
+    bool id_ok = true;
+    if (ids) {
+        const int id = __ldg(ids + r);
+        id_ok = id >= 0 && id < vocab;
+        src = table + static_cast<size_t>(id_ok ? id : 0) * D;
+    }
+    float ss = 0.0f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = id_ok ? src[d] : 0.0f;
+        if (a) {
+            const size_t i = static_cast<size_t>(r) * D + d;
+            float contrib = ga ? __fmul_rn(a[i], __ldg(ga + d)) : a[i];
+            if (b) contrib = __fadd_rn(contrib, __fmul_rn(b[i], __ldg(gb + d)));
+            v = __fadd_rn(v, contrib);
+        }
+        row[d] = v;
+        if (hidden_out) hidden_out[static_cast<size_t>(r) * D + d] = v;
+        if (trace) trace[static_cast<size_t>(r) * D + d] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(D)), eps)));
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float n = __fmul_rn(row[d], inv);
+        if (out1) out1[static_cast<size_t>(r) * D + d] = w1 ? __fmul_rn(n, __ldg(w1 + d)) : n;
+        if (out2) out2[static_cast<size_t>(r) * D + d] = w2 ? __fmul_rn(n, __ldg(w2 + d)) : n;
+    }
+}
+
+__device__ __forceinline__ float silu_two_sided(float g) {     // Tensor::silu (OXN/nsos/src/tensor.cpp:3273-3280)
+    const float e = expf(-fabsf(g));
+    const float sig = __fdiv_rn(g >= 0.0f ? 1.0f : e, __fadd_rn(1.0f, e));
+    return __fmul_rn(g, sig);
+}
+
+// conv step -> SSD step -> (y * silu(z)).rmsnorm(eps) * weight for one sequence per CTA: the three stages of
+// Mamba2SSD::forward_faithful_step between the projections and the out projection
+// (OXN/nsos/src/mamba2.cpp:4062-4123), with the conv output and the per-head decay terms kept in shared memory.
+__global__ void __launch_bounds__(kFusedThreads)
+mamba_mix_kernel(const float* __restrict__ xv, const float* __restrict__ zv, const float* __restrict__ Bv,
+                 const float* __restrict__ Cv, const float* __restrict__ dt, const float* __restrict__ conv_w,
+                 const float* __restrict__ conv_b, const float* __restrict__ A_log, const float* __restrict__ Dp,
+                 const float* __restrict__ norm_w, float* __restrict__ ring, float* __restrict__ state, int n_heads,
+                 int d_head, int N, int n_groups, int K, float eps, float* __restrict__ out) {
+    extern __shared__ float sm[];
+    const int d_inner = n_heads * d_head, GS = n_groups * N, conv_dim = d_inner + 2 * GS;
+    float* xbc = sm;                          // [conv_dim]
+    float* gated = xbc + conv_dim;            // [d_inner]
+    float* delta_s = gated + d_inner;         // [n_heads]
+    float* decay_s = delta_s + n_heads;       // [n_heads]
+    float* scratch = decay_s + n_heads;       // [32]
+    const int r = blockIdx.x;
+    const int taps = K - 1;
+    float* rr = ring + static_cast<size_t>(r) * (taps > 0 ? taps : 1) * conv_dim;
+    for (int c = threadIdx.x; c < conv_dim; c += blockDim.x) {
+        const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
+                                          : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
+                                                              : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
+        float value = __ldg(conv_b + c);
+        for (int j = 0; j < K; ++j) {
+            const float tap = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
+            value = __fadd_rn(value, __fmul_rn(__ldg(conv_w + static_cast<size_t>(c) * K + j), tap));
+        }
+        xbc[c] = silu_stable(value);
+        for (int s2 = 0; s2 + 1 < taps; ++s2) rr[static_cast<size_t>(s2) * conv_dim + c] = rr[static_cast<size_t>(s2 + 1) * conv_dim + c];
+        if (taps > 0) rr[static_cast<size_t>(taps - 1) * conv_dim + c] = current;
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        const float dt_raw = dt[static_cast<size_t>(r) * n_heads + h];
+        const float a_log = __ldg(A_log + h);
+        const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
+        float decay;
+        if (!isfinite(dt_raw) || !isfinite(a_log)) {
+            decay = nanf("");
+        } else {
+            const double log_delta = dt_raw < -20.0f ? static_cast<double>(dt_raw) : log(static_cast<double>(delta));
+            const double log_q = log_delta + static_cast<double>(a_log);
+            decay = log_q > 50.0 ? 0.0f : static_cast<float>(exp(-exp(log_q)));
+        }
+        delta_s[h] = delta;
+        decay_s[h] = decay;
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    for (int chan = threadIdx.x; chan < d_inner; chan += blockDim.x) {
+        const int h = chan / d_head;
+        const int group = (h * n_groups) / n_heads;
+        const float delta = delta_s[h], decay = decay_s[h];
+        const float input = xbc[chan];
+        float y = __fmul_rn(__ldg(Dp + h), input);
+        float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
+        for (int n = 0; n < N; ++n) {
+            const float hv = __fadd_rn(__fmul_rn(decay, st[n]), __fmul_rn(__fmul_rn(delta, xbc[d_inner + group * N + n]), input));
+            st[n] = hv;
+            y = __fadd_rn(y, __fmul_rn(hv, xbc[d_inner + GS + group * N + n]));
+        }
+        const float gv = __fmul_rn(y, silu_two_sided(zv[static_cast<size_t>(r) * d_inner + chan]));
+        gated[chan] = gv;
+        ss += gv * gv;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d_inner)), eps)));
+    for (int chan = threadIdx.x; chan < d_inner; chan += blockDim.x) {
+        const float n = __fmul_rn(gated[chan], inv);
+        out[static_cast<size_t>(r) * d_inner + chan] = norm_w ? __fmul_rn(n, __ldg(norm_w + chan)) : n;
+    }
+}
+
 // ---- out = x + (a * ga [+ b * gb]); ga == null: out = x + a ----------------------------------------------------
 __global__ void __launch_bounds__(256) gated_residual_kernel(const float* __restrict__ x, const float* __restrict__ a,
                                                              const float* __restrict__ ga, const float* __restrict__ b,
@@ -470,6 +608,7 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
     if (!status) return TBL_ERR_CUDA;
     const int D = m.d_model, B = batch;
     const size_t BD = static_cast<size_t>(B) * D;
+    if (sizeof(float) * (D + 32) > 48 * 1024) return TBL_ERR_SHAPE;   // the fused glue keeps a row of the residual stream in shared memory
     auto launched = [&]() { note_launch(); return cudaGetLastError() == cudaSuccess ? TBL_OK : TBL_ERR_CUDA; };
     auto linear = [&](const tbl_linear_view& v, const float* x, float* y) {
         return tbl_linear_forward(x, v.packed, v.strips, B > 64 ? v.w_i8 : nullptr, v.weight_scale, B, v.inputs, v.outputs,
@@ -485,49 +624,61 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         }
         return TBL_OK;
     };
-    auto norm = [&](const float* x, const float* w, float eps, float* out) {
-        return tbl_row_norm(x, nullptr, w, B, D, eps, out, 8, nullptr, nullptr, nullptr, stream);
-    };
-    auto residual = [&](const float* x, const float* a, const float* ga, const float* b, const float* gb, float* out, float* trace) {
-        const int64_t n = static_cast<int64_t>(BD);
-        const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-        gated_residual_kernel<<<grid, 256, 0, st>>>(x, a, ga, b, gb, B, D, out, trace);
+    // closes the pending residual add (x + a*ga [+ b*gb]) into `hidden_out` and opens the next stage with up to
+    // two norms of the sum; with ids: x is the embedding row
+    auto residual_norm = [&](const float* x, const int32_t* ids, const float* a, const float* ga, const float* b2,
+                             const float* gb, float eps, const float* w1, const float* w2, float* hidden_out, float* trace,
+                             float* out1, float* out2) {
+        residual_norm_kernel<<<B, kFusedThreads, sizeof(float) * (D + 32), st>>>(x, ids, m.embedding, m.vocab, a, ga, b2, gb, D, eps,
+                                                                                 w1, w2, hidden_out, trace, out1, out2);
         return launched();
     };
 
-    embedding_gather_kernel<<<B, 256, 0, st>>>(token_ids_dev, m.embedding, m.vocab, D, S.hidden[0], hidden_trace_dev);
-    if ((rc = launched()) != TBL_OK) return rc;
+    // The residual add that ends a block is carried as "pending" and applied by the kernel that opens the next
+    // stage: h = x_pending + (a*ga + b*gb).
+    struct Pending { const float* x; const int32_t* ids; const float* a; const float* ga; const float* b; const float* gb; };
+    Pending pend{nullptr, token_ids_dev, nullptr, nullptr, nullptr, nullptr};
     int cur = 0;
     for (int i = 0; i < m.n_blocks; ++i) {
         const tbl_decode_block& b = m.blocks[i];
         const tbl_mamba_block& mm = b.mamba;
-        const float* h = S.hidden[cur];
-        float* trace = hidden_trace_dev ? hidden_trace_dev + (static_cast<size_t>(i) + 1) * BD : nullptr;
-        if ((rc = norm(h, b.core_norm_w, b.core_norm_eps, S.core)) != TBL_OK) return rc;
-        // Mamba-2 branch: five projections of the normalised row, conv step, SSD step, gated norm, out projection
+        if (mm.d_inner > 16 * 1024) return TBL_ERR_SHAPE;
+        float* h = S.hidden[cur];
+        float* trace = hidden_trace_dev ? hidden_trace_dev + static_cast<size_t>(i) * BD : nullptr;
+        // hidden state entering this block (+ trace of the previous block's output), core norm and, in hybrid
+        // blocks, the attention branch's own norm of the same row
+        if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, b.core_norm_eps, b.core_norm_w,
+                                b.hybrid ? b.attn_norm_w : nullptr, h, trace, S.core, b.hybrid ? S.attn_in : nullptr)) != TBL_OK)
+            return rc;
+        // Mamba-2 branch: five projections of the normalised row, then conv step + SSD step + gated norm in one
+        // kernel, then the out projection
         const tbl_linear_view proj[5] = {mm.x, mm.z, mm.B, mm.C, mm.dt};
         if ((rc = group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK) return rc;
         const int GS = mm.n_groups * mm.d_state, conv_dim = mm.d_inner + 2 * GS;
-        mamba_conv_step_kernel<<<dim3((conv_dim + 255) / 256, B), 256, 0, st>>>(
-            S.proj, S.proj + 2 * S.proj_stride, S.proj + 3 * S.proj_stride, mm.conv_w, mm.conv_b, state.block[i].ring,
-            mm.d_inner, GS, mm.conv_kernel, S.xbc);
+        const size_t mix_smem = sizeof(float) * (conv_dim + mm.d_inner + 2 * mm.n_heads + 32);
+        if (mix_smem > 48 * 1024) {
+            static bool configured[64] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev < 0 || dev >= 64 || !configured[dev]) {
+                if (cudaFuncSetAttribute(mamba_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+                    return TBL_ERR_CUDA;
+                if (dev >= 0 && dev < 64) configured[dev] = true;
+            }
+        }
+        mamba_mix_kernel<<<B, kFusedThreads, mix_smem, st>>>(
+            S.proj, S.proj + S.proj_stride, S.proj + 2 * S.proj_stride, S.proj + 3 * S.proj_stride, S.proj + 4 * S.proj_stride,
+            mm.conv_w, mm.conv_b, mm.A_log, mm.D, mm.norm_w, state.block[i].ring, state.block[i].ssm, mm.n_heads, mm.d_head,
+            mm.d_state, mm.n_groups, mm.conv_kernel, mm.norm_eps, S.gated);
         if ((rc = launched()) != TBL_OK) return rc;
-        mamba_ssd_step_kernel<<<dim3((mm.d_inner + 127) / 128, B), 128, 0, st>>>(
-            S.xbc, S.proj + 4 * S.proj_stride, mm.A_log, mm.D, state.block[i].ssm, mm.n_heads, mm.d_head, mm.d_state,
-            mm.n_groups, S.y);
-        if ((rc = launched()) != TBL_OK) return rc;
-        rc = tbl_row_norm(S.y, S.proj + S.proj_stride, mm.norm_w, B, mm.d_inner, mm.norm_eps, S.gated, 8, nullptr, nullptr,
-                          nullptr, stream);
-        if (rc != TBL_OK) return rc;
         if ((rc = linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
         if (!b.hybrid) {
-            if ((rc = residual(h, S.mamba_out, nullptr, nullptr, nullptr, S.hidden[cur ^ 1], trace)) != TBL_OK) return rc;
+            pend = Pending{h, nullptr, S.mamba_out, nullptr, nullptr, nullptr};
             cur ^= 1;
             continue;
         }
         // attention branch on its own norm of the same residual stream
         const tbl_attention_block& a = b.attn;
-        if ((rc = norm(h, b.attn_norm_w, b.core_norm_eps, S.attn_in)) != TBL_OK) return rc;
         const tbl_linear_view qkv[2] = {a.q, a.kv};
         if ((rc = group(qkv, 2, S.attn_in, S.qkv, S.qkv_stride)) != TBL_OK) return rc;
         const size_t attn_smem = sizeof(float) * (3 * a.head_dim + kAttnThreads + capacity);
@@ -547,17 +698,22 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
             a.rope_cos, a.rope_sin, a.rope_positions, a.n_heads, a.n_kv_heads, a.head_dim, a.sliding_window, S.heads, status);
         if ((rc = launched()) != TBL_OK) return rc;
         if ((rc = linear(a.out, S.heads, S.attn_out)) != TBL_OK) return rc;
-        if ((rc = residual(h, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, S.res, nullptr)) != TBL_OK) return rc;
-        // FFN: norm -> up -> squared ReLU -> down, as one stack
-        if ((rc = norm(S.res, b.ff_norm_w, 1e-5f, S.ffn_in)) != TBL_OK) return rc;
-        // (two launches with the squared ReLU in the first one's epilogue: at this width a launch boundary is cheaper
-        // than the persistent stack's grid-wide layer boundary)
+        // res = h + (mamba*gate + attn*gate), and its norm for the FFN: up -> squared ReLU -> down (two launches with
+        // the squared ReLU in the first one's epilogue: at this width a launch boundary is cheaper than the persistent
+        // stack's grid-wide layer boundary)
+        if ((rc = residual_norm(h, nullptr, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, 1e-5f, b.ff_norm_w, nullptr, S.res,
+                                nullptr, S.ffn_in, nullptr)) != TBL_OK)
+            return rc;
         if ((rc = linear_view_forward(b.ffn_up, S.ffn_in, B, TBL_RMS_FAST, true, S.ffn_mid, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
         if ((rc = linear_view_forward(b.ffn_down, S.ffn_mid, B, TBL_RMS_FAST, false, S.ffn_out, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
-        if ((rc = residual(S.res, S.ffn_out, b.ffn_gate, nullptr, nullptr, S.hidden[cur ^ 1], trace)) != TBL_OK) return rc;
+        pend = Pending{S.res, nullptr, S.ffn_out, b.ffn_gate, nullptr, nullptr};
         cur ^= 1;
     }
-    if ((rc = norm(S.hidden[cur], m.final_norm_w, m.final_norm_eps, S.core)) != TBL_OK) return rc;
+    // the last block's residual add, the final norm and the LM head
+    float* last_trace = hidden_trace_dev ? hidden_trace_dev + static_cast<size_t>(m.n_blocks) * BD : nullptr;
+    if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, m.final_norm_eps, m.final_norm_w, nullptr,
+                            S.hidden[cur], last_trace, S.core, nullptr)) != TBL_OK)
+        return rc;
     if ((rc = linear(m.head, S.core, logits_dev)) != TBL_OK) return rc;
     advance_positions_kernel<<<(B + 127) / 128, 128, 0, st>>>(state.positions, B);
     return launched();

@@ -261,7 +261,7 @@ def time_decode(batch: int, iters: int = 50, context: int = 512, cfg: Optional[d
     params = synthetic_params(cfg, seed)
     eng = DecodeEngine(params, batch=batch, capacity=context + iters + 8)
     gen = torch.Generator().manual_seed(seed)
-    draw = lambda: torch.randint(0, cfg["vocab_size"], (batch,), generator=gen, dtype=torch.int32)
+    draw = lambda: torch.randint(0, cfg["vocab_size"], (batch,), generator=gen, dtype=torch.int32).cuda()
     eng.step(draw())
     launches = eng.capture()
     for _ in range(context - 1):             # fill the caches: the timed steps attend over `context` tokens

@@ -30,7 +30,11 @@ def main() -> None:
     ap.add_argument("--gated", action="store_true", help="row norm: SiLU gate first (the Mamba-2 epilogue)")
     ap.add_argument("--codes", choices=["no", "also", "only"], default="no",
                     help="row norm: also emit the int8 codes of the result, or only them (no fp32 store)")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="time tbl_chain_forward instead: a stack of this many --n x --k layers (n == k) on --m rows")
     args = ap.parse_args()
+    if args.chain:
+        return chain(args)
     if args.moe:
         return moe(args)
     if args.norm:
@@ -104,6 +108,72 @@ def main() -> None:
     print(json.dumps({"m": m, "n": n, "k": k, "us_per_call": round(us, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
                       "tops": round(2.0 * m * n * k / us / 1e6, 1), "weight_buffers": buffers,
                       "graph": not args.no_graph, "device_status": status}))
+
+
+def chain(args) -> None:
+    """A stack of square ternary layers through tbl_chain_forward (one persistent launch when the shape allows it)."""
+    import torch
+    from . import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the ternary linear path has no CPU fallback")
+    L = capi.lib()
+    torch.cuda.set_device(0)
+    m, n, k, layers = args.m, args.n, args.k, args.chain
+    if n != k or k % 16:
+        raise SystemExit("--chain needs n == k, a multiple of 16")
+    stream = torch.cuda.current_stream().cuda_stream
+    keep = []
+    views = (capi.LinearView * layers)()
+    for v in views:
+        words = torch.randint(0, 2 ** 31 - 1, (n * k // 16,), dtype=torch.int32, device="cuda") & 0x2AAAAAAA
+        strips = None
+        if k % 256 == 0:
+            strips = torch.empty(L.tbl_strip_bytes(n, k), dtype=torch.uint8, device="cuda")
+            capi.check(L.tbl_relayout_strips(words.data_ptr(), n, k, strips.data_ptr(), stream), "tbl_relayout_strips")
+        keep.extend([words, strips])
+        v.weight, v.magnitude, v.bias, v.w_i8 = None, None, None, None
+        v.packed = words.data_ptr()
+        v.strips = None if strips is None else strips.data_ptr()
+        v.inputs, v.outputs, v.activation_bits, v.rms_input, v.weight_scale = k, n, 8, 0, 0.016
+    x = torch.randn((m, k), device="cuda")
+    y = torch.empty((m, n), device="cuda")
+    ws_bytes = L.tbl_chain_workspace_bytes(views, layers, m)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+
+    def call() -> None:
+        capi.check(L.tbl_chain_forward(views, layers, None, x.data_ptr(), m, 0, y.data_ptr(), ws.data_ptr(), ws_bytes,
+                                       torch.cuda.current_stream().cuda_stream), "tbl_chain_forward")
+
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    before = L.tbl_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.no_graph:
+        e0.record()
+        for _ in range(args.iters):
+            call()
+        e1.record()
+        launches = (L.tbl_launch_count() - before) // args.iters
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+        launches = L.tbl_launch_count() - before
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.iters):
+            graph.replay()
+        e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / args.iters
+    algorithmic = layers * (n * k // 4 + 4 * m * k + 4 * m * n + 4 * (1 + m))
+    print(json.dumps({"chain": True, "layers": layers, "m": m, "n": n, "k": k, "us_per_stack": round(us, 2),
+                      "us_per_layer": round(us / layers, 2), "gb_per_s": round(algorithmic / us / 1e3, 1),
+                      "kernel_launches": int(launches), "graph": not args.no_graph,
+                      "device_status": L.tbl_device_status(stream)}))
 
 
 def norm(args) -> None:
