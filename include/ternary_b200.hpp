@@ -281,6 +281,28 @@ private:
     PackedState host_;
 };
 
+// launch_grouped_decode_projections with the reference's argument list (OXN/nsos/include/cuda/kernels.cuh:27-29,
+// OXN/nsos/src/cuda/moe_kernels.cu:779-784): `groups` linears on ONE input row, view g writing output + g*output_stride.
+// Differences a caller has to know: the descriptors are read on the HOST -- pass the host vector that
+// GpuProjectionGroup::forward fills before it uploads a device copy (OXN/nsos/src/gpu_projection_group.cpp:15-29) --
+// and `prepared` / `scales`, the caller's two ExecutionContext slots (float [groups*inputs] and float [groups],
+// gpu_projection_group.cpp:33-36), serve as this library's scratch: `prepared_floats` says how large the first is.
+// All views must share inputs, activation_bits and rms_input (the row is quantised once; the reference's own
+// callers satisfy this: Q/KV, Mamba x/z/B/C/dt).  Throws std::invalid_argument / std::runtime_error like the shim above.
+inline void launch_grouped_decode_projections(const tbl_linear_view* views_host, const float* input, float* prepared,
+                                              std::size_t prepared_floats, float* scales, float* output, int groups,
+                                              int output_stride, void* stream, int rms_mode = TBL_RMS_FAST) {
+    (void)scales;     // the per-row scale lives inside `prepared` here
+    if (!views_host || groups <= 0) throw std::invalid_argument("launch_grouped_decode_projections: no descriptors");
+    const std::size_t need = tbl_grouped_workspace_bytes(groups, views_host[0].inputs);
+    if (prepared_floats * sizeof(float) < need)
+        throw std::invalid_argument("launch_grouped_decode_projections: the GroupedPrepared slot is smaller than " +
+                                    std::to_string(need) + " bytes");
+    throw_on_status(tbl_grouped_forward(views_host, groups, input, output, output_stride, rms_mode, prepared,
+                                        prepared_floats * sizeof(float), stream),
+                    "launch_grouped_decode_projections");
+}
+
 // Sticky device status (bounded waits that gave up, MoE route overflow); synchronises the stream.
 inline void check_device(void* stream) {
     const int status = tbl_device_status(stream);

@@ -69,6 +69,41 @@ __global__ void __launch_bounds__(256) mamba_conv_step_kernel(const float* __res
     if (taps > 0) rr[static_cast<size_t>(taps - 1) * conv_dim + c] = current;
 }
 
+
+// One channel of the SSD recurrence: h[n] = decay*h[n] + (delta*B[n])*x ; y = D*x + sum_n h[n]*C[n], n ascending.
+// The state row is staged through registers in chunks of 16 so that its loads are issued together (a load placed
+// after the previous element's store would wait for it: the compiler cannot prove they do not alias).
+__device__ __forceinline__ float ssd_channel(float* __restrict__ st, const float* __restrict__ Bg, const float* __restrict__ Cg,
+                                             int N, float decay, float delta, float input, float y) {
+    int n0 = 0;
+    for (; n0 + 16 <= N; n0 += 16) {
+        float hv[16];
+        if ((reinterpret_cast<uintptr_t>(st + n0) & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 v = *reinterpret_cast<const float4*>(st + n0 + 4 * q);
+                hv[4 * q] = v.x; hv[4 * q + 1] = v.y; hv[4 * q + 2] = v.z; hv[4 * q + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < 16; ++n) hv[n] = st[n0 + n];
+        }
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            hv[n] = __fadd_rn(__fmul_rn(decay, hv[n]), __fmul_rn(__fmul_rn(delta, Bg[n0 + n]), input));
+            y = __fadd_rn(y, __fmul_rn(hv[n], Cg[n0 + n]));
+        }
+#pragma unroll
+        for (int n = 0; n < 16; ++n) st[n0 + n] = hv[n];
+    }
+    for (int n = n0; n < N; ++n) {
+        const float hv = __fadd_rn(__fmul_rn(decay, st[n]), __fmul_rn(__fmul_rn(delta, Bg[n]), input));
+        st[n] = hv;
+        y = __fadd_rn(y, __fmul_rn(hv, Cg[n]));
+    }
+    return y;
+}
+
 // ---- SSD recurrence step: h = decay*h + delta*B*x ; y = D*x + sum_n h*C -------------------------------------
 // One thread per (row, channel); delta = softplus(dt), decay = exp(-delta*exp(A_log)) in double.
 __global__ void __launch_bounds__(128) mamba_ssd_step_kernel(const float* __restrict__ xBC, const float* __restrict__ dt,
@@ -94,16 +129,9 @@ __global__ void __launch_bounds__(128) mamba_ssd_step_kernel(const float* __rest
     }
     const float* row = xBC + static_cast<size_t>(r) * conv_dim;
     const float input = row[chan];
-    float out = __fmul_rn(__ldg(Dp + h), input);
     float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
-    for (int n = 0; n < N; ++n) {
-        const float Bvalue = row[d_inner + group * N + n];
-        const float Cvalue = row[d_inner + GS + group * N + n];
-        const float hv = __fadd_rn(__fmul_rn(decay, st[n]), __fmul_rn(__fmul_rn(delta, Bvalue), input));
-        st[n] = hv;
-        out = __fadd_rn(out, __fmul_rn(hv, Cvalue));
-    }
-    y[static_cast<size_t>(r) * d_inner + chan] = out;
+    y[static_cast<size_t>(r) * d_inner + chan] = ssd_channel(st, row + d_inner + group * N, row + d_inner + GS + group * N, N, decay,
+                                                           delta, input, __fmul_rn(__ldg(Dp + h), input));
 }
 
 // ---- single-token attention over the KV cache ----------------------------------------------------------------
@@ -330,13 +358,9 @@ mamba_mix_kernel(const float* __restrict__ xv, const float* __restrict__ zv, con
         const int group = (h * n_groups) / n_heads;
         const float delta = delta_s[h], decay = decay_s[h];
         const float input = xbc[chan];
-        float y = __fmul_rn(__ldg(Dp + h), input);
         float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
-        for (int n = 0; n < N; ++n) {
-            const float hv = __fadd_rn(__fmul_rn(decay, st[n]), __fmul_rn(__fmul_rn(delta, xbc[d_inner + group * N + n]), input));
-            st[n] = hv;
-            y = __fadd_rn(y, __fmul_rn(hv, xbc[d_inner + GS + group * N + n]));
-        }
+        const float y = ssd_channel(st, xbc + d_inner + group * N, xbc + d_inner + GS + group * N, N, decay, delta, input,
+                                    __fmul_rn(__ldg(Dp + h), input));
         const float gv = __fmul_rn(y, silu_two_sided(zv[static_cast<size_t>(r) * d_inner + chan]));
         gated[chan] = gv;
         ss += gv * gv;

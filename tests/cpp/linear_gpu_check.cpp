@@ -112,6 +112,27 @@ int main(int argc, char** argv) {
         tbl_linear_view view;
         CHECK(layer.prepare_gpu_decode_view(view));
         CHECK(view.inputs == K && view.outputs == N && view.packed != nullptr && view.rms_input == (exact ? 0 : 1));
+        // the grouped seam with the reference's argument list: two descriptors of this layer on the first input row
+        {
+            const tbl_linear_view views[2] = {view, view};
+            const size_t prepared_floats = 2 * static_cast<size_t>(K) + 1024;
+            float *prepared = nullptr, *scales = nullptr, *grouped = nullptr;
+            CHECK(cudaMalloc(reinterpret_cast<void**>(&prepared), prepared_floats * 4) == cudaSuccess &&
+                  cudaMalloc(reinterpret_cast<void**>(&scales), 2 * 4) == cudaSuccess &&
+                  cudaMalloc(reinterpret_cast<void**>(&grouped), 2 * static_cast<size_t>(N) * 4) == cudaSuccess);
+            tb::launch_grouped_decode_projections(views, dx, prepared, prepared_floats, scales, grouped, 2, N, stream,
+                                                  TBL_RMS_REFERENCE_ORDER);
+            std::vector<float> rows(2 * static_cast<size_t>(N));
+            cudaMemcpyAsync(rows.data(), grouped, rows.size() * 4, cudaMemcpyDeviceToHost, stream);
+            tb::check_device(stream);
+            CHECK(std::memcmp(rows.data(), want.data(), static_cast<size_t>(N) * 4) == 0);
+            CHECK(std::memcmp(rows.data() + N, want.data(), static_cast<size_t>(N) * 4) == 0);
+            bool small = false;
+            try { tb::launch_grouped_decode_projections(views, dx, prepared, 8, scales, grouped, 2, N, stream); }
+            catch (const std::invalid_argument&) { small = true; }
+            CHECK(small);
+            cudaFree(prepared); cudaFree(scales); cudaFree(grouped);
+        }
         cudaFree(dx); cudaFree(dy); cudaFree(scratch);
     }
     CHECK(live_allocations == 0);     // the layer released everything it was given
