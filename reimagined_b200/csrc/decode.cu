@@ -323,47 +323,131 @@ mamba_mix_kernel(const float* __restrict__ xv, const float* __restrict__ zv, con
     const int r = blockIdx.x;
     const int taps = K - 1;
     float* rr = ring + static_cast<size_t>(r) * (taps > 0 ? taps : 1) * conv_dim;
-    for (int c = threadIdx.x; c < conv_dim; c += blockDim.x) {
-        const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
-                                          : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
-                                                              : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
-        float value = __ldg(conv_b + c);
-        for (int j = 0; j < K; ++j) {
-            const float tap = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
-            value = __fadd_rn(value, __fmul_rn(__ldg(conv_w + static_cast<size_t>(c) * K + j), tap));
+    // The kernel runs as one CTA per sequence, so its duration is a sum of memory round trips: every phase issues
+    // all of a thread's loads before it uses any of them (kBatch channels at a time).
+    constexpr int kBatch = 4, kMaxK = 4;
+    // per-head step sizes and decays, by the last warp while the others start on the convolution
+    if (static_cast<int>(threadIdx.x) >= static_cast<int>(blockDim.x) - 32) {
+        for (int h = threadIdx.x - (blockDim.x - 32); h < n_heads; h += 32) {
+            const float dt_raw = dt[static_cast<size_t>(r) * n_heads + h];
+            const float a_log = __ldg(A_log + h);
+            const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
+            float decay;
+            if (!isfinite(dt_raw) || !isfinite(a_log)) {
+                decay = nanf("");
+            } else {
+                const double log_delta = dt_raw < -20.0f ? static_cast<double>(dt_raw) : log(static_cast<double>(delta));
+                const double log_q = log_delta + static_cast<double>(a_log);
+                decay = log_q > 50.0 ? 0.0f : static_cast<float>(exp(-exp(log_q)));
+            }
+            delta_s[h] = delta;
+            decay_s[h] = decay;
         }
-        xbc[c] = silu_stable(value);
-        for (int s2 = 0; s2 + 1 < taps; ++s2) rr[static_cast<size_t>(s2) * conv_dim + c] = rr[static_cast<size_t>(s2 + 1) * conv_dim + c];
-        if (taps > 0) rr[static_cast<size_t>(taps - 1) * conv_dim + c] = current;
     }
-    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
-        const float dt_raw = dt[static_cast<size_t>(r) * n_heads + h];
-        const float a_log = __ldg(A_log + h);
-        const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
-        float decay;
-        if (!isfinite(dt_raw) || !isfinite(a_log)) {
-            decay = nanf("");
+    for (int c0 = threadIdx.x; c0 < conv_dim; c0 += blockDim.x * kBatch) {
+        float tapv[kBatch][kMaxK], wv[kBatch][kMaxK], bias[kBatch];
+        if (K <= kMaxK) {
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int c = c0 + i * blockDim.x;
+                if (c < conv_dim) {
+                    const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
+                                                      : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
+                                                                          : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
+#pragma unroll
+                    for (int j = 0; j < kMaxK; ++j) {
+                        if (j < K) {
+                            tapv[i][j] = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
+                            wv[i][j] = __ldg(conv_w + static_cast<size_t>(c) * K + j);
+                        }
+                    }
+                    bias[i] = __ldg(conv_b + c);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int c = c0 + i * blockDim.x;
+                if (c < conv_dim) {
+                    float value = bias[i];
+#pragma unroll
+                    for (int j = 0; j < kMaxK; ++j)
+                        if (j < K) value = __fadd_rn(value, __fmul_rn(wv[i][j], tapv[i][j]));
+                    xbc[c] = silu_stable(value);
+                    // the window moves on: taps 1.. become 0.., the newest input goes last
+#pragma unroll
+                    for (int j = 0; j + 1 < kMaxK; ++j)
+                        if (j < taps) rr[static_cast<size_t>(j) * conv_dim + c] = tapv[i][j + 1];
+                }
+            }
         } else {
-            const double log_delta = dt_raw < -20.0f ? static_cast<double>(dt_raw) : log(static_cast<double>(delta));
-            const double log_q = log_delta + static_cast<double>(a_log);
-            decay = log_q > 50.0 ? 0.0f : static_cast<float>(exp(-exp(log_q)));
+            for (int i = 0; i < kBatch; ++i) {
+                const int c = c0 + i * blockDim.x;
+                if (c >= conv_dim) break;
+                const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
+                                                  : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
+                                                                      : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
+                float value = __ldg(conv_b + c);
+                for (int j = 0; j < K; ++j) {
+                    const float tap = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
+                    value = __fadd_rn(value, __fmul_rn(__ldg(conv_w + static_cast<size_t>(c) * K + j), tap));
+                }
+                xbc[c] = silu_stable(value);
+                for (int s2 = 0; s2 + 1 < taps; ++s2) rr[static_cast<size_t>(s2) * conv_dim + c] = rr[static_cast<size_t>(s2 + 1) * conv_dim + c];
+                if (taps > 0) rr[static_cast<size_t>(taps - 1) * conv_dim + c] = current;
+            }
         }
-        delta_s[h] = delta;
-        decay_s[h] = decay;
     }
     __syncthreads();
     float ss = 0.0f;
-    for (int chan = threadIdx.x; chan < d_inner; chan += blockDim.x) {
-        const int h = chan / d_head;
-        const int group = (h * n_groups) / n_heads;
-        const float delta = delta_s[h], decay = decay_s[h];
-        const float input = xbc[chan];
-        float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
-        const float y = ssd_channel(st, xbc + d_inner + group * N, xbc + d_inner + GS + group * N, N, decay, delta, input,
-                                    __fmul_rn(__ldg(Dp + h), input));
-        const float gv = __fmul_rn(y, silu_two_sided(zv[static_cast<size_t>(r) * d_inner + chan]));
-        gated[chan] = gv;
-        ss += gv * gv;
+    for (int ch0 = threadIdx.x; ch0 < d_inner; ch0 += blockDim.x * kBatch) {
+        float zval[kBatch], dval[kBatch];
+        float hv[kBatch][16];
+        const bool fast = N == 16;
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int chan = ch0 + i * blockDim.x;
+            if (chan < d_inner) {
+                zval[i] = zv[static_cast<size_t>(r) * d_inner + chan];
+                dval[i] = __ldg(Dp + chan / d_head);
+                if (fast) {
+                    const float4* st4 = reinterpret_cast<const float4*>(state + (static_cast<size_t>(r) * d_inner + chan) * 16);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 v = st4[q];
+                        hv[i][4 * q] = v.x; hv[i][4 * q + 1] = v.y; hv[i][4 * q + 2] = v.z; hv[i][4 * q + 3] = v.w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int chan = ch0 + i * blockDim.x;
+            if (chan < d_inner) {
+                const int h = chan / d_head;
+                const int group = (h * n_groups) / n_heads;
+                const float delta = delta_s[h], decay = decay_s[h];
+                const float input = xbc[chan];
+                const float* Bg = xbc + d_inner + group * N;
+                const float* Cg = xbc + d_inner + GS + group * N;
+                float* st = state + (static_cast<size_t>(r) * d_inner + chan) * N;
+                float y = __fmul_rn(dval[i], input);
+                if (fast) {
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) {
+                        hv[i][n] = __fadd_rn(__fmul_rn(decay, hv[i][n]), __fmul_rn(__fmul_rn(delta, Bg[n]), input));
+                        y = __fadd_rn(y, __fmul_rn(hv[i][n], Cg[n]));
+                    }
+                    float4* st4 = reinterpret_cast<float4*>(st);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) st4[q] = make_float4(hv[i][4 * q], hv[i][4 * q + 1], hv[i][4 * q + 2], hv[i][4 * q + 3]);
+                } else {
+                    y = ssd_channel(st, Bg, Cg, N, decay, delta, input, y);
+                }
+                const float gv = __fmul_rn(y, silu_two_sided(zval[i]));
+                gated[chan] = gv;
+                ss += gv * gv;
+            }
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d_inner)), eps)));
