@@ -43,7 +43,7 @@ sys.path.insert(0, ROOT)
 
 K_DIM = 16384
 N_DIM = 16384
-LAYERS = 6
+LAYERS = 16
 ROWS = 1
 METRIC = "ternary_gemv_hbm_gbs"
 UNIT = "GB/s"

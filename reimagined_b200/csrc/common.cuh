@@ -82,6 +82,20 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
+// The same copy for data that is read once (a weight stream): the lines are marked evict-first in L2, so that the
+// stream does not push out the small buffers other CTAs are about to read.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
 // 128-bit load from a 32-bit shared-space address (keeps the access an LDS with 32-bit address
 // arithmetic instead of a generic load the compiler cannot always prove to be shared).
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {

@@ -98,7 +98,7 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
                                                   const bool rms_fast, const float q_max, const unsigned* sync,
                                                   const unsigned target, const bool first_layer, const int par,
                                                   uint8_t* acts_resident, ConsumerState* cs, int* status,
-                                                  unsigned long long* trace) {
+                                                  unsigned long long* trace, const bool paired) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_groups = R * K / 16;
     constexpr int kRows = SINGLE ? 1 : kMaxRows;
@@ -249,7 +249,19 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
             }
             const int e = (threadIdx.x + i * kT) * 16;
             const uint4 codes = transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
-            *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) = codes;
+            if (SINGLE && paired) {
+                // single-row order of the full-stage path: word j of quarter x sits beside word j of quarter x ^ 1
+                // (128-bit slot 2 * (x >> 1) + (j >> 1), word 2 * (j & 1) + (x & 1)), so that the two B registers of
+                // an MMA come out of one 128-bit load as an aligned register pair and need no moves
+                const int kb = e >> 8, r = e & 255, tq = r >> 6, xq = (r >> 4) & 3;
+                uint32_t* dst = reinterpret_cast<uint32_t*>(acts_resident + kb * 256 + (xq >> 1) * 128 + tq * 16) + (xq & 1);
+                dst[0] = codes.x;
+                dst[2] = codes.y;
+                dst[16] = codes.z;
+                dst[18] = codes.w;
+            } else {
+                *reinterpret_cast<uint4*>(acts_resident + qp_offset(m, R, K, e - m * K)) = codes;
+            }
         }
     }
 #pragma unroll
@@ -329,6 +341,7 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
         const int par = l & 1;
 
         if (producer) {
+            const uint64_t stream_policy = l2_evict_first_policy();
             for (int s = s_begin; s < s_end && alive;) {
                 const int cnt = min(slots, s_end - s);
                 const int local = s;
@@ -351,9 +364,9 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                     if (lane < ((nb + 3) >> 2)) {
                         const int sl = slab + lane;
                         const int sbs = min(4, nblk - 4 * sl);
-                        bulk_g2s(wst + lane * cnt * 4096,
-                                 L.strips + ((static_cast<size_t>(4) * sl * nstrips + static_cast<size_t>(local) * sbs) << 10),
-                                 cnt * sbs * 1024, &full[st]);
+                        bulk_g2s_hint(wst + lane * cnt * 4096,
+                                      L.strips + ((static_cast<size_t>(4) * sl * nstrips + static_cast<size_t>(local) * sbs) << 10),
+                                      cnt * sbs * 1024, &full[st], stream_policy);
                     }
                 }
             }
@@ -371,9 +384,9 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
             const unsigned target = l > 0 ? static_cast<unsigned>((P.layer[l - 1].N + 15) >> 4) : 0u;
             const bool ok = R == 1
                 ? quantise_resident<true>(xin, R, K, L.rms_fast != 0, L.q_max, sync, target, l == 0, par, acts_resident,
-                                          cs, P.status, tr)
+                                          cs, P.status, tr, fast)
                 : quantise_resident<false>(xin, R, K, L.rms_fast != 0, L.q_max, sync, target, l == 0, par, acts_resident,
-                                           cs, P.status, tr);
+                                           cs, P.status, tr, false);
             if (!ok) { alive = false; break; }
         } else if (l == 0) {
             asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
@@ -420,8 +433,9 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                             const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
 #pragma unroll
                             for (int xp = 0; xp < 2; ++xp) {
-                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
-                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
+                                // paired order: the 128-bit slot 2 * xp + (j >> 1) holds {b0, b1} of positions j, j + 1
+                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].z, o.b[2 * xp + 1].x, o.b[2 * xp + 1].z};
+                                const uint32_t b1[4] = {o.b[2 * xp].y, o.b[2 * xp].w, o.b[2 * xp + 1].y, o.b[2 * xp + 1].w};
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const uint32_t mk = 0x03030303u << (2 * j);
