@@ -6,6 +6,8 @@ The shared library lands beside this file so it travels with the source tree.
 """
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import subprocess
 import sys
@@ -23,18 +25,45 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-li
          "-Xptxas", "-v"]
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB):
-        return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+STAMP = LIB + ".sources"
+
+
+def _digest() -> str:
+    """SHA-256 over the sources, the public header and the flags: what the library was built from."""
+    h = hashlib.sha256(" ".join(FLAGS).encode())
+    deps = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC))
     deps.append(os.path.join(HERE, "..", "include", "ternary_b200.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale() -> bool:
+    # by content, not by time stamp: a copy of the tree (another machine, a fresh checkout) keeps the library valid
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
+        return True
+    with open(STAMP) as f:
+        return f.read().strip() != _digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
+    # one builder at a time: several ranks of one job may get here together
+    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    with open(os.path.join(HERE, "build", "lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if force or _stale():
+                _compile(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return LIB
+
+
+def _compile(verbose: bool) -> None:
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
@@ -55,8 +84,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         print("\n".join(log))
     if failed:
         raise RuntimeError("nvcc failed; see output above")
-    subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], check=True)
-    return LIB
+    # link beside the target and rename: a process that is loading the old library never sees a half-written file
+    tmp = LIB + ".tmp"
+    subprocess.run([NVCC, "-shared", "-o", tmp, *objs, "-lcudart"], check=True)
+    os.replace(tmp, LIB)
+    with open(STAMP, "w") as f:
+        f.write(_digest())
 
 
 if __name__ == "__main__":
