@@ -16,6 +16,12 @@
 // end and stores rows with plain coalesced stores instead of box stores.
 // The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1; the next
 // block's tcgen05.ld is issued before the current block is converted and stored.
+// Tall mode (MT = 2, large problems): a tile is 256 activation rows x 256 weight rows -- two M = 128 MMAs per
+// k-step share one weight box, which cuts the operand bytes fetched through L2 per output by a third (the kernel
+// is bound by that fetch at 8192-deep K, not by the tensor pipe).  The two accumulators then are the two halves
+// of one tile: the epilogue of a tile overlaps the next tile's main loop only while its first half drains.
+// Tiles are walked in groups of kGroupM row tiles x all column tiles, so that the tiles in flight at any time
+// share a few activation and weight boxes in L2.
 // Every wait is bounded: on a timeout the role records the status word and falls through to
 // the common exit, where TMEM is released.
 #include <cuda.h>
@@ -33,7 +39,8 @@ constexpr int BM = 128;          // activation rows per tile (UMMA M)
 constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
 // ring depth: what fits beside the 32 KB of epilogue staging (narrow tiles get a deeper ring: with few
 // rows the kernel streams weights and wants more bytes in flight per SM)
-__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8); }
+__host__ __device__ constexpr int stages_for(int bn, int mt = 1) { return mt == 2 ? 3 : (bn >= 256 ? 4 : (bn >= 128 ? 6 : 8)); }
+constexpr int kGroupM = 16;      // row tiles per group of the tile walk
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;        // two warps per TMEM lane quarter, each taking every other 32-column block
 constexpr int kThreads = 32 * (2 + kEpiWarps);
@@ -69,13 +76,17 @@ struct GroupTable {
 struct NoGroups {};
 
 // Tile t of the launch -> (problem, first row in the shared arrays, rows left in the problem, n-tile).
-template <bool GROUPED, typename Table>
+template <bool GROUPED, int MT, typename Table>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Table& gt, int t, int& g, int& row0, int& rows,
                                             int& tn) {
     if constexpr (!GROUPED) {
         if (t >= p.tiles_m * p.tiles_n) return false;
-        const int tm = t % p.tiles_m;
-        g = 0; tn = t / p.tiles_m; row0 = tm * 128; rows = p.M - row0;
+        // groups of kGroupM row tiles; inside a group the row tile runs fastest, then the column tile
+        const int per_group = kGroupM * p.tiles_n;
+        const int grp = t / per_group, in_grp = t - grp * per_group;
+        const int gm = min(kGroupM, p.tiles_m - grp * kGroupM);
+        const int tm = grp * kGroupM + in_grp % gm;
+        g = 0; tn = in_grp / gm; row0 = tm * (128 * MT); rows = p.M - row0;
         return true;
     } else {
         int base = 0;
@@ -97,7 +108,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Table& gt
 using namespace tc05;
 
 
-template <int BN, bool GROUPED>
+template <int BN, bool GROUPED, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_y, const GemmParams p,
@@ -105,8 +116,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int kStages = stages_for(BN);
-    constexpr int kABytes = BM * BK;
+    static_assert(MT == 1 || (BN == 256 && !GROUPED), "tall tiles: 256 x 256, plain mode");
+    constexpr int kStages = stages_for(BN, MT);
+    constexpr int kABytes = MT * BM * BK;
     constexpr int kBBytes = BN * BK;
     constexpr int kStageBytes = kABytes + kBBytes;
     uint8_t* epi_stage = smem + kStages * kStageBytes;                 // 8 warps x 4 KB
@@ -141,7 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             bool alive = true;
             int g, row0, rows, tn;
-            for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn); tile += gridDim.x) {
+            for (int tile = blockIdx.x; alive && decode_tile<GROUPED, MT>(p, gt, tile, g, row0, rows, tn); tile += gridDim.x) {
                 const CUtensorMap* bmap = &map_b;
                 if constexpr (GROUPED) bmap = &gt.b[g];
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -156,6 +168,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // (grouped: rows past the problem's last belong to the next problem or lie past the
                     // array, where the copy fills zeros; their accumulator rows are never stored)
                     tma_load_2d(a_dst, &map_a, kb * BK, row0, &full[s]);
+                    if constexpr (MT == 2) tma_load_2d(a_dst + BM * BK, &map_a, kb * BK, row0 + BM, &full[s]);
                     tma_load_2d(b_dst, bmap, kb * BK, tn * BN, &full[s]);
                 }
             }
@@ -169,15 +182,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0, local = 0;
             bool alive = true;
             int g, row0, rows, tn;
-            for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn);
+            for (int tile = blockIdx.x; alive && decode_tile<GROUPED, MT>(p, gt, tile, g, row0, rows, tn);
                  tile += gridDim.x, ++local) {
+                // MT == 1: the tile's accumulator is buffer local & 1.  MT == 2: both buffers, one per half of the tile.
                 const int buf = local & 1;
-                if (local >= 2) {
-                    alive = mbar_wait_bounded(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status);
-                    if (!alive) break;
+                if constexpr (MT == 1) {
+                    if (local >= 2) {
+                        alive = mbar_wait_bounded(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status);
+                        if (!alive) break;
+                    }
+                } else {
+                    if (local >= 1) {
+                        alive = mbar_wait_bounded(&tmem_empty[0], (local - 1) & 1, p.status) &&
+                                mbar_wait_bounded(&tmem_empty[1], (local - 1) & 1, p.status);
+                        if (!alive) break;
+                    }
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + (MT == 1 ? buf * BN : 0);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
                     alive = mbar_wait_bounded(&full[s], (it / kStages) & 1, p.status);
@@ -186,13 +208,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 32; ++kk) {
-                        umma_i8(d_tmem, smem_desc_sw128(a_addr + kk * 32), smem_desc_sw128(b_addr + kk * 32), idesc,
-                                (kb | kk) != 0 ? 1u : 0u);
+                    for (int h = 0; h < MT; ++h) {
+#pragma unroll
+                        for (int kk = 0; kk < BK / 32; ++kk) {
+                            umma_i8(d_tmem + h * BN, smem_desc_sw128(a_addr + h * (BM * BK) + kk * 32),
+                                    smem_desc_sw128(b_addr + kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty[s]);   // stage reusable once these MMAs have read it
                 }
-                if (alive) umma_commit(&tmem_full[buf]);
+                if (alive) {
+                    if constexpr (MT == 1) {
+                        umma_commit(&tmem_full[buf]);
+                    } else {
+                        umma_commit(&tmem_full[0]);
+                        umma_commit(&tmem_full[1]);
+                    }
+                }
             }
         }
     } else {
@@ -202,14 +234,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint8_t* stage = epi_stage + (warp - 2) * 4096;
         int local = 0;
         bool alive = true;
-        int g, row0, rows, tn;
-        for (int tile = blockIdx.x; alive && decode_tile<GROUPED>(p, gt, tile, g, row0, rows, tn);
+        int g, tile_row0, tile_rows, tn;
+        for (int tile = blockIdx.x; alive && decode_tile<GROUPED, MT>(p, gt, tile, g, tile_row0, tile_rows, tn);
              tile += gridDim.x, ++local) {
-            const int buf = local & 1;
-            alive = mbar_wait_bounded(&tmem_full[buf], (local >> 1) & 1, p.status);
+          for (int h = 0; h < MT && alive; ++h) {
+            // MT == 1: buffer local & 1 holds the tile.  MT == 2: buffer h holds rows h * 128 .. of the tile.
+            const int buf = MT == 1 ? (local & 1) : h;
+            alive = mbar_wait_bounded(&tmem_full[buf], (MT == 1 ? (local >> 1) : local) & 1, p.status);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
+            const int row0 = tile_row0 + h * BM, rows = tile_rows - h * BM;
             const int m = row0 + quarter * 32 + lane;            // row in the activation / output arrays
             const bool row_ok = quarter * 32 + lane < rows;
             float wscale = p.weight_scale;
@@ -301,6 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -315,11 +351,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 
-template <int BN>
+template <int BN, int MT = 1>
 cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const GemmParams& p,
                       cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN, false>;
-    const size_t smem = 1024 + stages_for(BN) * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
+    auto kernel = gemm_tcgen05_kernel<BN, false, MT>;
+    const size_t smem = 1024 + stages_for(BN, MT) * (MT * BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -338,7 +374,7 @@ cudaError_t launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
 template <int BN>
 cudaError_t launch_grouped_bn(const CUtensorMap& ma, const GemmParams& p, const GroupTable& gt, int grid,
                               cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN, true>;
+    auto kernel = gemm_tcgen05_kernel<BN, true, 1>;
     const size_t smem = 1024 + stages_for(BN) * (BM * BK + BN * BK) + kEpiWarps * 4096 + 256;
     static bool configured[64] = {};
     int dev = 0;
@@ -419,7 +455,10 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
         // few rows: the launch streams the weights once and wants every SM pulling -- narrower tiles
         if (bn == 128 && t128 < 100 && N > 64) bn = 64;
     }
-    p.tiles_m = (M + BM - 1) / BM;
+    // tall tiles (256 x 256) where they still give every SM several tiles: a third fewer operand bytes per output
+    const long long tall_tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const bool tall = bn == 256 && tall_tiles >= 4 * kNumSm;
+    p.tiles_m = tall ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     // TMA stores need a 16-byte row pitch and base
     p.use_tma_store = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
@@ -431,6 +470,7 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
     } else {
         my = ma;  // unused
     }
+    if (tall) return launch_bn<256, 2>(ma, mb, my, p, stream);
     return bn == 256 ? launch_bn<256>(ma, mb, my, p, stream)
                      : (bn == 128 ? launch_bn<128>(ma, mb, my, p, stream) : launch_bn<64>(ma, mb, my, p, stream));
 }

@@ -71,6 +71,25 @@ def test_sweep_grid_at_full_size(cuda, port, tbl, size, M):
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(5000, 7680, 512), (4999, 7712, 640), (9000, 4200, 256)])
+def test_tall_tiles_with_ragged_edges(cuda, port, tbl, M, N, K):
+    """Large prefill problems run on 256 x 256 tiles (two accumulator halves per tile); rows and columns that
+    do not fill the last tile, and a last group of row tiles shorter than the others."""
+    import gpu_helpers as H
+    from oracle import fast
+    rng = np.random.default_rng(M + N + K)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02))
+    words, scale = _pack_with_library(tbl, w)
+    t = port.unpack_i8(words, N, K)
+    dwords = H.words_dev(words)
+    i8 = H.expand_i8(dwords, N, K)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    y = H.linear_forward(H.dev(x), dwords, scale, N, w_i8=i8).cpu().numpy()
+    want, *_ = fast.linear_forward(x, t, scale)
+    assert bits_equal(y, want), f"M={M} N={N} K={K}: {int((y != want).sum())} of {y.size} outputs differ"
+    assert H.device_status() == 0
+
+
 @pytest.mark.parametrize("size,M", [(8192, 128), (16384, 64), (16384, 128)])
 def test_sweep_grid_two_bit_weights_only(cuda, port, tbl, size, M):
     """The same layer without its int8 expansion: every M must still be served from the 2-bit strips."""
