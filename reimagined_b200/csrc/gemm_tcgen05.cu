@@ -41,6 +41,11 @@ constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
 // rows the kernel streams weights and wants more bytes in flight per SM)
 __host__ __device__ constexpr int stages_for(int bn, int mt = 1) { return mt == 2 ? 3 : (bn >= 256 ? 4 : (bn >= 128 ? 6 : 8)); }
 constexpr int kGroupM = 16;      // row tiles per group of the tile walk
+// Tall mode pays once every SM has a 256 x 256 tile and the k-loop is long enough to amortise the undoubled
+// accumulator (measured: 1024 x 16384 x 16384 +13 %, 4096^3 +3 %, 8192 x 2048 x 2048 -1 %, 1024 x 4096 x 4096 -34 %).
+__host__ inline bool tall_tiles_pay(long long tall_tiles, int K) {
+    return tall_tiles >= 4 * 148 || (tall_tiles >= 148 && K >= 4096);
+}
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;        // two warps per TMEM lane quarter, each taking every other 32-column block
 constexpr int kThreads = 32 * (2 + kEpiWarps);
@@ -444,9 +449,12 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
     p.weight_scale = weight_scale; p.M = M; p.K = K; p.N = N;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
-    // tile width: 256 unless the narrower tile fills the 148 SMs clearly better (wave quantisation)
+    // tall tiles (256 x 256) where there are enough of them: a third fewer operand bytes through L2 per output
+    const long long tall_tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const bool tall = N >= 256 && tall_tiles_pay(tall_tiles, K);
+    // otherwise the tile width: 256 unless the narrower tile fills the 148 SMs clearly better (wave quantisation)
     int bn = N > 128 ? 256 : 128;
-    if (bn == 256) {
+    if (bn == 256 && !tall) {
         const long long tm = (M + BM - 1) / BM;
         const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
         const double e256 = static_cast<double>(t256) / (((t256 + kNumSm - 1) / kNumSm) * kNumSm);
@@ -455,9 +463,6 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
         // few rows: the launch streams the weights once and wants every SM pulling -- narrower tiles
         if (bn == 128 && t128 < 100 && N > 64) bn = 64;
     }
-    // tall tiles (256 x 256) where they still give every SM several tiles: a third fewer operand bytes per output
-    const long long tall_tiles = static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    const bool tall = bn == 256 && tall_tiles >= 4 * kNumSm;
     p.tiles_m = tall ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     // TMA stores need a 16-byte row pitch and base
