@@ -442,8 +442,10 @@ def decode_section(H: Harness, steps: int):
 
 
 def colsplit_section(H: Harness, L, capi, layers):
-    """The 16384-wide layer split by output columns over the ranks: each rank's linear writes its [M, N/g] block into
-    its slot of the gather buffer, one in-place NCCL all-gather, one re-tile pass over local memory."""
+    """The 16384-wide layer split by output columns over the ranks, two ways: (1) each rank's linear writes its
+    [M, N/g] block into its slot of the gather buffer, one in-place NCCL all-gather, one re-tile pass over local
+    memory; (2) fused: the GEMM epilogue stores every tile into all ranks' copies of the output over NVLink
+    (tbl_linear_forward_scatter), then one barrier across the ranks."""
     torch, dist = H.torch, H.dist
     from reimagined_b200 import sharding
     g, r = H.world, H.rank
@@ -495,6 +497,32 @@ def colsplit_section(H: Harness, L, capi, layers):
         ms_one = H.timed(unsharded, reps) / reps
         rows = torch.linspace(0, M - 1, 16).long().cuda()
         same = bool(torch.equal(y[rows], y_full[rows]))
+        # (2) the exchange fused into the GEMM epilogue
+        fused = None
+        try:
+            import ctypes
+            peer = sharding.PeerOutput(M, n)
+            order = [(r + 1 + i) % g for i in range(g)]
+            dests = (ctypes.c_void_p * g)(*[peer.pointers[q] for q in order])
+
+            def fused_step():
+                capi.check(L.tbl_linear_forward_scatter(x.data_ptr(), w8.data_ptr(), scale, M, k, n_local, 8, 0, None, None, dests,
+                                                        g, n, n_local * r, ws.data_ptr(), ws_bytes,
+                                                        torch.cuda.current_stream().cuda_stream), "tbl_linear_forward_scatter")
+                peer.barrier()
+
+            for _ in range(3):
+                fused_step()
+            ms_fused = H.timed(fused_step, reps) / reps
+            fused_same = bool(torch.equal(peer.tensor[rows], y_full[rows]))
+            sent = M * n_local * 4 * (g - 1)
+            fused = {"total_us": ms_fused * 1e3, "matches_unsharded_bit_for_bit": fused_same,
+                     "bytes_stored_to_peers_per_gpu": sent, "nvlink_out_gbs_per_gpu": sent / (ms_fused * 1e-3) / 1e9,
+                     "speedup_vs_one_gpu": ms_one / ms_fused, "strong_scaling_efficiency": ms_one / ms_fused / g,
+                     "speedup_vs_all_gather_path": ms_total / ms_fused}
+            del peer
+        except Exception as exc:      # no peer mapping on this box: the all-gather path above stands alone
+            fused = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
         gathered_bytes = M * n * 4
         out.append({"M": M, "K": k, "N": n, "columns_per_gpu": n_local, "matches_unsharded_bit_for_bit": same,
                     "compute_us": ms_compute * 1e3, "all_gather_us": ms_gather * 1e3, "retile_us": ms_retile * 1e3,
@@ -502,7 +530,7 @@ def colsplit_section(H: Harness, L, capi, layers):
                     "all_gather_bus_gbs": gathered_bytes * (g - 1) / g / (ms_gather * 1e-3) / 1e9,
                     "all_gather_share_of_total": ms_gather / ms_total,
                     "unsharded_one_gpu_us": ms_one * 1e3, "speedup_vs_one_gpu": ms_one / ms_total,
-                    "strong_scaling_efficiency": ms_one / ms_total / g})
+                    "strong_scaling_efficiency": ms_one / ms_total / g, "fused_epilogue_exchange": fused})
         del w8, w8_full, stacked, y, y_full, x
         torch.cuda.empty_cache()
     return out
@@ -518,6 +546,8 @@ def run_ours(args):
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    # peer mappings of the column-split output are plain (no NVLink multicast object is bound to them)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the ternary linear path has no CPU fallback")

@@ -165,6 +165,22 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
                        const float* magnitude_dev, const float* bias_dev, float* y_dev,
                        void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* The same forward for a column-split layer whose output every GPU of the node needs whole: this GPU holds
+ * the weight rows [col0, col0 + N) of an [N_total, K] layer and writes its [M, N] block of y straight into
+ * `n_dest` arrays -- its own and its peers' mappings of the full output, row pitch `ldy` elements -- from the
+ * GEMM epilogue (plain 128-bit stores over NVLink for the peers), so that no all-gather and no re-tile pass
+ * follow.  The caller orders the GPUs before the output is read (a barrier across the ranks on the stream).
+ * Needs M > 64 and the int8 expansion (the tcgen05 path); N, ldy and col0 multiples of 4; y_dest_host holds
+ * device pointers that are valid on this GPU (peer access enabled or a symmetric-memory mapping).  Shapes the
+ * tensor-core path does not serve return TBL_ERR_UNSUPPORTED: write into a local slot and all-gather instead.
+ * The reference has no multi-GPU inference (OXN/nsos/src/fabric_v2.cpp stages gradients through the host);
+ * this is the B200 counterpart of one model spread over the NVLink domain. */
+#define TBL_MAX_PEERS 8
+int tbl_linear_forward_scatter(const float* x_dev, const int8_t* w_i8_dev, float weight_scale, int M, int K, int N,
+                               int bits, int rms_mode, const float* magnitude_dev, const float* bias_dev,
+                               float* const* y_dest_host, int n_dest, long long ldy, long long col0,
+                               void* workspace_dev, size_t workspace_bytes, void* stream);
+
 /* Largest scratch tbl_linear_forward_noalloc can serve: tbl_linear_workspace_bytes(M,K,N) must not
  * exceed this (e.g. M*K <= 1 MiB of int8 codes: 64 rows of K = 16384, or 1365 rows of K = 768). */
 #define TBL_NOALLOC_SCRATCH_BYTES (2u * 1024u * 1024u + 64u * 1024u)

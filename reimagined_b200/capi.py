@@ -137,6 +137,8 @@ _SIGNATURES = {
     "tbl_edge_pack_write": (C.c_int, [C.POINTER(EdgeLayerSrc), C.c_int, _vp, C.c_size_t, C.POINTER(C.c_size_t)]),
     "tbl_sha256_hex": (None, [_vp, C.c_size_t, C.c_char_p]),
     "tbl_selftest_bounded_wait": (C.c_int, [_vp, _vp]),
+    "tbl_linear_forward_scatter": (C.c_int, [_vp, _vp, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp,
+                                             C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_longlong, _vp, C.c_size_t, _vp]),
     "tbl_device_status": (C.c_int, [_vp]),
     "tbl_set_kernel_events": (None, [_vp, _vp]),
     "tbl_set_chain_trace": (None, [_vp, C.c_size_t]),

@@ -282,6 +282,36 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
                     strip ? strips_dev : nullptr, weight_scale, magnitude_dev, bias_dev, M, K, N, y_dev, nullptr, st);
 }
 
+int tbl_linear_forward_scatter(const float* x_dev, const int8_t* w_i8_dev, float weight_scale, int M, int K, int N,
+                               int bits, int rms_mode, const float* magnitude_dev, const float* bias_dev,
+                               float* const* y_dest_host, int n_dest, long long ldy, long long col0,
+                               void* workspace_dev, size_t workspace_bytes, void* stream) {
+    if (!x_dev || !w_i8_dev || !y_dest_host) return TBL_ERR_INVALID_ARG;
+    const int rc = check_problem(M, K, N, weight_scale, bits);
+    if (rc != TBL_OK) return rc;
+    if (rms_mode < TBL_RMS_NONE || rms_mode > TBL_RMS_REFERENCE_ORDER) return TBL_ERR_INVALID_ARG;
+    if (n_dest < 1 || n_dest > TBL_MAX_PEERS || ldy < col0 + N || col0 < 0) return TBL_ERR_INVALID_ARG;
+    if (M <= 64) return TBL_ERR_UNSUPPORTED;
+    if ((N & 3) || (ldy & 3) || (col0 & 3)) return TBL_ERR_ALIGNMENT;
+    if (!aligned16(x_dev) || !aligned16(w_i8_dev)) return TBL_ERR_ALIGNMENT;
+    GemmScatter sc{};
+    sc.count = n_dest; sc.ld = ldy; sc.col0 = col0;
+    for (int d = 0; d < n_dest; ++d) {
+        if (!y_dest_host[d]) return TBL_ERR_INVALID_ARG;
+        if (!aligned16(y_dest_host[d])) return TBL_ERR_ALIGNMENT;
+        sc.dest[d] = y_dest_host[d];
+    }
+    if (!workspace_dev || workspace_bytes < tbl_linear_workspace_bytes(M, K, N)) return TBL_ERR_WORKSPACE;
+    if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const Workspace w = carve(workspace_dev, M, K);
+    cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, w.q, nullptr, w.act_scales,
+                                         w.q_sums, w.inv_norm, nullptr, QuantSegments{}, st);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    return cuda_status(launch_gemm_tcgen05(w.q, w.act_scales, w_i8_dev, weight_scale, magnitude_dev, bias_dev, M, K, N,
+                                           nullptr, nullptr, st, &sc));
+}
+
 }  // extern "C"
 
 namespace tbl {

@@ -62,6 +62,7 @@ struct GemmParams {
     int tiles_m, tiles_n;
     int use_tma_store;
     int* status;
+    GemmScatter scatter;      // count > 0: tiles go to these arrays (plain 128-bit stores, peers included), not to y
 };
 
 // Grouped mode (mixture-of-experts stages): problem g multiplies rows [offset[g], offset[g] + rows[g]) of the
@@ -315,6 +316,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                                         ((lane & 3) << 2));
                         if (col < p.N) p.y[static_cast<size_t>(row0 + quarter * 32 + rr) * p.N + col] = x;
                     }
+                } else if (p.scatter.count > 0) {
+                    // stage the block (row = lane, swizzled), then every destination gets it as 128-byte row
+                    // segments: 4 rows x 8 chunks of 16 bytes per store instruction
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 f = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = f;
+                    }
+                    __syncwarp();
+                    const int valid = min(32, rows - quarter * 32);
+                    const int chunk = lane & 7, rsub = lane >> 3;
+                    const int col = n0 + 4 * chunk;
+#pragma unroll 1
+                    for (int d = 0; d < p.scatter.count; ++d) {
+                        float* base = p.scatter.dest[d] + p.scatter.col0 + col;
+#pragma unroll
+                        for (int i8 = 0; i8 < 8; ++i8) {
+                            const int rr = 4 * i8 + rsub;
+                            if (rr < valid && col < p.N) {      // N % 4 == 0 is checked on the host
+                                const float4 f = *reinterpret_cast<const float4*>(stage + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                                *reinterpret_cast<float4*>(base + static_cast<size_t>(row0 + quarter * 32 + rr) * p.scatter.ld) = f;
+                            }
+                        }
+                    }
                 } else if (p.use_tma_store) {
                     // the previous block's store must have finished reading the staging buffer
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -443,8 +469,13 @@ cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales
 
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8, float weight_scale,
                                 const float* magnitude, const float* bias, int M, int K, int N, float* y,
-                                int32_t* acc_debug, cudaStream_t stream) {
+                                int32_t* acc_debug, cudaStream_t stream, const GemmScatter* scatter) {
     GemmParams p{};
+    if (scatter) {
+        if (scatter->count < 1 || scatter->count > TBL_MAX_PEERS || (N & 3) || (scatter->ld & 3) || (scatter->col0 & 3))
+            return cudaErrorInvalidValue;
+        p.scatter = *scatter;
+    }
     p.act_scales = act_scales; p.magnitude = magnitude; p.bias = bias; p.y = y; p.acc_debug = acc_debug;
     p.weight_scale = weight_scale; p.M = M; p.K = K; p.N = N;
     p.status = device_status_ptr();
@@ -466,7 +497,7 @@ cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const 
     p.tiles_m = tall ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     // TMA stores need a 16-byte row pitch and base
-    p.use_tma_store = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    p.use_tma_store = !scatter && (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
     CUtensorMap ma, mb, my;
     if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, M, K, BK, BM)) return cudaErrorUnknown;
     if (!make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_i8, N, K, BK, bn)) return cudaErrorUnknown;

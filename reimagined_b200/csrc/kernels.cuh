@@ -126,9 +126,18 @@ int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int 
                         void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
+// `scatter` (optional): instead of y, the epilogue writes every output tile into `count` arrays -- this GPU's and
+// its peers' mappings of one [M, ld] output -- at column col0 + n: the column-split exchange done by the GEMM's own
+// stores over NVLink.
+struct GemmScatter {
+    float* dest[TBL_MAX_PEERS];
+    int count;
+    long long ld, col0;
+};
 cudaError_t launch_gemm_tcgen05(const int8_t* q, const float* act_scales, const int8_t* w_i8,
                                 float weight_scale, const float* magnitude, const float* bias,
-                                int M, int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream);
+                                int M, int K, int N, float* y, int32_t* acc_debug, cudaStream_t stream,
+                                const GemmScatter* scatter = nullptr);
 cudaError_t launch_gemm_tcgen05_grouped(const int8_t* q, const float* act_scales, const int8_t* const* w_i8,
                                         const float* weight_scales, const float* const* magnitudes,
                                         const float* const* biases, const int* rows_dev, const int* offset_dev,

@@ -5,7 +5,9 @@ Rows of the activation matrix (tokens / sequences) are independent, so the defau
 The one shape that is also split by output columns is the largest one (K = N = 16384): rank r owns
 the weight rows [r*N/g, (r+1)*N/g) -- in the canonical packing a contiguous run of words, i.e. a
 self-contained packed matrix that keeps the GLOBAL weight_scale -- computes y[:, its columns] for all
-rows, and one all-gather assembles y.  The reference has no multi-GPU inference at all
+rows, and one all-gather assembles y -- or, for prefill-sized batches, no collective at all: the GEMM's epilogue
+stores every tile into all GPUs' copies of y over NVLink (PeerOutput + forward_fused below), so the exchange
+runs under the tensor-core work.  The reference has no multi-GPU inference at all
 (OXN/nsos/src/fabric_v2.cpp is an optional host-staged MPI layer for gradients); this module is the
 B200 counterpart of "one GPU lane per model" (OXN/nsos/include/jamba.h:739-747) at g lanes.
 """
@@ -90,6 +92,27 @@ def gather_columns(y_local, world: int, group=None, rank=None):
     return retile(gather_columns_inplace(stacked, rank, group))
 
 
+class PeerOutput:
+    """An fp32 [rows, n_total] output that exists on every GPU of the group at once and is mapped into every
+    process (torch symmetric memory): `pointers[r]` is rank r's copy as seen from this GPU.  Writers use plain
+    stores; `barrier()` orders all ranks on the current stream (call it after the writing kernels and before the
+    output is read, and again before the buffer is overwritten by a next step)."""
+
+    def __init__(self, rows: int, n_total: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.tensor = symm.empty((rows, n_total), dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+        self.rows, self.n_total = rows, n_total
+
+    def barrier(self):
+        self.handle.barrier()
+
+
 class ColumnParallelBitLinear:
     """Column-split ternary linear: each rank runs a BitLinear over its slice of the output columns with
     the global weight_scale, then the outputs are all-gathered."""
@@ -121,3 +144,32 @@ class ColumnParallelBitLinear:
         self.shard.forward(x, out=stacked[self.rank])
         gather_columns_inplace(stacked, self.rank, group)
         return retile(stacked, out)
+
+    def forward_fused(self, x, peer_out: PeerOutput):
+        """x [M, K] (replicated), M > 64 -> y [M, N] in `peer_out.tensor` on every rank: the shard's tcgen05 GEMM
+        stores each of its output tiles into all ranks' copies of y (its own last, the peers starting from the
+        next rank so that the ranks do not all target the same GPU at once); one barrier across the ranks, no
+        all-gather, no re-tile."""
+        import ctypes
+        import torch
+        from . import capi
+        sh = self.shard
+        if sh._dev is None or sh._dev["w_i8"] is None:
+            raise RuntimeError("forward_fused needs the int8 expansion: to('cuda', with_int8=True)")
+        k, n = sh.in_features, sh.out_features
+        m = x.numel() // k
+        if (m, n * self.world) != (peer_out.rows, peer_out.n_total):
+            raise ValueError("peer output has the wrong shape")
+        order = [(self.rank + 1 + i) % self.world for i in range(self.world)]
+        dests = (ctypes.c_void_p * self.world)(*[peer_out.pointers[r] for r in order])
+        ws = sh._workspace(m)
+        d = sh._dev
+        exact = sh.exact_linear_mode
+        rc = capi.lib().tbl_linear_forward_scatter(
+            x.data_ptr(), d["w_i8"].data_ptr(), sh.weight_scale, m, k, n, sh.precision_bits, 0 if exact else sh.rms_mode,
+            None if exact else d["magnitude"].data_ptr(), d["bias"].data_ptr() if sh.use_bias else None,
+            dests, self.world, n * self.world, n * self.rank, ws.data_ptr(), ws.numel(),
+            torch.cuda.current_stream().cuda_stream)
+        capi.check(rc, "tbl_linear_forward_scatter")
+        peer_out.barrier()
+        return peer_out.tensor
