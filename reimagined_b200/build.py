@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libternary_b200.so")
 SOURCES = ["api.cu", "quantize.cu", "gemv_stream.cu", "gemv_generic.cu", "gemv_strip.cu", "gemv_chain.cu",
-           "gemm_tcgen05.cu", "moe.cu", "glue.cu", "decode.cu", "packer.cpp", "edge_pack.cpp"]
+           "gemm_tcgen05.cu", "gemm_widen.cu", "moe.cu", "glue.cu", "decode.cu", "packer.cpp", "edge_pack.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 # IEEE division/sqrt and no fast-math: the fp32 epilogue and the quantiser scale are part of the
 # bit-exact contract.  -lineinfo keeps profiler source correlation.

@@ -125,6 +125,14 @@ cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, con
 int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
                         void* workspace, size_t workspace_bytes, cudaStream_t st);
 
+// gemm_widen.cu -- 1 <= M <= 64 rows per launch on the strip-major 2-bit weights: widened to bytes inside the kernel,
+// tcgen05 int8 MMAs with the weights as the A operand.  q: row-major codes; qw_scratch: gemm_widen_scratch_bytes.
+bool gemm_widen_supported(int M, int K, int N);
+size_t gemm_widen_scratch_bytes(int M, int K);
+cudaError_t launch_gemm_widen(const int8_t* q, int8_t* qw_scratch, const float* act_scales, const int32_t* q_sums,
+                              const void* strips, float weight_scale, const float* magnitude, const float* bias,
+                              int M, int K, int N, float* y, cudaStream_t stream);
+
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
 // `scatter` (optional): instead of y, the epilogue writes every output tile into `count` arrays -- this GPU's and
 // its peers' mappings of one [M, ld] output -- at column col0 + n: the column-split exchange done by the GEMM's own

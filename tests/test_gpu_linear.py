@@ -203,6 +203,27 @@ def test_strip_relayout_is_a_permutation(cuda, port, tbl):
                             assert (got_chunk == 0x55555555).all()
 
 
+@pytest.mark.parametrize("M,N,K,rms", [(33, 136, 1536, 0), (48, 1000, 2560, 1), (64, 776, 1536, 2), (100, 300, 1024, 0),
+                                       (128, 1024, 4096, 1), (40, 129, 512, 0)])
+def test_mid_batch_widening_tensor_core_path(cuda, port, tbl, M, N, K, rms):
+    """33 <= M <= 128 on the strip-major 2-bit weights with K % 512 == 0: widened in shared memory and multiplied by
+    tcgen05 MMAs, 64 rows per pass; ragged row tiles, a short last slab (K % 1024 != 0), every RMS mode."""
+    import gpu_helpers as H
+    w, x, mag, bias = make_case(7 * M + N + K, N, K, M, affine=True, xscale=3.0)
+    words, scale, *_ = port.pack_weights(w)
+    oy, *_ = port.linear_forward(x, words, scale, N, rms_input=1 if rms else 0, magnitude=mag, bias=bias)
+    dwords = H.words_dev(words)
+    y = H.linear_forward(H.dev(x), dwords, scale, N, rms_mode=rms, magnitude=H.dev(mag), bias=H.dev(bias),
+                         strips=H.relayout_strips(dwords, N, K)).cpu().numpy()
+    if rms == 1:
+        # parallel sum of squares: a code may move by one step at a rounding boundary -> bounded, tiny drift
+        assert np.abs(y - oy).max() <= 2e-2 * np.abs(oy).max()
+        assert np.median(np.abs(y - oy)) <= 1e-5 * np.abs(oy).max()
+    else:
+        assert bits_equal(y, oy)
+    assert H.device_status() == 0
+
+
 @pytest.mark.parametrize("M", [65, 100, 200])
 def test_packed_path_for_large_m_without_int8_copy(cuda, port, tbl, M):
     """w_i8 == NULL: every M runs on the packed words (activation tiles of 64 per pass)."""
