@@ -40,7 +40,7 @@ struct Workspace {
     size_t bytes;
 };
 
-constexpr int kWidenMinRows = 32;     // more rows than this (and <= 128, K % 512 == 0): the widening tensor-core kernel
+constexpr int kWidenMinRows = 32;     // more rows than this (and <= 256, K % 512 == 0): the widening tensor-core kernel
 
 Workspace carve(void* base, int M, int K) {
     Workspace w;
@@ -272,14 +272,14 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
     if (!workspace_dev || workspace_bytes < tbl_linear_workspace_bytes(M, K, N)) return TBL_ERR_WORKSPACE;
     if (!aligned16(workspace_dev)) return TBL_ERR_ALIGNMENT;
     const Workspace w = carve(workspace_dev, M, K);
-    // mid-size batches on the strip-major 2-bit weights: widened in shared memory, multiplied on the tcgen05 tensor cores, 64 rows
-    // per pass (the plane-major copy of the codes takes the place of the interleaved one in the workspace)
-    if (strip && M > kWidenMinRows && M <= 2 * 64 && (K & 511) == 0) {
+    // mid-size batches on the strip-major 2-bit weights: widened in shared memory, multiplied on the tcgen05 tensor cores, up to
+    // 128 rows per pass (the plane-major copy of the codes takes the place of the interleaved one in the workspace)
+    if (strip && M > kWidenMinRows && M <= 2 * 128 && (K & 511) == 0) {
         cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, w.q, nullptr, w.act_scales,
                                              w.q_sums, w.inv_norm, nullptr, QuantSegments{}, st);
         if (e != cudaSuccess) return TBL_ERR_CUDA;
-        for (int m0 = 0; m0 < M; m0 += 64) {
-            const int rows = M - m0 < 64 ? M - m0 : 64;
+        for (int m0 = 0; m0 < M; m0 += 128) {
+            const int rows = M - m0 < 128 ? M - m0 : 128;
             e = launch_gemm_widen(w.q + static_cast<size_t>(m0) * K, w.qp + static_cast<size_t>(m0) * K, w.act_scales + m0,
                                   w.q_sums + m0, strips_dev, weight_scale, magnitude_dev, bias_dev, rows, K, N,
                                   y_dev + static_cast<size_t>(m0) * N, st);

@@ -1,4 +1,4 @@
-// Mid-size batches (17 <= M <= 64 rows per pass) on the 2-bit weights: the words are widened to bytes INSIDE the
+// Mid-size batches (up to 128 rows per pass) on the 2-bit weights: the words are widened to bytes INSIDE the
 // kernel and multiplied on the 5th-generation tensor cores, so the weights cross HBM once at two bits each and
 // the multiply-accumulate work leaves the SM's issue slots.  The weights are read in the strip-major layout of
 // the decode GEMV (gemv_strip.cu): a tile's share of a 1024-deep slab is one contiguous run of memory, fetched
@@ -22,7 +22,7 @@
 //   warp 1     MMA issuer (one lane): per half k-block (two planes) 8 x tcgen05.mma kind::i8 (u8 x s8 -> s32,
 //              M = 128, N = n_pad, K = 32); owns the TMEM allocation
 //   warp 2     activation producer: per half k-block two TMA boxes [n_pad rows x 128 B] (L2-resident) into a ring
-//              of 3 (n_pad = 64) to 12 slots
+//              of 2 (n_pad = 128) to 16 slots
 //   warps 3-10 widen: warp w owns strip w of the tile; per k-block it reads the strip's two 1 KB blocks as four
 //              512-byte half-blocks (lane = 4g + t holds the 16-byte chunk t of row g or g + 8) and writes the
 //              planes of each chunk into a ring of three A buffers of two planes (conflict-free 128-bit shared
@@ -32,7 +32,7 @@
 // Every wait is bounded: on a timeout the role records the status word and falls through to the common exit,
 // where TMEM is released.
 //
-// Measured (16384 x 16384, B200): 41 us per pass whatever the batch (tensor pipe 42 % busy).  An MMA of this shape
+// Measured (16384 x 16384, B200): 41 us per pass for any batch up to 64 rows (tensor pipe 42 % busy).  An MMA of this shape
 // lasts 46 cycles for any N <= 64, so the 96 KB of widened planes that fit hold only ~1 100 cycles of tensor work,
 // less than the round trip commit -> widen warps wake -> stores -> arrive -> issue that recycles a buffer: the
 // kernel is bound by that loop, not by HBM (10 us), the widening (ALU 4 us) or the MMAs (12 us).  Neither the
@@ -52,13 +52,12 @@ constexpr int kWidenThreads = 32 * (3 + kWidenWarps);
 constexpr int kBlockK = 512;                 // weights of K per k-block
 constexpr int kRawBytes = 8 * 4096;          // one slab of a tile: 8 strips x 4 blocks of 1 KB
 constexpr int kPlaneBytes = 128 * 128;       // one widened plane of a k-block
-constexpr int kMaxNpad = 64;
+constexpr int kMaxNpad = 128;
 constexpr int kRawStages = 2;
 constexpr int kAStages = 3;                  // A buffers of two planes (half a k-block)
 constexpr int kAHalfBytes = 2 * kPlaneBytes;
-constexpr int kMaxBStages = 16;              // activation boxes of two planes: as many as fit kBRingBytes (3 at n_pad = 64)
-constexpr int kBRingBytes = 48 * 1024;
-constexpr uint32_t kTmemCols = 256;          // 4 planes x n_pad columns
+constexpr int kMaxBStages = 16;              // activation boxes of two planes: as many as fit kBRingBytes (2 at n_pad = 128)
+constexpr int kBRingBytes = 64 * 1024;
 constexpr int kNumSmW = 148;
 
 struct WidenParams {
@@ -126,6 +125,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = p.n_pad > 64 ? 512u : 256u;      // 4 planes x n_pad columns, a power of two
     if (threadIdx.x == 0) {
         for (int s = 0; s < kRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kWidenWarps); }
         for (int s = 0; s < kAStages; ++s) { mbar_init(&a_full[s], kWidenWarps); mbar_init(&a_empty[s], 1); }
@@ -136,7 +136,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
         fence_proxy_async();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -329,7 +329,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
