@@ -238,6 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are this warp's
         const int half = (warp - 2) >> 2;      // which of the two warps of the quarter: blocks half, half+2, ...
         uint8_t* stage = epi_stage + (warp - 2) * 4096;
+        const uint64_t store_policy = l2_evict_first_policy();
         int local = 0;
         bool alive = true;
         int g, tile_row0, tile_rows, tn;
@@ -354,7 +355,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&map_y, n0, row0 + quarter * 32, stage);
+                        tma_store_2d_hint(&map_y, n0, row0 + quarter * 32, stage, store_policy);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 } else if (row_ok) {

@@ -23,6 +23,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
                  : "memory");
 }
 
+// The same store with an L2 cache policy (createpolicy): outputs that nobody re-reads soon are written evict-first
+// so that they do not push the operands of the tiles in flight out of L2.
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, int c0, int c1, const void* src, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_u32(src)), "l"(policy)
+                 : "memory");
+}
+
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     // K-major, 128-byte swizzle: 8-row groups are 1024 B apart (SBO = 64 x 16 B); LBO unused (1);
     // descriptor version 1; layout type 2 = SWIZZLE_128B
