@@ -355,6 +355,65 @@ int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int 
 
 }  // namespace tbl
 
+namespace tbl {
+
+namespace {
+bool prologue_ok(const StripPrologue& pre) {
+    const void* ptrs[] = {pre.a, pre.ga, pre.b, pre.gb, pre.norm_w, pre.hidden_out, pre.trace_out};
+    for (const void* q : ptrs)
+        if (q && (reinterpret_cast<uintptr_t>(q) & 15)) return false;
+    return (pre.b == nullptr) == (pre.gb == nullptr) && (pre.a != nullptr || (pre.ga == nullptr && pre.b == nullptr));
+}
+}  // namespace
+
+int grouped_forward_rows_pre(const tbl_linear_view* views, int groups, const float* x, int rows, float* out,
+                             long long out_stride, const StripPrologue& pre, cudaStream_t st) {
+    if (!views || !x || !out || groups <= 0 || groups > TBL_MAX_GROUPS || rows <= 0) return TBL_ERR_INVALID_ARG;
+    const int K = views[0].inputs;
+    if (!gemv_strip_supported(K) || rows > gemv_strip_fused_rows(K) || !prologue_ok(pre) ||
+        (reinterpret_cast<uintptr_t>(x) & 15))
+        return TBL_ERR_UNSUPPORTED;
+    StripProblem pr[TBL_MAX_GROUPS];
+    for (int g = 0; g < groups; ++g) {
+        const tbl_linear_view& v = views[g];
+        if (!v.strips || (reinterpret_cast<uintptr_t>(v.strips) & 15) || v.inputs != K || v.weight != nullptr ||
+            v.activation_bits != views[0].activation_bits || (v.rms_input != 0) != (views[0].rms_input != 0))
+            return TBL_ERR_UNSUPPORTED;
+        if (static_cast<long long>(v.outputs) * rows > out_stride) return TBL_ERR_SHAPE;
+        pr[g] = StripProblem{};
+        pr[g].strips = static_cast<const uint8_t*>(v.strips);
+        pr[g].magnitude = v.magnitude; pr[g].bias = v.bias;
+        pr[g].y = out + static_cast<size_t>(g) * out_stride;
+        pr[g].weight_scale = v.weight_scale; pr[g].rows = rows;
+        pr[g].N = v.outputs; pr[g].K = K; pr[g].ldy = v.outputs;
+        pr[g].x = x; pr[g].q_max = 127.0f;
+        if (v.activation_bits != 8) return TBL_ERR_UNSUPPORTED;
+        pr[g].rms_fast = v.rms_input != 0;
+        pr[g].pre = pre;
+    }
+    const cudaError_t e = launch_gemv_strip(pr, groups, st);
+    return e == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+int linear_view_forward_pre(const tbl_linear_view& v, const float* x, int rows, bool squared_relu, const StripPrologue& pre,
+                            float* y, cudaStream_t st) {
+    if (!x || !y || rows <= 0) return TBL_ERR_INVALID_ARG;
+    if (!v.strips || (reinterpret_cast<uintptr_t>(v.strips) & 15) || v.weight != nullptr || v.activation_bits != 8 ||
+        !gemv_strip_supported(v.inputs) || rows > gemv_strip_fused_rows(v.inputs) || !prologue_ok(pre) ||
+        (reinterpret_cast<uintptr_t>(x) & 15))
+        return TBL_ERR_UNSUPPORTED;
+    StripProblem pr{};
+    pr.strips = static_cast<const uint8_t*>(v.strips); pr.x = x; pr.q_max = 127.0f;
+    pr.rms_fast = v.rms_input != 0; pr.magnitude = v.magnitude; pr.bias = v.bias; pr.y = y;
+    pr.weight_scale = v.weight_scale; pr.rows = rows; pr.N = v.outputs; pr.K = v.inputs; pr.ldy = v.outputs;
+    pr.squared_relu = squared_relu ? 1 : 0;
+    pr.pre = pre;
+    const cudaError_t e = launch_gemv_strip(&pr, 1, st);
+    return e == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
+}
+
+}  // namespace tbl
+
 // ---- grouped variant ---------------------------------------------------------------------------
 
 namespace {

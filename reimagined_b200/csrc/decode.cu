@@ -743,9 +743,18 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
     };
 
     // The residual add that ends a block is carried as "pending" and applied by the kernel that opens the next
-    // stage: h = x_pending + (a*ga + b*gb).
+    // stage: h = x_pending + (a*ga + b*gb).  For few rows (B * D <= 16384) that kernel is the GEMV itself: the
+    // add, the store of the residual stream and the RMSNorm x weight run in its prologue (StripPrologue), so a block
+    // costs no launch for them; the first block (embedding rows) and larger batches use residual_norm_kernel.
     struct Pending { const float* x; const int32_t* ids; const float* a; const float* ga; const float* b; const float* gb; };
     Pending pend{nullptr, token_ids_dev, nullptr, nullptr, nullptr, nullptr};
+    auto pre_of = [](const Pending& pd, const float* norm_w, float eps, float* hidden_out, float* trace) {
+        StripPrologue pre{};
+        pre.a = pd.a; pre.ga = pd.ga; pre.b = pd.b; pre.gb = pd.gb;
+        pre.norm_w = norm_w; pre.norm_eps = eps; pre.hidden_out = hidden_out; pre.trace_out = trace;
+        return pre;
+    };
+    const bool fold = B <= gemv_strip_fused_rows(D);
     int cur = 0;
     for (int i = 0; i < m.n_blocks; ++i) {
         const tbl_decode_block& b = m.blocks[i];
@@ -753,15 +762,23 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         if (mm.d_inner > 16 * 1024) return TBL_ERR_SHAPE;
         float* h = S.hidden[cur];
         float* trace = hidden_trace_dev ? hidden_trace_dev + static_cast<size_t>(i) * BD : nullptr;
-        // hidden state entering this block (+ trace of the previous block's output), core norm and, in hybrid
-        // blocks, the attention branch's own norm of the same row
-        if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, b.core_norm_eps, b.core_norm_w,
-                                b.hybrid ? b.attn_norm_w : nullptr, h, trace, S.core, b.hybrid ? S.attn_in : nullptr)) != TBL_OK)
-            return rc;
-        // Mamba-2 branch: five projections of the normalised row, then conv step + SSD step + gated norm in one
-        // kernel, then the out projection
         const tbl_linear_view proj[5] = {mm.x, mm.z, mm.B, mm.C, mm.dt};
-        if ((rc = group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK) return rc;
+        // hidden state entering this block (+ trace of the previous block's output), core norm, then the five
+        // projections of the normalised row
+        bool folded = false;
+        if (fold && !pend.ids) {
+            rc = grouped_forward_rows_pre(proj, 5, pend.x, B, S.proj, static_cast<long long>(S.proj_stride),
+                                          pre_of(pend, b.core_norm_w, b.core_norm_eps, h, trace), st);
+            if (rc == TBL_OK) folded = true;
+            else if (rc != TBL_ERR_UNSUPPORTED) return rc;
+        }
+        if (!folded) {
+            if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, b.core_norm_eps, b.core_norm_w,
+                                    b.hybrid ? b.attn_norm_w : nullptr, h, trace, S.core, b.hybrid ? S.attn_in : nullptr)) != TBL_OK)
+                return rc;
+            if ((rc = group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK) return rc;
+        }
+        // conv step + SSD step + gated norm in one kernel, then the out projection
         const int GS = mm.n_groups * mm.d_state, conv_dim = mm.d_inner + 2 * GS;
         const size_t mix_smem = sizeof(float) * (conv_dim + mm.d_inner + 2 * mm.n_heads + 32);
         if (mix_smem > 48 * 1024) {
@@ -788,7 +805,20 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         // attention branch on its own norm of the same residual stream
         const tbl_attention_block& a = b.attn;
         const tbl_linear_view qkv[2] = {a.q, a.kv};
-        if ((rc = group(qkv, 2, S.attn_in, S.qkv, S.qkv_stride)) != TBL_OK) return rc;
+        bool qkv_folded = false;
+        if (folded) {
+            rc = grouped_forward_rows_pre(qkv, 2, h, B, S.qkv, static_cast<long long>(S.qkv_stride),
+                                          pre_of(Pending{}, b.attn_norm_w, b.core_norm_eps, nullptr, nullptr), st);
+            if (rc == TBL_OK) qkv_folded = true;
+            else if (rc != TBL_ERR_UNSUPPORTED) return rc;
+            if (!qkv_folded) {
+                // the attention norm alone (x = h, nothing pending), then the projections
+                if ((rc = residual_norm(h, nullptr, nullptr, nullptr, nullptr, nullptr, b.core_norm_eps, b.attn_norm_w, nullptr,
+                                        nullptr, nullptr, S.attn_in, nullptr)) != TBL_OK)
+                    return rc;
+            }
+        }
+        if (!qkv_folded && (rc = group(qkv, 2, S.attn_in, S.qkv, S.qkv_stride)) != TBL_OK) return rc;
         const size_t attn_smem = sizeof(float) * (3 * a.head_dim + kAttnThreads + capacity);
         if (attn_smem > 200 * 1024) return TBL_ERR_SHAPE;
         if (attn_smem > 48 * 1024) {
@@ -809,20 +839,40 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         // res = h + (mamba*gate + attn*gate), and its norm for the FFN: up -> squared ReLU -> down (two launches with
         // the squared ReLU in the first one's epilogue: at this width a launch boundary is cheaper than the persistent
         // stack's grid-wide layer boundary)
-        if ((rc = residual_norm(h, nullptr, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, 1e-5f, b.ff_norm_w, nullptr, S.res,
-                                nullptr, S.ffn_in, nullptr)) != TBL_OK)
-            return rc;
-        if ((rc = linear_view_forward(b.ffn_up, S.ffn_in, B, TBL_RMS_FAST, true, S.ffn_mid, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
+        bool up_folded = false;
+        if (fold) {
+            rc = linear_view_forward_pre(b.ffn_up, h, B, true,
+                                         pre_of(Pending{nullptr, nullptr, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate},
+                                                b.ff_norm_w, 1e-5f, S.res, nullptr),
+                                         S.ffn_mid, st);
+            if (rc == TBL_OK) up_folded = true;
+            else if (rc != TBL_ERR_UNSUPPORTED) return rc;
+        }
+        if (!up_folded) {
+            if ((rc = residual_norm(h, nullptr, S.mamba_out, b.mamba_gate, S.attn_out, b.attn_gate, 1e-5f, b.ff_norm_w, nullptr, S.res,
+                                    nullptr, S.ffn_in, nullptr)) != TBL_OK)
+                return rc;
+            if ((rc = linear_view_forward(b.ffn_up, S.ffn_in, B, TBL_RMS_FAST, true, S.ffn_mid, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
+        }
         if ((rc = linear_view_forward(b.ffn_down, S.ffn_mid, B, TBL_RMS_FAST, false, S.ffn_out, S.lin, S.lin_bytes, st)) != TBL_OK) return rc;
         pend = Pending{S.res, nullptr, S.ffn_out, b.ffn_gate, nullptr, nullptr};
         cur ^= 1;
     }
     // the last block's residual add, the final norm and the LM head
     float* last_trace = hidden_trace_dev ? hidden_trace_dev + static_cast<size_t>(m.n_blocks) * BD : nullptr;
-    if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, m.final_norm_eps, m.final_norm_w, nullptr,
-                            S.hidden[cur], last_trace, S.core, nullptr)) != TBL_OK)
-        return rc;
-    if ((rc = linear(m.head, S.core, logits_dev)) != TBL_OK) return rc;
+    bool head_folded = false;
+    if (fold && !pend.ids) {
+        rc = linear_view_forward_pre(m.head, pend.x, B, false, pre_of(pend, m.final_norm_w, m.final_norm_eps, S.hidden[cur], last_trace),
+                                     logits_dev, st);
+        if (rc == TBL_OK) head_folded = true;
+        else if (rc != TBL_ERR_UNSUPPORTED) return rc;
+    }
+    if (!head_folded) {
+        if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, m.final_norm_eps, m.final_norm_w, nullptr,
+                                S.hidden[cur], last_trace, S.core, nullptr)) != TBL_OK)
+            return rc;
+        if ((rc = linear(m.head, S.core, logits_dev)) != TBL_OK) return rc;
+    }
     advance_positions_kernel<<<(B + 127) / 128, 128, 0, st>>>(state.positions, B);
     return launched();
 }

@@ -131,10 +131,90 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                 for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
+        // optional residual add in front: x += a * ga [+ b * gb] (same operations, same order as the stand-alone
+        // residual kernel, so the residual stream is bit-identical); CTA 0 stores the sum
+        if (pr.pre.a) {
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                if (grow[i] >= 0) {
+                    const int e = (threadIdx.x + i * kT) * 16, k0 = e - grow[i] * K;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        float4 c = __ldg(reinterpret_cast<const float4*>(pr.pre.a + e + 4 * q4));
+                        if (pr.pre.ga) {
+                            const float4 g4 = __ldg(reinterpret_cast<const float4*>(pr.pre.ga + k0 + 4 * q4));
+                            c.x = __fmul_rn(c.x, g4.x); c.y = __fmul_rn(c.y, g4.y); c.z = __fmul_rn(c.z, g4.z); c.w = __fmul_rn(c.w, g4.w);
+                        }
+                        if (pr.pre.b) {
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(pr.pre.b + e + 4 * q4));
+                            const float4 g4 = __ldg(reinterpret_cast<const float4*>(pr.pre.gb + k0 + 4 * q4));
+                            c.x = __fadd_rn(c.x, __fmul_rn(b4.x, g4.x)); c.y = __fadd_rn(c.y, __fmul_rn(b4.y, g4.y));
+                            c.z = __fadd_rn(c.z, __fmul_rn(b4.z, g4.z)); c.w = __fadd_rn(c.w, __fmul_rn(b4.w, g4.w));
+                        }
+                        xv[i][q4].x = __fadd_rn(xv[i][q4].x, c.x); xv[i][q4].y = __fadd_rn(xv[i][q4].y, c.y);
+                        xv[i][q4].z = __fadd_rn(xv[i][q4].z, c.z); xv[i][q4].w = __fadd_rn(xv[i][q4].w, c.w);
+                    }
+                }
+            }
+        }
         // The loads above are in the memory pipeline: only now may the producer warp queue its (much
         // larger) weight copies behind them.  Issued the other way round, x waits for up to a ring of
         // weights (measured: 3.5K .. 10.5K cycles until the last x load returned, against ~2K).
         asm volatile("bar.arrive 11, %0;" ::"r"(kT + 32) : "memory");
+        if (blockIdx.x == 0 && (pr.pre.hidden_out || pr.pre.trace_out)) {
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                if (grow[i] >= 0) {
+                    const int e = (threadIdx.x + i * kT) * 16;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        if (pr.pre.hidden_out) *reinterpret_cast<float4*>(pr.pre.hidden_out + e + 4 * q4) = xv[i][q4];
+                        if (pr.pre.trace_out) *reinterpret_cast<float4*>(pr.pre.trace_out + e + 4 * q4) = xv[i][q4];
+                    }
+                }
+            }
+        }
+        if (pr.pre.norm_w) {
+            // RMSNorm x weight of the rows (the norm that opens a stage of the hybrid): the same reduction as the
+            // input RMSNorm below with the caller's eps, then (x * inv) * w
+            float ss[kMaxFusedRows];
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) ss[m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                float q = 0.0f;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    q += xv[i][q4].x * xv[i][q4].x + xv[i][q4].y * xv[i][q4].y + xv[i][q4].z * xv[i][q4].z + xv[i][q4].w * xv[i][q4].w;
+#pragma unroll
+                for (int m = 0; m < kMaxFusedRows; ++m) if (grow[i] == m) ss[m] += q;
+            }
+#pragma unroll
+            for (int m = 0; m < kMaxFusedRows; ++m) {
+                if (m < R) {
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+                    if (lane == 0) s_red[warp * kMaxFusedRows + m] = ss[m];
+                }
+            }
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                if (grow[i] >= 0) {
+                    float r = s_red[grow[i]];
+                    for (int w = 1; w < kConsumers; ++w) r += s_red[w * kMaxFusedRows + grow[i]];
+                    const float f = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(r, static_cast<float>(K)), pr.pre.norm_eps)));
+                    const int k0 = (threadIdx.x + i * kT) * 16 - grow[i] * K;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 w4 = __ldg(reinterpret_cast<const float4*>(pr.pre.norm_w + k0 + 4 * q4));
+                        xv[i][q4].x = __fmul_rn(__fmul_rn(xv[i][q4].x, f), w4.x); xv[i][q4].y = __fmul_rn(__fmul_rn(xv[i][q4].y, f), w4.y);
+                        xv[i][q4].z = __fmul_rn(__fmul_rn(xv[i][q4].z, f), w4.z); xv[i][q4].w = __fmul_rn(__fmul_rn(xv[i][q4].w, f), w4.w);
+                    }
+                }
+            }
+            asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory");      // s_red is reused by the input RMSNorm below
+        }
         if (pr.rms_fast) {
             // per-row sum of squares: thread partials, warp shuffles, then a
             // fixed-order sum over the warps

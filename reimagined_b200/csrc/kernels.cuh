@@ -73,6 +73,21 @@ cudaError_t launch_gemv_generic(const int8_t* q, const float* act_scales, const 
 
 // gemv_strip.cu -- 1 <= M <= 64 rows per pass, int8 mma.sync tensor cores, strip-major weights,
 // problem table for grouped launches.
+// Optional work in front of the fused quantiser of a strip GEMV (single problem, or several sharing the input rows):
+// the residual add that closes a block of the hybrid and the RMSNorm x weight that opens the next stage, so that
+// neither needs a launch of its own:  x <- x + a * ga [+ b * gb]  (ga null: x + a), stored to hidden_out / trace_out
+// by CTA 0, then  x <- (x * rsqrt(mean(x^2) + norm_eps)) * norm_w.  All arrays are [rows, K] or [K], 16-byte aligned.
+struct StripPrologue {
+    const float* a;
+    const float* ga;
+    const float* b;
+    const float* gb;
+    const float* norm_w;      // null: no norm
+    float norm_eps;
+    float* hidden_out;        // may be null
+    float* trace_out;         // may be null
+};
+
 struct StripProblem {
     const uint8_t* strips;    // strip-major packed weights (launch_relayout_strips)
     const int8_t* qp;         // interleaved int8 activations
@@ -94,6 +109,7 @@ struct StripProblem {
     const float* x;
     float q_max;
     int rms_fast;             // apply the (parallel-sum) input RMSNorm before quantising
+    StripPrologue pre;        // fused launches only (problem 0's is used); all null = none
 };
 // rows the strip kernel can quantise in its own prologue for this K (0 = none)
 int gemv_strip_fused_rows(int K);
@@ -120,6 +136,14 @@ size_t gemv_chain_workspace_bytes(const ChainLayer* layers, int count, int rows)
 void set_chain_trace(void* buffer, size_t bytes);
 cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, const float* x, float* y,
                               void* workspace, cudaStream_t stream);
+
+// api.cu -- the same two calls with a residual add / RMSNorm x weight in the GEMV's own prologue (StripPrologue).
+// They serve only shapes the fused-prologue strip kernel takes (strip copies present, rows <= gemv_strip_fused_rows(K),
+// 16-byte aligned arrays) and return TBL_ERR_UNSUPPORTED otherwise: the caller then runs the pieces separately.
+int grouped_forward_rows_pre(const tbl_linear_view* views, int groups, const float* x, int rows, float* out,
+                             long long out_stride, const StripPrologue& pre, cudaStream_t st);
+int linear_view_forward_pre(const tbl_linear_view& v, const float* x, int rows, bool squared_relu, const StripPrologue& pre,
+                            float* y, cudaStream_t st);
 
 // api.cu -- one view's forward with an optional squared ReLU (fused into the GEMV epilogue where possible)
 int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
