@@ -9,7 +9,10 @@ namespace {
 constexpr int kRouteThreads = 256;
 
 // One CTA walks the experts in index order and, inside an expert, the rows in row order, handing
-// out consecutive slots: slots of expert e are [offsets[e], offsets[e] + counts[e]).
+// out consecutive slots: slots of expert e are [offsets[e], offsets[e] + counts[e]).  The routing weights are
+// read once, up front (a bit per expert and row, kept in registers for up to kRouteChunks x 256 rows): the walk
+// itself then touches only shared memory, instead of one dependent global round trip per expert.
+constexpr int kRouteChunks = 8;
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const float* __restrict__ routing, int rows, int experts, int capacity, MoeLists L,
                  int* status) {
@@ -17,12 +20,32 @@ moe_route_kernel(const float* __restrict__ routing, int rows, int experts, int c
     __shared__ int base;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) base = 0;
+    const bool cached = rows <= kRouteChunks * kRouteThreads && experts <= 32;
+    uint32_t mask[kRouteChunks];
+#pragma unroll
+    for (int c = 0; c < kRouteChunks; ++c) {
+        mask[c] = 0u;
+        const int r = c * kRouteThreads + threadIdx.x;
+        if (cached && r < rows) {
+            for (int e = 0; e < experts; ++e)
+                mask[c] |= routing[static_cast<size_t>(r) * experts + e] != 0.0f ? 1u << e : 0u;
+        }
+    }
     __syncthreads();
     for (int e = 0; e < experts; ++e) {
         const int start = base;
-        for (int r0 = 0; r0 < rows; r0 += kRouteThreads) {
+#pragma unroll 1
+        for (int r0 = 0, c = 0; r0 < rows; r0 += kRouteThreads, ++c) {
             const int r = r0 + threadIdx.x;
-            const bool hit = r < rows && routing[static_cast<size_t>(r) * experts + e] != 0.0f;
+            bool hit;
+            if (cached) {
+                uint32_t mk = mask[0];
+#pragma unroll
+                for (int i = 1; i < kRouteChunks; ++i) if (c == i) mk = mask[i];
+                hit = (mk >> e & 1u) != 0u;
+            } else {
+                hit = r < rows && routing[static_cast<size_t>(r) * experts + e] != 0.0f;
+            }
             const unsigned ballot = __ballot_sync(0xffffffffu, hit);
             const int before = __popc(ballot & ((1u << lane) - 1));
             if (lane == 0) warp_totals[warp] = __popc(ballot);

@@ -62,3 +62,49 @@ def test_linear_forward_routes_large_m_to_gemm(cuda, port, tbl):
     y = H.linear_forward(H.dev(x), dw, scale, N, w_i8=H.expand_i8(dw, N, K), rms_mode=2)
     assert bits_equal(y.cpu().numpy(), oy)
     assert H.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,parts", [(130, 256, 512, 2), (200, 96, 256, 3), (520, 1024, 4096, 2)])
+def test_scatter_epilogue_writes_column_blocks_of_one_output(cuda, port, tbl, M, N, K, parts):
+    """tbl_linear_forward_scatter on one GPU: the layer is split by output columns into `parts` calls, each storing its
+    block into TWO copies of the full [M, N] output at its column offset (the peers' mappings in the multi-GPU use);
+    both copies must equal the unsharded oracle bit for bit, and nothing outside a call's columns may be touched."""
+    import ctypes
+    import torch
+    import gpu_helpers as H
+    from reimagined_b200 import capi
+    L = capi.lib()
+    rng = np.random.default_rng(M + N + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    mag = (1 + 0.2 * rng.standard_normal(N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    words, scale, *_ = port.pack_weights(w)
+    want, *_ = port.linear_forward(x, words, scale, N, magnitude=mag, bias=bias)
+    n_local = N // parts
+    outs = [torch.full((M, N), 7.5, dtype=torch.float32, device="cuda") for _ in range(2)]
+    dx, dmag, dbias = H.dev(x), H.dev(mag), H.dev(bias)
+    wpr = K // 16
+    for p in range(parts):
+        shard = np.ascontiguousarray(words.reshape(N, wpr)[p * n_local:(p + 1) * n_local]).reshape(-1)
+        dshard = H.words_dev(shard)
+        i8 = H.expand_i8(dshard, n_local, K)
+        nbytes = L.tbl_linear_workspace_bytes(M, K, n_local)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        dests = (ctypes.c_void_p * 2)(outs[0].data_ptr(), outs[1].data_ptr())
+        rc = L.tbl_linear_forward_scatter(dx.data_ptr(), i8.data_ptr(), float(scale), M, K, n_local, 8, 0,
+                                          dmag[p * n_local:].data_ptr(), dbias[p * n_local:].data_ptr(), dests, 2, N,
+                                          p * n_local, ws.data_ptr(), nbytes, H.stream_ptr())
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        got = outs[0].cpu().numpy()
+        assert np.all(got[:, (p + 1) * n_local:] == 7.5)          # later blocks untouched so far
+    for o in outs:
+        y = o.cpu().numpy()
+        assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+    # refused: rows the tensor-core path does not serve, misaligned column offset
+    assert L.tbl_linear_forward_scatter(dx.data_ptr(), i8.data_ptr(), float(scale), 64, K, n_local, 8, 0, None, None, dests, 2, N, 0,
+                                        ws.data_ptr(), nbytes, H.stream_ptr()) == -10
+    assert L.tbl_linear_forward_scatter(dx.data_ptr(), i8.data_ptr(), float(scale), M, K, n_local, 8, 0, None, None, dests, 2, N + 2, 2,
+                                        ws.data_ptr(), nbytes, H.stream_ptr()) == -6
+    assert H.device_status() == 0
