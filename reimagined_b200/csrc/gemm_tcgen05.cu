@@ -197,13 +197,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         alive = mbar_wait_bounded(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status);
                         if (!alive) break;
                     }
-                } else {
-                    if (local >= 1) {
-                        alive = mbar_wait_bounded(&tmem_empty[0], (local - 1) & 1, p.status) &&
-                                mbar_wait_bounded(&tmem_empty[1], (local - 1) & 1, p.status);
-                        if (!alive) break;
-                    }
                 }
+                // (MT == 2: each half is waited for just before the first MMA that writes it, below: the epilogue
+                // drains half 0 first, so this tile's first MMAs run while half 1 is still being stored)
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (MT == 1 ? buf * BN : 0);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -215,12 +211,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int h = 0; h < MT; ++h) {
+                        if constexpr (MT == 2) {
+                            if (kb == 0 && local >= 1) {
+                                alive = mbar_wait_bounded(&tmem_empty[h], (local - 1) & 1, p.status);
+                                if (!alive) break;
+                                tc_fence_after();
+                            }
+                        }
 #pragma unroll
                         for (int kk = 0; kk < BK / 32; ++kk) {
                             umma_i8(d_tmem + h * BN, smem_desc_sw128(a_addr + h * (BM * BK) + kk * 32),
                                     smem_desc_sw128(b_addr + kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
                         }
                     }
+                    if (!alive) break;
                     umma_commit(&empty[s]);   // stage reusable once these MMAs have read it
                 }
                 if (alive) {
