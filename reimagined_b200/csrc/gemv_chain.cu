@@ -18,7 +18,8 @@
 // that gives up sets TBL_DEV_WAIT_TIMEOUT and the CTA leaves.
 //
 // Weight layout, stage layout, widening and the MMA are those of gemv_strip.cu (strips of 16 rows, 1 KB
-// blocks, slab-major order, mma.sync.m16n8k32.u8.s8 with the weights as the A operand).
+// blocks, slab-major order, mma.sync.m16n8k32.u8.s8 with the weights as the A operand); single-row layers with
+// full 2048-deep stages take their dot products with dp4a on the same masked words instead (no tensor pipe).
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -250,9 +251,8 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
             const int e = (threadIdx.x + i * kT) * 16;
             const uint4 codes = transpose4x4_bytes(make_uint4(wds[0], wds[1], wds[2], wds[3]));
             if (SINGLE && paired) {
-                // single-row order of the full-stage path: word j of quarter x sits beside word j of quarter x ^ 1
-                // (128-bit slot 2 * (x >> 1) + (j >> 1), word 2 * (j & 1) + (x & 1)), so that the two B registers of
-                // an MMA come out of one 128-bit load as an aligned register pair and need no moves
+                // single-row order of the full-stage path: word j (plane j) of quarter x goes to 128-bit slot
+                // 2 * (x >> 1) + (j >> 1), word 2 * (j & 1) + (x & 1)
                 const int kb = e >> 8, r = e & 255, tq = r >> 6, xq = (r >> 4) & 3;
                 uint32_t* dst = reinterpret_cast<uint32_t*>(acts_resident + kb * 256 + (xq >> 1) * 128 + tq * 16) + (xq & 1);
                 dst[0] = codes.x;
@@ -415,7 +415,7 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                     const uint32_t stage_addr = stage_base_addr + st * stage_bytes;
                     if (fast) {
                         // single row, full 2048-deep stage: blocks part, part+2 of both slabs with constant
-                        // offsets; the loads of a block are issued ahead of the MMAs of the block before it
+                        // offsets; the loads of a block are issued ahead of the arithmetic of the block before it
                         const uint32_t w0 = stage_addr + lane * 16 + (slot * 4 + part) * 1024;
                         const uint32_t w1 = w0 + cnt * 4096;
                         const uint32_t a0 = acts_resident_addr + t * 16 + (ksi * 8 + part) * 256;
@@ -428,19 +428,28 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                             for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + x * 64);
                             return o;
                         };
+                        // One row: seven of an MMA's eight columns would be idle, and its 8 issues per block cost the
+                        // tensor pipe as much as 32 dp4a cost the FMA pipe (measured: 14.3 against 14.8 us per layer).
+                        // Each lane takes the dot products of its own 16-byte chunks (row g and row g + 8, 64 weights
+                        // each) with the matching 64 codes, plane by plane; the four lanes of a row meet once per layer
+                        // (shuffles below).  acc[p][0] / acc[p][2] are the plane-p sums of row g / g + 8, where the
+                        // MMA form of the multi-row path keeps column 0 of the same rows.  The codes of plane p of
+                        // quarter x sit in 128-bit slot 2 * (x >> 1) + (p >> 1), word 2 * (p & 1) + (x & 1) (the
+                        // paired order the quantiser writes for these layers; with the plain order -- word p of slot
+                        // x -- the same loop compiles to a schedule that is 3 % slower).
                         auto mma_block = [&](const Operands& o) {
                             const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
                             const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
 #pragma unroll
-                            for (int xp = 0; xp < 2; ++xp) {
-                                // paired order: the 128-bit slot 2 * xp + (j >> 1) holds {b0, b1} of positions j, j + 1
-                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].z, o.b[2 * xp + 1].x, o.b[2 * xp + 1].z};
-                                const uint32_t b1[4] = {o.b[2 * xp].y, o.b[2 * xp].w, o.b[2 * xp + 1].y, o.b[2 * xp + 1].w};
+                            for (int x = 0; x < 4; ++x) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const uint32_t mk = 0x03030303u << (2 * j);
-                                    mma_u8s8(acc[j], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
-                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                for (int pl = 0; pl < 4; ++pl) {
+                                    const uint4& q = o.b[(x >> 1) * 2 + (pl >> 1)];
+                                    const int idx = (pl & 1) * 2 + (x & 1);
+                                    const uint32_t a = idx == 0 ? q.x : (idx == 1 ? q.y : (idx == 2 ? q.z : q.w));
+                                    const uint32_t mk = 0x03030303u << (2 * pl);
+                                    acc[pl][0] = dp4a_su(static_cast<int>(a), lw[x] & mk, acc[pl][0]);
+                                    acc[pl][2] = dp4a_su(static_cast<int>(a), hw[x] & mk, acc[pl][2]);
                                 }
                             }
                         };
@@ -494,6 +503,19 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
             if (threadIdx.x == 0) stamp(l, 4);
 
             if (active) {
+                if (fast) {
+                    // the four lanes of a row (t = 0..3) hold the sums of their quarters of every k-block
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+                            int v = acc[j][e];
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                            acc[j][e] = v;
+                        }
+                    }
+                }
                 // exact recombination of the 4^j-scaled partial sums, then the two warps of a strip meet
                 int tot[4];
 #pragma unroll
