@@ -9,13 +9,16 @@
 // at a grid-wide barrier and quantise the new activation row, the first stages of layer l+1 are already
 // landing.  The weight stream of the whole stack is one uninterrupted front-to-back sweep of HBM.
 //
-// Layer boundary (consumer warps only).  The epilogue warp of each strip stores its 16 outputs per row,
-// publishes their maxima with atomicMax (max is exact in any order, so the next quantiser's scale is bit-identical
-// to a separate absmax pass), fences and counts its strip as arrived -- per warp, with no CTA-wide barrier, so
-// the round trips of the seven strips of a CTA overlap.  The quantiser of the next layer polls the counter
-// (bounded) until all strips have arrived, reads the row (L2-resident) and quantises it straight into shared
-// memory.  The grid must be co-resident: the kernel is launched cooperatively.  Every wait is bounded; a wait
-// that gives up sets TBL_DEV_WAIT_TIMEOUT and the CTA leaves.
+// Layer boundary (consumer warps only).  The epilogue warp of each strip stores its 16 outputs per row and counts
+// its strip as arrived -- per warp, with no CTA-wide barrier and NO fence, so neither the round trips of the seven
+// strips of a CTA nor a store's way to L2 are waited for.  The quantiser of the next layer polls the counter
+// (bounded) until all strips have arrived and reads the row (L2-resident).  Because nothing orders a strip's stores
+// before its arrival, a value may still be on its way then: every activation buffer starts the launch filled with
+// all-ones words -- a bit pattern the writers never store (they replace that one NaN by the canonical one) -- so a
+// load validates itself and is repeated (bounded) until no word is the filler.  The row maximum is then taken over
+// the loaded values (max is exact in any order) and the row is quantised straight into shared memory.  The grid
+// must be co-resident: the kernel is launched cooperatively.  Every wait is bounded; a wait that gives up sets
+// TBL_DEV_WAIT_TIMEOUT and the CTA leaves.
 //
 // Weight layout, stage layout, widening and the MMA are those of gemv_strip.cu (strips of 16 rows, 1 KB
 // blocks, slab-major order, mma.sync.m16n8k32.u8.s8 with the weights as the A operand); single-row layers with
@@ -42,9 +45,10 @@ struct ChainParams {
     int count, rows;
     const float* x;        // [rows, K_0]
     float* y;              // [rows, N_last]
-    float* act[2];         // ping-pong activations between layers, [rows, width]
-    unsigned* sync;        // [count][16]: word 0 = strips of the layer that have arrived, words 1..8 = bit patterns of
-                           // the row maxima of the layer's output; zero at launch
+    float* act_base;       // activations between layers: buffer l holds layer l's output, [rows, width], all-ones bits at launch
+    size_t act_stride;
+    unsigned* sync;        // [count][16]: word 0 = strips of the layer that have arrived, counted up from 0xffffffff
+                           // (the launch's memset fills counters and activation buffers with the same byte)
     int ks, stage_shift, stages, slots_max, acts_bytes;
     int* status;
     unsigned long long* trace;   // profiling aid: [cta][layer][8] nanosecond stamps, or null
@@ -70,12 +74,6 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     return v;
 }
 
-__device__ __forceinline__ uint2 ld_acquire_gpu_v2(const unsigned* p) {
-    uint2 v;
-    asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 10, %0;" ::"r"(kT) : "memory"); }
 
 // Shared-memory state of the consumer warps.  The per-row scale and code sum are double-buffered by layer parity:
@@ -84,15 +82,14 @@ struct ConsumerState {
     float scale[2][kMaxRows];
     int qsum[2][kMaxRows];
     float red[kConsumers * kMaxRows];
-    uint32_t amax[kMaxRows];      // local absmax reduction (first layer)
-    uint32_t pub[kMaxRows];       // row maxima published by the previous layer's epilogue warps
+    uint32_t amax[kMaxRows];      // absmax reduction over the CTA's threads
     int ok;
 };
 static_assert(sizeof(ConsumerState) <= kStateBytes, "consumer state must fit its slot");
 
 // Per-token absmax quantiser of rows*K <= 16384 inputs into the resident interleaved shared-memory copy; same
-// arithmetic as the stand-alone quantiser.  `sync` != null: x is the previous layer's output; it is complete when
-// that layer's arrival counter reaches `target`, and its row maxima are final then, so no absmax pass is needed.
+// arithmetic as the stand-alone quantiser.  `sync` != null: x is the previous layer's output; its strips have all
+// been issued when that layer's arrival counter reaches `target`, and each loaded word tells whether it has landed.
 // Returns false when a bounded wait gave up (status word set).
 template <bool SINGLE>
 __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, const int R, const int K,
@@ -108,18 +105,14 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
         cs->amax[threadIdx.x] = 0u;
     }
     if (sync) {
-        if (static_cast<int>(threadIdx.x) < R) {
+        if (threadIdx.x == 0) {
             bool ok = false;
-            unsigned value = 0u;
             for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
-                const uint2 v = ld_acquire_gpu_v2(sync);
-                if (v.x >= target) { ok = true; value = v.y; break; }
+                if (ld_acquire_gpu(sync) + 1u >= target) { ok = true; break; }      // the counter starts at 0xffffffff
             }
-            if (ok && threadIdx.x > 0) value = ld_acquire_gpu(sync + 1 + threadIdx.x);
             if (!ok) { atomicOr(status, TBL_DEV_WAIT_TIMEOUT); cs->ok = 0; }
-            cs->pub[threadIdx.x] = value;
         }
-        bar_consumers();     // every consumer warp has left the previous layer; maxima and zeroed sums visible
+        bar_consumers();     // every consumer warp has left the previous layer; zeroed sums and maxima visible
         if (*reinterpret_cast<volatile int*>(&cs->ok) == 0) return false;
     }
     if (trace && threadIdx.x == 0) trace[1] = global_ns();
@@ -142,6 +135,33 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
         } else {
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (sync) {
+        // the writers do not fence: a value may still be on its way when the counter is complete.  The buffers start as
+        // all-ones words (never a result: the writers replace that one NaN pattern), so a load validates itself.
+        for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+            uint32_t least = 1u;
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                if (grow[i] >= 0) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        least = min(least, ~__float_as_uint(xv[i][q4].x)); least = min(least, ~__float_as_uint(xv[i][q4].y));
+                        least = min(least, ~__float_as_uint(xv[i][q4].z)); least = min(least, ~__float_as_uint(xv[i][q4].w));
+                    }
+                }
+            }
+            if (least != 0u) break;
+            if (spin + 1 == kGridSpinLimit) { atomicOr(status, TBL_DEV_WAIT_TIMEOUT); cs->ok = 0; }
+#pragma unroll
+            for (int i = 0; i < kGroups; ++i) {
+                const int Gl = threadIdx.x + i * kT;
+                if (grow[i] >= 0) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) xv[i][q4] = __ldcg(reinterpret_cast<const float4*>(x + Gl * 16 + 4 * q4));
+                }
+            }
         }
     }
     // first layer only: the producer warp starts queueing weight copies once these loads are in flight
@@ -197,11 +217,7 @@ __device__ __forceinline__ bool quantise_resident(const float* __restrict__ x, c
         }
     }
     float amax[kRows];
-    if (sync) {
-        // max_k fl(|x_k| * inv) == fl(max_k |x_k| * inv): rounding is monotone
-#pragma unroll
-        for (int m = 0; m < kRows; ++m) amax[m] = m < R ? __fmul_rn(__uint_as_float(cs->pub[m]), inv[m]) : 0.0f;
-    } else {
+    {
         float mx[kRows];
 #pragma unroll
         for (int m = 0; m < kRows; ++m) mx[m] = 0.0f;
@@ -374,8 +390,8 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
         }
 
         // ---------------- consumer warps ----------------
-        const float* xin = l == 0 ? P.x : P.act[(l - 1) & 1];
-        float* yout = l == P.count - 1 ? P.y : P.act[l & 1];
+        const float* xin = l == 0 ? P.x : P.act_base + static_cast<size_t>(l - 1) * P.act_stride;
+        float* yout = l == P.count - 1 ? P.y : P.act_base + static_cast<size_t>(l) * P.act_stride;
         const bool has_work = s_begin < s_end;
         if (threadIdx.x == 0) stamp(l, 0);
         if (has_work) {
@@ -530,7 +546,6 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                 // the buffer is reused by the next pass: the reader must be done before the writer returns
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * kWps) : "memory");
                 if (part == 0) {
-                    float omax[2] = {0.0f, 0.0f};
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int n = (local + slot) * 16 + g + 8 * h;
@@ -541,28 +556,15 @@ gemv_chain_kernel(const __grid_constant__ ChainParams P) {
                                 const int total = tot[2 * h + c] - cs->qsum[par][m];
                                 float v = epilogue(total, __fmul_rn(cs->scale[par][m], L.weight_scale), L.magnitude, L.bias, n);
                                 if (L.squared_relu) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
+                                if (__float_as_uint(v) == 0xffffffffu) v = __uint_as_float(0x7fffffffu);
                                 yout[static_cast<size_t>(m) * N + n] = v;
-                                omax[c] = fmaxf(omax[c], fabsf(v));
                             }
                         }
                     }
                     if (l + 1 < P.count) {
-                        // layer boundary, per strip: publish this strip's row maxima, make the stores visible and
-                        // count the strip as arrived
-                        unsigned* sync = P.sync + l * 16;
-#pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            uint32_t u = __float_as_uint(omax[c]);
-                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 4));
-                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 8));
-                            u = max(u, __shfl_xor_sync(0xffffffffu, u, 16));
-                            if (g == 0 && 2 * t + c < R && u != 0u) atomicMax(sync + 1 + 2 * t + c, u);
-                        }
+                        // layer boundary, per strip: count the strip as arrived (no fence: the readers validate)
                         __syncwarp();
-                        if (lane == 0) {
-                            __threadfence();
-                            atomicAdd(sync, 1u);
-                        }
+                        if (lane == 0) atomicAdd(P.sync + l * 16, 1u);
                     }
                 }
             }
@@ -626,7 +628,7 @@ ChainScratch chain_scratch(const ChainLayer* layers, int count, int rows) {
     ChainScratch c{};
     c.sync_bytes = round_up(static_cast<size_t>(count) * 16 * sizeof(unsigned), 256);
     c.act_bytes = round_up(static_cast<size_t>(rows) * width * sizeof(float), 256);
-    c.total = c.sync_bytes + 2 * c.act_bytes;
+    c.total = c.sync_bytes + static_cast<size_t>(count) * c.act_bytes;
     return c;
 }
 }  // namespace
@@ -679,10 +681,10 @@ cudaError_t launch_gemv_chain(const ChainLayer* layers, int count, int rows, con
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     const ChainScratch sc = chain_scratch(layers, count, rows);
     P.sync = reinterpret_cast<unsigned*>(ws);
-    P.act[0] = reinterpret_cast<float*>(ws + sc.sync_bytes);
-    P.act[1] = reinterpret_cast<float*>(ws + sc.sync_bytes + sc.act_bytes);
-    // arrival counters and published maxima start at zero
-    cudaError_t e = cudaMemsetAsync(ws, 0, sc.sync_bytes, stream);
+    P.act_base = reinterpret_cast<float*>(ws + sc.sync_bytes);
+    P.act_stride = sc.act_bytes / sizeof(float);
+    // arrival counters and activation buffers start as all-ones words
+    cudaError_t e = cudaMemsetAsync(ws, 0xff, sc.sync_bytes + static_cast<size_t>(count > 1 ? count - 1 : 0) * sc.act_bytes, stream);
     if (e != cudaSuccess) return e;
 
     cudaLaunchConfig_t cfg{};
