@@ -145,3 +145,26 @@ def test_chain_rejects_bad_stacks(cuda, port, tbl):
     views[1].inputs = 512
     arr = (type(views[0]) * 2)(*views)
     assert tbl.tbl_chain_forward(arr, 2, None, H.ptr(x), 1, 0, H.ptr(y), H.ptr(ws), 16, H.stream_ptr()) == -7
+
+
+@pytest.mark.parametrize("bad", [np.inf, -np.inf, np.nan, 3.0e38])
+def test_non_finite_values_between_layers_do_not_stall_the_stack(cuda, port, tbl, bad):
+    """A layer's output travels to the next layer through buffers whose filler word marks "not written yet".  Values
+    that are not finite (an infinite or NaN input spreads through every layer) must neither be mistaken for the
+    filler nor keep a reader waiting: the call returns at once with a clean status word; rows that are finite are
+    still exact."""
+    import time
+    import gpu_helpers as H
+    rng = np.random.default_rng(17)
+    rows, widths = 2, [1024, 2048, 512, 1024]
+    views, keep, host = _stack(port, H, rng, widths)
+    x = rng.standard_normal((rows, widths[0])).astype(np.float32)
+    x[1, 5] = bad
+    import torch
+    t0 = time.perf_counter()
+    y = H.chain_forward(views, H.dev(x))
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert H.device_status() == 0
+    want = _oracle(port, host, x[:1], None)
+    assert bits_equal(y[:1].cpu().numpy(), want)
