@@ -537,18 +537,21 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
                             for (int x = 0; x < 4; ++x) o.b[x] = lds128(ablk + x * 64);
                             return o;
                         };
+                        // One row: each lane takes the dot products of its own 16-byte chunks (row g and row g + 8,
+                        // 64 weights each) with the matching 64 codes by dp4a, plane by plane -- seven of an MMA's
+                        // eight columns would be idle; the four lanes of a row meet once, after the k-loop.
+                        // acc[p][0][0] / acc[p][0][2] are the plane-p sums of row g / g + 8.
                         auto mma_block = [&](const Operands& o) {
                             const uint32_t lw[4] = {o.lo.x, o.lo.y, o.lo.z, o.lo.w};
                             const uint32_t hw[4] = {o.hi.x, o.hi.y, o.hi.z, o.hi.w};
 #pragma unroll
-                            for (int xp = 0; xp < 2; ++xp) {
-                                const uint32_t b0[4] = {o.b[2 * xp].x, o.b[2 * xp].y, o.b[2 * xp].z, o.b[2 * xp].w};
-                                const uint32_t b1[4] = {o.b[2 * xp + 1].x, o.b[2 * xp + 1].y, o.b[2 * xp + 1].z, o.b[2 * xp + 1].w};
+                            for (int x = 0; x < 4; ++x) {
+                                const uint32_t a[4] = {o.b[x].x, o.b[x].y, o.b[x].z, o.b[x].w};   // word p: plane p of quarter x
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const uint32_t mk = 0x03030303u << (2 * j);
-                                    mma_u8s8(acc[j][0], lw[2 * xp] & mk, hw[2 * xp] & mk, lw[2 * xp + 1] & mk,
-                                             hw[2 * xp + 1] & mk, b0[j], b1[j]);
+                                    acc[j][0][0] = dp4a_su(static_cast<int>(a[j]), lw[x] & mk, acc[j][0][0]);
+                                    acc[j][0][2] = dp4a_su(static_cast<int>(a[j]), hw[x] & mk, acc[j][0][2]);
                                 }
                             }
                         };
@@ -590,6 +593,19 @@ gemv_strip_kernel(const __grid_constant__ StripParams P) {
             if (!alive) break;
 
             if (active) {
+                if constexpr (FAST == 1) {
+                    // the four lanes of a row (t = 0..3) hold the sums of their quarters of every k-block
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+                            int v = acc[j][0][e];
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                            acc[j][0][e] = v;
+                        }
+                    }
+                }
                 // exact recombination of the scaled partial sums, then the cross-warp reduction
                 int tot[NT][4];
 #pragma unroll
