@@ -9,6 +9,8 @@
 // log and the tree-shaped sums of the norms and the softmax denominator.
 #include <cmath>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -457,6 +459,132 @@ mamba_mix_kernel(const float* __restrict__ xv, const float* __restrict__ zv, con
     }
 }
 
+// The same three stages with a sequence's channels spread over a thread-block cluster of kMixCluster CTAs (one SM
+// cannot hide the latency of a sequence's 100 KB of state on its own: 20 us per launch as one CTA).  CTA `rank` owns
+// a contiguous slice of the d_inner channels: their conv taps, ring rows, SSD state rows and outputs.  The B and C
+// channels of the convolution (2 * n_groups * d_state values every CTA needs) are recomputed by every CTA from the
+// same ring taps; only rank 0 moves their window on, after a cluster barrier behind which every CTA holds the taps
+// in registers.  The gated norm's sum of squares is the fixed-order sum of the CTAs' partial sums, exchanged through
+// rank 0's shared memory (distributed shared memory).  One channel per thread; kernel width K <= 4, d_state = 16.
+constexpr int kMixCluster = 8;
+constexpr int kMixThreads = 256;
+__global__ void __launch_bounds__(kMixThreads)
+mamba_mix_cluster_kernel(const float* __restrict__ xv, const float* __restrict__ zv, const float* __restrict__ Bv,
+                         const float* __restrict__ Cv, const float* __restrict__ dt, const float* __restrict__ conv_w,
+                         const float* __restrict__ conv_b, const float* __restrict__ A_log, const float* __restrict__ Dp,
+                         const float* __restrict__ norm_w, float* __restrict__ ring, float* __restrict__ state,
+                         int n_heads, int d_head, int n_groups, int K, float eps, float* __restrict__ out) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int N = 16, kMaxK = 4;
+    extern __shared__ float sm[];
+    const int d_inner = n_heads * d_head, GS = n_groups * N, conv_dim = d_inner + 2 * GS;
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int r = blockIdx.x / kMixCluster;
+    const int per = (d_inner + kMixCluster - 1) / kMixCluster;
+    const int c_lo = min(d_inner, rank * per), n_own = min(d_inner, c_lo + per) - c_lo;
+    float* xs = sm;                           // [per]     conv outputs of the CTA's own channels
+    float* bc = xs + per;                     // [2 * GS]  conv outputs of the B and C channels
+    float* delta_s = bc + 2 * GS;             // [n_heads]
+    float* decay_s = delta_s + n_heads;       // [n_heads]
+    float* scratch = decay_s + n_heads;       // [32]
+    float* parts = scratch + 32;              // [kMixCluster], rank 0's copy is the one used
+    const int taps = K - 1;
+    float* rr = ring + static_cast<size_t>(r) * (taps > 0 ? taps : 1) * conv_dim;
+    // per-head step sizes and decays, by the last warp while the others start on the convolution
+    if (static_cast<int>(threadIdx.x) >= kMixThreads - 32) {
+        for (int h = threadIdx.x - (kMixThreads - 32); h < n_heads; h += 32) {
+            const float dt_raw = dt[static_cast<size_t>(r) * n_heads + h];
+            const float a_log = __ldg(A_log + h);
+            const float delta = dt_raw > 20.0f ? dt_raw : (dt_raw < -20.0f ? expf(dt_raw) : log1pf(expf(dt_raw)));
+            float decay;
+            if (!isfinite(dt_raw) || !isfinite(a_log)) {
+                decay = nanf("");
+            } else {
+                const double log_delta = dt_raw < -20.0f ? static_cast<double>(dt_raw) : log(static_cast<double>(delta));
+                const double log_q = log_delta + static_cast<double>(a_log);
+                decay = log_q > 50.0 ? 0.0f : static_cast<float>(exp(-exp(log_q)));
+            }
+            delta_s[h] = delta;
+            decay_s[h] = decay;
+        }
+    }
+    // convolution: thread i < n_own takes channel c_lo + i, the next 2 * GS threads the B and C channels
+    const int idx = threadIdx.x;
+    const int c = idx < n_own ? c_lo + idx : (idx < n_own + 2 * GS ? d_inner + (idx - n_own) : -1);
+    float tapv[kMaxK];
+    if (c >= 0) {
+        const float current = c < d_inner ? xv[static_cast<size_t>(r) * d_inner + c]
+                                          : (c < d_inner + GS ? Bv[static_cast<size_t>(r) * GS + c - d_inner]
+                                                              : Cv[static_cast<size_t>(r) * GS + c - d_inner - GS]);
+        float wv[kMaxK];
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+            if (j < K) {
+                tapv[j] = j < taps ? rr[static_cast<size_t>(j) * conv_dim + c] : current;
+                wv[j] = __ldg(conv_w + static_cast<size_t>(c) * K + j);
+            }
+        }
+        float value = __ldg(conv_b + c);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j)
+            if (j < K) value = __fadd_rn(value, __fmul_rn(wv[j], tapv[j]));
+        const float act = silu_stable(value);
+        if (c < d_inner) xs[idx] = act; else bc[c - d_inner] = act;
+    }
+    // SSD state row, gate and skip weight of the thread's channel: in flight across the barrier
+    float hv[N], zval = 0.0f, dval = 0.0f;
+    const int chan = c_lo + idx;
+    if (idx < n_own) {
+        zval = zv[static_cast<size_t>(r) * d_inner + chan];
+        dval = __ldg(Dp + chan / d_head);
+        const float4* st4 = reinterpret_cast<const float4*>(state + (static_cast<size_t>(r) * d_inner + chan) * N);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 v = st4[q];
+            hv[4 * q] = v.x; hv[4 * q + 1] = v.y; hv[4 * q + 2] = v.z; hv[4 * q + 3] = v.w;
+        }
+    }
+    cluster.sync();          // every CTA holds the taps it needs: the windows may move on; conv outputs visible
+    if (c >= 0 && (c < d_inner || rank == 0)) {
+#pragma unroll
+        for (int j = 0; j + 1 < kMaxK; ++j)
+            if (j < taps) rr[static_cast<size_t>(j) * conv_dim + c] = tapv[j + 1];
+    }
+    float ss = 0.0f, gv = 0.0f;
+    if (idx < n_own) {
+        const int h = chan / d_head;
+        const int group = (h * n_groups) / n_heads;
+        const float delta = delta_s[h], decay = decay_s[h];
+        const float input = xs[idx];
+        const float* Bg = bc + group * N;
+        const float* Cg = bc + GS + group * N;
+        float y = __fmul_rn(dval, input);
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+            hv[n] = __fadd_rn(__fmul_rn(decay, hv[n]), __fmul_rn(__fmul_rn(delta, Bg[n]), input));
+            y = __fadd_rn(y, __fmul_rn(hv[n], Cg[n]));
+        }
+        float4* st4 = reinterpret_cast<float4*>(state + (static_cast<size_t>(r) * d_inner + chan) * N);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st4[q] = make_float4(hv[4 * q], hv[4 * q + 1], hv[4 * q + 2], hv[4 * q + 3]);
+        gv = __fmul_rn(y, silu_two_sided(zval));
+        ss = gv * gv;
+    }
+    const float partial = block_sum(ss, scratch);
+    if (threadIdx.x == 0) cluster.map_shared_rank(parts, 0)[rank] = partial;
+    cluster.sync();
+    const float* all = cluster.map_shared_rank(parts, 0);
+    float total = 0.0f;
+    for (int k = 0; k < kMixCluster; ++k) total += all[k];        // fixed order: the same sum in every CTA
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d_inner)), eps)));
+    if (idx < n_own) {
+        const float n = __fmul_rn(gv, inv);
+        out[static_cast<size_t>(r) * d_inner + chan] = norm_w ? __fmul_rn(n, __ldg(norm_w + chan)) : n;
+    }
+    cluster.sync();          // rank 0's shared memory stays alive until every CTA has read the partial sums
+}
+
 // ---- out = x + (a * ga [+ b * gb]); ga == null: out = x + a ----------------------------------------------------
 __global__ void __launch_bounds__(256) gated_residual_kernel(const float* __restrict__ x, const float* __restrict__ a,
                                                              const float* __restrict__ ga, const float* __restrict__ b,
@@ -791,10 +919,33 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                 if (dev >= 0 && dev < 64) configured[dev] = true;
             }
         }
-        mamba_mix_kernel<<<B, kFusedThreads, mix_smem, st>>>(
-            S.proj, S.proj + S.proj_stride, S.proj + 2 * S.proj_stride, S.proj + 3 * S.proj_stride, S.proj + 4 * S.proj_stride,
-            mm.conv_w, mm.conv_b, mm.A_log, mm.D, mm.norm_w, state.block[i].ring, state.block[i].ssm, mm.n_heads, mm.d_head,
-            mm.d_state, mm.n_groups, mm.conv_kernel, mm.norm_eps, S.gated);
+        const int per_cta = (mm.d_inner + kMixCluster - 1) / kMixCluster;
+        if (mm.d_state == 16 && mm.conv_kernel >= 1 && mm.conv_kernel <= 4 && per_cta + 2 * GS <= kMixThreads) {
+            // a sequence's channels over a cluster of 8 CTAs
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(static_cast<unsigned>(kMixCluster) * B);
+            cfg.blockDim = dim3(kMixThreads);
+            cfg.dynamicSmemBytes = sizeof(float) * (per_cta + 2 * GS + 2 * mm.n_heads + 32 + kMixCluster);
+            cfg.stream = st;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = kMixCluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            if (cudaLaunchKernelEx(&cfg, mamba_mix_cluster_kernel, static_cast<const float*>(S.proj),
+                                   static_cast<const float*>(S.proj + S.proj_stride),
+                                   static_cast<const float*>(S.proj + 2 * S.proj_stride),
+                                   static_cast<const float*>(S.proj + 3 * S.proj_stride),
+                                   static_cast<const float*>(S.proj + 4 * S.proj_stride), mm.conv_w, mm.conv_b, mm.A_log, mm.D,
+                                   mm.norm_w, state.block[i].ring, state.block[i].ssm, mm.n_heads, mm.d_head, mm.n_groups,
+                                   mm.conv_kernel, mm.norm_eps, S.gated) != cudaSuccess)
+                return TBL_ERR_CUDA;
+        } else {
+            mamba_mix_kernel<<<B, kFusedThreads, mix_smem, st>>>(
+                S.proj, S.proj + S.proj_stride, S.proj + 2 * S.proj_stride, S.proj + 3 * S.proj_stride, S.proj + 4 * S.proj_stride,
+                mm.conv_w, mm.conv_b, mm.A_log, mm.D, mm.norm_w, state.block[i].ring, state.block[i].ssm, mm.n_heads, mm.d_head,
+                mm.d_state, mm.n_groups, mm.conv_kernel, mm.norm_eps, S.gated);
+        }
         if ((rc = launched()) != TBL_OK) return rc;
         if ((rc = linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
         if (!b.hybrid) {
