@@ -140,20 +140,35 @@ __global__ void __launch_bounds__(128) mamba_ssd_step_kernel(const float* __rest
 // One CTA per (query head, row).  RoPE on q and on the new key at the row's position; the first head of a
 // KV group appends the rotated key and the value to the cache; every CTA keeps the new key / value of its group
 // in shared memory, so no CTA reads what another one writes in this launch.
-constexpr int kAttnThreads = 128;
+//   scores   one cached token per thread, the dot product in dimension order (a thread streams a whole key row)
+//   softmax  warp shuffles, then one value per warp through shared memory
+//   values   head_dim / 4 threads cover one value row with 128-bit loads; the CTA's thread groups take the cached
+//            tokens round-robin, several rows in flight per thread, and their partial sums are added in group
+//            order.  (With one dimension per thread and the tokens in sequence the launch's time was the cache's
+//            load latency times the context length.)
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnPartial = 4 * kAttnThreads;     // floats: one float4 of partial sums per thread
+constexpr int kAttnMaxHeadDim = 4 * kAttnThreads;  // a value row is covered by at most one CTA's worth of float4s
+
+static size_t attention_smem_bytes(int head_dim, int capacity) {
+    return sizeof(float) * (static_cast<size_t>(3) * head_dim + kAttnWarps + kAttnPartial + capacity);
+}
+
 __global__ void __launch_bounds__(kAttnThreads)
 attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ kv, float* __restrict__ k_cache,
                         float* __restrict__ v_cache, int capacity, const int32_t* __restrict__ positions,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rope_positions,
                         int n_heads, int n_kv_heads, int head_dim, int sliding_window, float* __restrict__ out,
                         int* status) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float* qr = sm;                       // [head_dim]
     float* knew = qr + head_dim;          // [head_dim]
     float* vnew = knew + head_dim;        // [head_dim]
-    float* red = vnew + head_dim;         // [kAttnThreads]
-    float* scores = red + kAttnThreads;   // [capacity]
-    const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+    float* red = vnew + head_dim;         // [kAttnWarps]
+    float* partial = red + kAttnWarps;    // [kAttnPartial]
+    float* scores = partial + kAttnPartial;   // [capacity]
+    const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kv_dim = n_kv_heads * head_dim, half = head_dim / 2, d_model = n_heads * head_dim;
     const int group = n_heads / n_kv_heads > 0 ? n_heads / n_kv_heads : 1;
     const int kvh = min(h / group, n_kv_heads - 1);
@@ -180,22 +195,23 @@ attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k
         vnew[i + half] = kh[kv_dim + i + half];
     }
     __syncthreads();
+    const size_t head_base = static_cast<size_t>(r) * capacity * kv_dim + static_cast<size_t>(kvh) * head_dim;
     if (h == kvh * group) {
-        float* kc = k_cache + (static_cast<size_t>(r) * capacity + pos) * kv_dim + kvh * head_dim;
-        float* vc = v_cache + (static_cast<size_t>(r) * capacity + pos) * kv_dim + kvh * head_dim;
+        float* kc = k_cache + head_base + static_cast<size_t>(pos) * kv_dim;
+        float* vc = v_cache + head_base + static_cast<size_t>(pos) * kv_dim;
         for (int d = tid; d < head_dim; d += kAttnThreads) { kc[d] = knew[d]; vc[d] = vnew[d]; }
     }
     const int cached = pos + 1;
     const int first = max(0, cached - sliding_window);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(head_dim)));
-    // scores: one token per thread, the dot product in dimension order
+    // scores: one token per thread, the dot product in dimension order; the new token's key is the one in shared memory
     float local_max = -1e30f;
     for (int t = first + tid; t < cached; t += kAttnThreads) {
         float dot = 0.0f;
         if (t == pos) {
             for (int d = 0; d < head_dim; ++d) dot = __fadd_rn(dot, __fmul_rn(qr[d], knew[d]));
         } else {
-            const float4* key = reinterpret_cast<const float4*>(k_cache + (static_cast<size_t>(r) * capacity + t) * kv_dim + kvh * head_dim);
+            const float4* key = reinterpret_cast<const float4*>(k_cache + head_base + static_cast<size_t>(t) * kv_dim);
             for (int d4 = 0; d4 < head_dim / 4; ++d4) {
                 const float4 k4 = key[d4];
                 dot = __fadd_rn(dot, __fmul_rn(qr[4 * d4], k4.x));
@@ -208,13 +224,13 @@ attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k
         scores[t - first] = sc;
         local_max = fmaxf(local_max, sc);
     }
-    red[tid] = local_max;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, o));
+    if (lane == 0) red[warp] = local_max;
     __syncthreads();
-    for (int o = kAttnThreads / 2; o; o >>= 1) {
-        if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
-        __syncthreads();
-    }
-    const float max_s = red[0];
+    float max_s = red[0];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) max_s = fmaxf(max_s, red[w]);
     __syncthreads();
     float local_sum = 0.0f;
     for (int t = first + tid; t < cached; t += kAttnThreads) {
@@ -222,22 +238,52 @@ attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k
         scores[t - first] = e;
         local_sum += e;
     }
-    red[tid] = local_sum;
-    __syncthreads();
-    for (int o = kAttnThreads / 2; o; o >>= 1) {
-        if (tid < o) red[tid] += red[tid + o];
-        __syncthreads();
-    }
-    const float inv_sum = __fdiv_rn(1.0f, fmaxf(red[0], 1e-9f));
-    // weighted sum of the values: one dimension per thread, tokens in order
-    for (int d = tid; d < head_dim; d += kAttnThreads) {
-        float acc = 0.0f;
-        const float* vbase = v_cache + static_cast<size_t>(r) * capacity * kv_dim + kvh * head_dim + d;
-        for (int t = first; t < cached; ++t) {
-            const float v = t == pos ? vnew[d] : vbase[static_cast<size_t>(t) * kv_dim];
-            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(scores[t - first], inv_sum), v));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) local_sum += __shfl_xor_sync(0xffffffffu, local_sum, o);
+    if (lane == 0) red[warp] = local_sum;
+    __syncthreads();                      // also: every thread's exp() is in scores[] now
+    float total = red[0];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) total += red[w];
+    const float inv_sum = __fdiv_rn(1.0f, fmaxf(total, 1e-9f));
+    // weighted sum of the values
+    const int row_threads = head_dim / 4;                     // threads that cover one value row
+    const int groups = kAttnThreads / row_threads;            // token groups of this CTA (>= 1: head_dim <= 4 * threads)
+    const int g = tid / row_threads, d4 = tid - g * row_threads;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (g < groups) {
+        const float4* vrow = reinterpret_cast<const float4*>(v_cache + head_base) + d4;
+        const size_t step = static_cast<size_t>(kv_dim / 4);   // float4s between two tokens' rows
+        constexpr int kInFlight = 8;
+        int t = first + g;
+        for (; t + (kInFlight - 1) * groups < pos; t += kInFlight * groups) {
+            float4 v[kInFlight];
+#pragma unroll
+            for (int j = 0; j < kInFlight; ++j) v[j] = vrow[static_cast<size_t>(t + j * groups) * step];
+#pragma unroll
+            for (int j = 0; j < kInFlight; ++j) {
+                const float p = __fmul_rn(scores[t + j * groups - first], inv_sum);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(p, v[j].x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(p, v[j].y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(p, v[j].z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(p, v[j].w));
+            }
         }
-        out[static_cast<size_t>(r) * d_model + h * head_dim + d] = acc;
+        for (; t < cached; t += groups) {
+            const float4 v = t == pos ? reinterpret_cast<const float4*>(vnew)[d4] : vrow[static_cast<size_t>(t) * step];
+            const float p = __fmul_rn(scores[t - first], inv_sum);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(p, v.x));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(p, v.y));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(p, v.z));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(p, v.w));
+        }
+        reinterpret_cast<float4*>(partial)[tid] = acc;        // partial[g][4 * d4 ..]: tid = g * row_threads + d4
+    }
+    __syncthreads();
+    for (int d = tid; d < head_dim; d += kAttnThreads) {
+        float sum = partial[d];
+        for (int j = 1; j < groups; ++j) sum = __fadd_rn(sum, partial[j * head_dim + d]);
+        out[static_cast<size_t>(r) * d_model + h * head_dim + d] = sum;
     }
 }
 
@@ -773,7 +819,8 @@ int tbl_attention_decode(const float* q_dev, const float* kv_dev, float* k_cache
     if (capacity <= 0 || rope_positions <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || head_dim % 4 ||
         sliding_window <= 0 || rows <= 0)
         return TBL_ERR_INVALID_ARG;
-    const size_t smem = sizeof(float) * (3 * head_dim + kAttnThreads + capacity);
+    if (head_dim > kAttnMaxHeadDim || (n_kv_heads * head_dim) % 4) return TBL_ERR_SHAPE;
+    const size_t smem = attention_smem_bytes(head_dim, capacity);
     if (smem > 200 * 1024) return TBL_ERR_SHAPE;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
@@ -970,7 +1017,8 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
             }
         }
         if (!qkv_folded && (rc = group(qkv, 2, S.attn_in, S.qkv, S.qkv_stride)) != TBL_OK) return rc;
-        const size_t attn_smem = sizeof(float) * (3 * a.head_dim + kAttnThreads + capacity);
+        if (a.head_dim > kAttnMaxHeadDim || a.head_dim % 4) return TBL_ERR_SHAPE;
+        const size_t attn_smem = attention_smem_bytes(a.head_dim, capacity);
         if (attn_smem > 200 * 1024) return TBL_ERR_SHAPE;
         if (attn_smem > 48 * 1024) {
             static bool configured[64] = {};

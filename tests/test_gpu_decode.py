@@ -124,6 +124,37 @@ def test_attention_decode_over_the_cache(cuda, port, tbl, rows, nh, nkv, hd, win
     assert not out.cpu().numpy().any()
 
 
+@pytest.mark.parametrize("rows,nh,nkv,hd,window,start", [(2, 4, 2, 64, 4096, 517), (1, 12, 12, 64, 4096, 255), (2, 2, 1, 32, 300, 700),
+                                                         (1, 2, 2, 128, 4096, 130), (3, 3, 3, 24, 4096, 97)])
+def test_attention_decode_over_a_long_cache(cuda, port, tbl, rows, nh, nkv, hd, window, start):
+    """Hundreds of cached tokens per row (the value sum is split over the CTA's thread groups and the loads are
+    batched there), rows at different positions, a sliding window shorter than the cache, head widths whose
+    value rows take 6, 8, 16 and 32 threads."""
+    import gpu_helpers as H
+    torch = cuda
+    rng = np.random.default_rng(start + hd)
+    capacity = rope_positions = start + 8
+    pos = np.arange(rope_positions, dtype=np.float32)[:, None]
+    freq = (1.0 / np.power(np.float32(10000.0), (2.0 * np.arange(hd // 2) / hd).astype(np.float32))).astype(np.float32)
+    cos_t, sin_t = np.cos(pos * freq).astype(np.float32), np.sin(pos * freq).astype(np.float32)
+    k_cache = rng.standard_normal((rows, capacity, nkv * hd)).astype(np.float32)
+    v_cache = rng.standard_normal((rows, capacity, nkv * hd)).astype(np.float32)
+    tokens = (start - 3 * np.arange(rows)).astype(np.int32)        # every row at its own position
+    d_k, d_v = H.dev(k_cache), H.dev(v_cache)
+    d_cos, d_sin = H.dev(cos_t), H.dev(sin_t)
+    for step in range(3):
+        q = rng.standard_normal((rows, nh * hd)).astype(np.float32)
+        kv = rng.standard_normal((rows, 2 * nkv * hd)).astype(np.float32)
+        d_pos = H.dev(tokens.copy())
+        want = port.attention_decode(q, kv, k_cache, v_cache, tokens, cos_t, sin_t, nh, nkv, hd, window)
+        out = torch.empty((rows, nh * hd), device="cuda")
+        assert tbl.tbl_attention_decode(H.ptr(H.dev(q)), H.ptr(H.dev(kv)), H.ptr(d_k), H.ptr(d_v), capacity, H.ptr(d_pos), H.ptr(d_cos),
+                                        H.ptr(d_sin), rope_positions, nh, nkv, hd, window, rows, H.ptr(out), H.stream_ptr()) == 0
+        assert rel_err(out.cpu().numpy(), want) <= 2e-6, f"step {step}"
+        assert bits_equal(d_k.cpu().numpy(), k_cache) and bits_equal(d_v.cpu().numpy(), v_cache)
+    assert H.device_status() == 0
+
+
 def _compare_step(tag, got_hidden, got_logits, want_hidden, want_logits):
     """Returns (worst residual error, worst logit error, share of logits within 1e-5, tight) after the loose asserts."""
     worst, worst_median = 0.0, 0.0
