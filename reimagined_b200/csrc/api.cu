@@ -40,7 +40,7 @@ struct Workspace {
     size_t bytes;
 };
 
-constexpr int kWidenMinRows = 32;     // more rows than this (and <= 256, K % 512 == 0): the widening tensor-core kernel
+constexpr int kWidenMinRows = 32;     // more rows than this (and <= 256, K % 256 == 0): the widening tensor-core kernel
 
 Workspace carve(void* base, int M, int K) {
     Workspace w;
@@ -48,13 +48,41 @@ Workspace carve(void* base, int M, int K) {
     size_t off = 0;
     const size_t mk = round_up(static_cast<size_t>(M) * K, 256);
     w.q = reinterpret_cast<int8_t*>(p + off); off += mk;
-    w.qp = reinterpret_cast<int8_t*>(p + off); off += mk;
+    // the second copy is the interleaved one (M * K bytes) or the plane-major one (rows padded to 512 codes)
+    w.qp = reinterpret_cast<int8_t*>(p + off); off += round_up(static_cast<size_t>(M) * round_up(static_cast<size_t>(K), 512), 256);
     const size_t vec = round_up(static_cast<size_t>(M) * 4, 256);
     w.act_scales = reinterpret_cast<float*>(p + off); off += vec;
     w.q_sums = reinterpret_cast<int32_t*>(p + off); off += vec;
     w.inv_norm = reinterpret_cast<float*>(p + off); off += vec;
     w.bytes = off;
     return w;
+}
+
+// Mid-size batches (kWidenMinRows < M <= 256) of up to kWidenMaxViews weight matrices that share the input rows: the
+// rows are quantised once, straight into the plane-major layout where the register quantiser serves the width, and
+// every pass of up to 128 rows is one launch of the widening tensor-core kernel over all the matrices.
+bool widen_rows_ok(int M, int K) { return M > kWidenMinRows && M <= 2 * 128 && K >= 256 && (K & 255) == 0; }
+
+int widen_forward(const WidenView* views, int count, const float* x, int M, int K, int bits, int rms_mode,
+                  const Workspace& w, cudaStream_t st) {
+    const int ld = gemm_widen_plane_ld(K);
+    const bool direct = K <= 32768;            // the register quantiser writes the planes itself
+    cudaError_t e = launch_quantize_rows(x, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, direct ? nullptr : w.q,
+                                         direct ? w.qp : nullptr, w.act_scales, w.q_sums, w.inv_norm, nullptr,
+                                         QuantSegments{}, st, direct ? ld : 0);
+    if (e != cudaSuccess) return TBL_ERR_CUDA;
+    for (int m0 = 0; m0 < M; m0 += 128) {
+        const int rows = M - m0 < 128 ? M - m0 : 128;
+        WidenView pass[kWidenMaxViews];
+        for (int v = 0; v < count; ++v) {
+            pass[v] = views[v];
+            pass[v].y = views[v].y + static_cast<size_t>(m0) * views[v].N;
+        }
+        e = launch_gemm_widen(pass, count, direct ? nullptr : w.q + static_cast<size_t>(m0) * K,
+                              w.qp + static_cast<size_t>(m0) * ld, w.act_scales + m0, w.q_sums + m0, rows, K, st);
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+    }
+    return TBL_OK;
 }
 
 // GEMV on already-quantised activations for any M (the tensor-core kernel walks M in tiles of 64).
@@ -274,18 +302,10 @@ int tbl_linear_forward(const float* x_dev, const uint32_t* words_dev, const void
     const Workspace w = carve(workspace_dev, M, K);
     // mid-size batches on the strip-major 2-bit weights: widened in shared memory, multiplied on the tcgen05 tensor cores, up to
     // 128 rows per pass (the plane-major copy of the codes takes the place of the interleaved one in the workspace)
-    if (strip && M > kWidenMinRows && M <= 2 * 128 && (K & 511) == 0) {
-        cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, w.q, nullptr, w.act_scales,
-                                             w.q_sums, w.inv_norm, nullptr, QuantSegments{}, st);
-        if (e != cudaSuccess) return TBL_ERR_CUDA;
-        for (int m0 = 0; m0 < M; m0 += 128) {
-            const int rows = M - m0 < 128 ? M - m0 : 128;
-            e = launch_gemm_widen(w.q + static_cast<size_t>(m0) * K, w.qp + static_cast<size_t>(m0) * K, w.act_scales + m0,
-                                  w.q_sums + m0, strips_dev, weight_scale, magnitude_dev, bias_dev, rows, K, N,
-                                  y_dev + static_cast<size_t>(m0) * N, st);
-            if (e != cudaSuccess) return TBL_ERR_CUDA;
-        }
-        return TBL_OK;
+    if (strip && widen_rows_ok(M, K)) {
+        WidenView v{};
+        v.strips = strips_dev; v.magnitude = magnitude_dev; v.bias = bias_dev; v.y = y_dev; v.weight_scale = weight_scale; v.N = N;
+        return widen_forward(&v, 1, x_dev, M, K, bits, rms_mode, w, st);
     }
     // the strip GEMV reads only the interleaved copy; the other paths read the row-major codes
     cudaError_t e = launch_quantize_rows(x_dev, nullptr, M, K, bits, rms_mode, TBL_TIE_EVEN, strip ? nullptr : w.q,
@@ -346,6 +366,17 @@ int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int 
         pr.weight_scale = v.weight_scale; pr.rows = rows; pr.N = v.outputs; pr.K = v.inputs; pr.ldy = v.outputs;
         pr.squared_relu = 1;
         return cuda_status(launch_gemv_strip(&pr, 1, st));
+    }
+    if (squared_relu && v.strips && aligned16(v.strips) && aligned16(x) && gemv_strip_supported(v.inputs) &&
+        !(v.w_i8 && rows > 64) && widen_rows_ok(rows, v.inputs) &&
+        check_problem(rows, v.inputs, v.outputs, v.weight_scale, v.activation_bits) == TBL_OK) {
+        // mid-size batches: the widening tensor-core kernel squares in its epilogue too
+        if (!workspace || workspace_bytes < tbl_linear_workspace_bytes(rows, v.inputs, v.outputs)) return TBL_ERR_WORKSPACE;
+        if (!aligned16(workspace)) return TBL_ERR_ALIGNMENT;
+        WidenView wv{};
+        wv.strips = v.strips; wv.magnitude = v.magnitude; wv.bias = v.bias; wv.y = y; wv.weight_scale = v.weight_scale;
+        wv.N = v.outputs; wv.squared_relu = 1;
+        return widen_forward(&wv, 1, x, rows, v.inputs, v.activation_bits, mode, carve(workspace, rows, v.inputs), st);
     }
     const int rc = tbl_linear_forward(x, v.packed, v.strips, rows > 64 ? v.w_i8 : nullptr, v.weight_scale, rows, v.inputs,
                                       v.outputs, v.activation_bits, mode, v.magnitude, v.bias, y, workspace, workspace_bytes, st);
@@ -592,6 +623,17 @@ int tbl_grouped_forward_rows(const tbl_linear_view* views_host, int groups, cons
             pr[g].rms_fast = mode == TBL_RMS_FAST;
         }
         return cuda_status(launch_gemv_strip(pr, groups, st));
+    }
+    if (mma && groups <= kWidenMaxViews && widen_rows_ok(rows, K)) {
+        // more rows than the GEMV's tiles serve well: one launch of the widening tensor-core kernel over all the views
+        WidenView wv[kWidenMaxViews];
+        for (int g = 0; g < groups; ++g) {
+            wv[g] = WidenView{};
+            wv[g].strips = views_host[g].strips; wv[g].magnitude = views_host[g].magnitude; wv[g].bias = views_host[g].bias;
+            wv[g].y = output_dev + static_cast<size_t>(g) * output_stride;
+            wv[g].weight_scale = views_host[g].weight_scale; wv[g].N = views_host[g].outputs;
+        }
+        return widen_forward(wv, groups, input_dev, rows, K, views_host[0].activation_bits, mode, w, st);
     }
     cudaError_t e = launch_quantize_rows(input_dev, nullptr, rows, K, views_host[0].activation_bits, mode,
                                          TBL_TIE_EVEN, mma ? nullptr : w.q, mma ? w.qp : nullptr, w.act_scales,

@@ -60,17 +60,32 @@ constexpr int kMaxBStages = 16;              // activation boxes of two planes: 
 constexpr int kBRingBytes = 64 * 1024;
 constexpr int kNumSmW = 148;
 
-struct WidenParams {
-    const float* act_scales;
-    const int32_t* q_sums;
+struct WidenTiles {            // one weight matrix of the launch
+    const uint8_t* strips;     // strip-major weights
     const float* magnitude;
     const float* bias;
     float* y;
     float weight_scale;
-    const uint8_t* strips;     // strip-major weights
-    int M, K, N, n_pad, kblocks, tiles, nstrips;
+    int N, nstrips;
+    int tile0;                 // its first tile in the launch's tile list (128 weight rows per tile)
+    int squared_relu;
+};
+
+struct WidenParams {
+    const float* act_scales;
+    const int32_t* q_sums;
+    WidenTiles view[kWidenMaxViews];
+    int views;
+    int M, K, n_pad, kblocks, tiles;
     int* status;
 };
+
+// the view a tile belongs to (the views' tile ranges are consecutive)
+__device__ __forceinline__ int view_of(const WidenParams& p, int tile) {
+    int v = 0;
+    while (v + 1 < p.views && tile >= p.view[v + 1].tile0) ++v;
+    return v;
+}
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -157,7 +172,8 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             int it = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
-                const int first = tile * 8, cnt = min(8, p.nstrips - first);
+                const WidenTiles& vw = p.view[view_of(p, tile)];
+                const int first = (tile - vw.tile0) * 8, cnt = min(8, vw.nstrips - first);
                 for (int sl = 0; sl < slabs; ++sl, ++it) {
                     const int s = it % kRawStages;
                     if (it >= kRawStages) {
@@ -168,7 +184,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
                     const uint32_t bytes = static_cast<uint32_t>(cnt) * sbs * 1024;
                     mbar_arrive_expect_tx(&raw_full[s], bytes);
                     bulk_g2s_hint(raw_buf + s * kRawBytes,
-                                  p.strips + ((static_cast<size_t>(4) * sl * p.nstrips + static_cast<size_t>(first) * sbs) << 10), bytes,
+                                  vw.strips + ((static_cast<size_t>(4) * sl * vw.nstrips + static_cast<size_t>(first) * sbs) << 10), bytes,
                                   &raw_full[s], policy);
                 }
             }
@@ -293,10 +309,15 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
-            const int n = tile * 128 + quarter * 32 + lane;
+            const WidenTiles& vw = p.view[view_of(p, tile)];
+            const int n = (tile - vw.tile0) * 128 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            const float mag = (p.magnitude && n < p.N) ? __ldg(p.magnitude + n) : 1.0f;
-            const float bia = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            const float mag = (vw.magnitude && n < vw.N) ? __ldg(vw.magnitude + n) : 1.0f;
+            const float bia = (vw.bias && n < vw.N) ? __ldg(vw.bias + n) : 0.0f;
+            const float wscale = vw.weight_scale;
+            const bool has_mag = vw.magnitude != nullptr, has_bias = vw.bias != nullptr, sq = vw.squared_relu != 0;
+            float* yv = vw.y;
+            const int N = vw.N;
             for (int m0 = ehalf * 16; m0 < n_pad; m0 += 32) {
                 uint32_t d0[16], d1[16], d2[16], d3[16];
                 tmem_ld16(t_row + m0, d0);
@@ -311,10 +332,11 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
                         // exact: plane p's sum is a multiple of 4^p
                         const int total = static_cast<int>(d0[j]) + (static_cast<int>(d1[j]) >> 2) + (static_cast<int>(d2[j]) >> 4) +
                                           (static_cast<int>(d3[j]) >> 6) - __ldg(p.q_sums + m);
-                        float v = __fmul_rn(static_cast<float>(total), __fmul_rn(__ldg(p.act_scales + m), p.weight_scale));
-                        if (p.magnitude) v = __fmul_rn(v, mag);
-                        if (p.bias) v = __fadd_rn(v, bia);
-                        if (n < p.N) p.y[static_cast<size_t>(m) * p.N + n] = v;
+                        float v = __fmul_rn(static_cast<float>(total), __fmul_rn(__ldg(p.act_scales + m), wscale));
+                        if (has_mag) v = __fmul_rn(v, mag);
+                        if (has_bias) v = __fadd_rn(v, bia);
+                        if (sq) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
+                        if (n < N) yv[static_cast<size_t>(m) * N + n] = v;
                     }
                 }
             }
@@ -338,38 +360,44 @@ inline size_t round_up_w(size_t v, size_t a) { return (v + a - 1) / a * a; }
 }  // namespace
 
 bool gemm_widen_supported(int M, int K, int N) {
-    return M >= 1 && M <= kMaxNpad && K >= 512 && (K & 511) == 0 && N >= 1;
+    return M >= 1 && M <= kMaxNpad && K >= 256 && (K & 255) == 0 && N >= 1;
 }
+
+int gemm_widen_plane_ld(int K) { return static_cast<int>(round_up_w(K, kBlockK)); }
 
 size_t gemm_widen_scratch_bytes(int M, int K) {
     return round_up_w(static_cast<size_t>(M) * round_up_w(K, kBlockK), 256);
 }
 
-// q: row-major codes [M, K]; qw_scratch: gemm_widen_scratch_bytes(M, K) bytes; strips: the strip-major weights.
-cudaError_t launch_gemm_widen(const int8_t* q, int8_t* qw_scratch, const float* act_scales, const int32_t* q_sums,
-                              const void* strips, float weight_scale, const float* magnitude, const float* bias,
-                              int M, int K, int N, float* y, cudaStream_t stream) {
-    if (!gemm_widen_supported(M, K, N)) return cudaErrorInvalidValue;
-    const int K_pad = static_cast<int>(round_up_w(K, kBlockK));
-    {
-        const long long groups = static_cast<long long>(M) * (K_pad >> 4);
-        const int grid = static_cast<int>((groups + 255) / 256 < 1184 ? (groups + 255) / 256 : 1184);
-        permute_planes_kernel<<<grid, 256, 0, stream>>>(q, M, K, K_pad, qw_scratch);
-        note_launch();
-    }
+cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q, int8_t* planes, const float* act_scales,
+                              const int32_t* q_sums, int M, int K, cudaStream_t stream) {
+    if (!views || count < 1 || count > kWidenMaxViews || !planes) return cudaErrorInvalidValue;
+    const int K_pad = gemm_widen_plane_ld(K);
     WidenParams p{};
-    p.act_scales = act_scales; p.q_sums = q_sums; p.magnitude = magnitude; p.bias = bias; p.y = y;
-    p.weight_scale = weight_scale; p.M = M; p.K = K; p.N = N;
+    p.act_scales = act_scales; p.q_sums = q_sums; p.M = M; p.K = K; p.views = count;
     p.n_pad = (M + 15) & ~15;
     p.kblocks = K_pad / kBlockK;
-    p.tiles = (N + 127) / 128;
-    p.nstrips = (N + 15) / 16;
-    p.strips = static_cast<const uint8_t*>(strips);
+    int tiles = 0;
+    for (int v = 0; v < count; ++v) {
+        if (!gemm_widen_supported(M, K, views[v].N) || !views[v].strips || !views[v].y) return cudaErrorInvalidValue;
+        WidenTiles& t = p.view[v];
+        t.strips = static_cast<const uint8_t*>(views[v].strips); t.magnitude = views[v].magnitude; t.bias = views[v].bias;
+        t.y = views[v].y; t.weight_scale = views[v].weight_scale; t.N = views[v].N; t.nstrips = (views[v].N + 15) / 16;
+        t.tile0 = tiles; t.squared_relu = views[v].squared_relu;
+        tiles += (views[v].N + 127) / 128;
+    }
+    p.tiles = tiles;
+    if (q) {
+        const long long groups = static_cast<long long>(M) * (K_pad >> 4);
+        const int grid = static_cast<int>((groups + 255) / 256 < 1184 ? (groups + 255) / 256 : 1184);
+        permute_planes_kernel<<<grid, 256, 0, stream>>>(q, M, K, K_pad, planes);
+        note_launch();
+    }
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
     CUtensorMap mq;
     // the plane-major codes [M rows, K_pad bytes], box 128 bytes x n_pad rows
-    if (!make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, qw_scratch, M, K_pad, 128, p.n_pad)) return cudaErrorUnknown;
+    if (!make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, M, K_pad, 128, p.n_pad)) return cudaErrorUnknown;
     const size_t smem = 1024 + kAStages * kAHalfBytes + kRawStages * kRawBytes + kBRingBytes + 512;
     static bool configured[64] = {};
     int dev = 0;

@@ -40,7 +40,7 @@ struct QuantSegments {
 cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
                                  int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
                                  int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
-                                 QuantSegments segments, cudaStream_t stream);
+                                 QuantSegments segments, cudaStream_t stream, int plane_ld = 0);
 cudaError_t launch_expand_i8(const uint32_t* words, int N, int K, int8_t* out, cudaStream_t stream);
 
 // gemv_stream.cu — M <= 4, CUDA-core dp4a, weights streamed by per-warp TMA rings.
@@ -149,13 +149,26 @@ int linear_view_forward_pre(const tbl_linear_view& v, const float* x, int rows, 
 int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
                         void* workspace, size_t workspace_bytes, cudaStream_t st);
 
-// gemm_widen.cu -- 1 <= M <= 64 rows per launch on the strip-major 2-bit weights: widened to bytes inside the kernel,
-// tcgen05 int8 MMAs with the weights as the A operand.  q: row-major codes; qw_scratch: gemm_widen_scratch_bytes.
+// gemm_widen.cu -- up to 128 rows per launch on the strip-major 2-bit weights: widened to bytes inside the kernel,
+// tcgen05 int8 MMAs with the weights as the A operand.  Up to kWidenMaxViews weight matrices that share the input
+// rows (and K) run in one launch.  `planes` holds gemm_widen_scratch_bytes(M, K) bytes: the plane-major codes,
+// written by the row quantiser itself (plane_ld = gemm_widen_plane_ld(K)) or, when `q` (row-major codes) is given,
+// by a permutation pass inside the launcher.
+constexpr int kWidenMaxViews = 8;
+struct WidenView {
+    const void* strips;
+    const float* magnitude;
+    const float* bias;
+    float* y;               // [M, N] row-major
+    float weight_scale;
+    int N;
+    int squared_relu;       // y = max(y, 0)^2 after the affine epilogue
+};
 bool gemm_widen_supported(int M, int K, int N);
+int gemm_widen_plane_ld(int K);
 size_t gemm_widen_scratch_bytes(int M, int K);
-cudaError_t launch_gemm_widen(const int8_t* q, int8_t* qw_scratch, const float* act_scales, const int32_t* q_sums,
-                              const void* strips, float weight_scale, const float* magnitude, const float* bias,
-                              int M, int K, int N, float* y, cudaStream_t stream);
+cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q, int8_t* planes, const float* act_scales,
+                              const int32_t* q_sums, int M, int K, cudaStream_t stream);
 
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
 // `scatter` (optional): instead of y, the epilogue writes every output tile into `count` arrays -- this GPU's and

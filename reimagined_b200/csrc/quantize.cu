@@ -212,6 +212,18 @@ quantize_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ ro
     }
 }
 
+// Plane-major codes for the widening tensor-core kernel (gemm_widen.cu): inside each block of 512 elements of a
+// row (leading dimension plane_ld, a multiple of 512), byte 4g + e of plane p (128 bytes per plane) is element
+// 16g + 4e + p.  `t` is the 4x4 byte transpose of the 16-element group at element j: its four words go to the four planes.
+__device__ __forceinline__ void store_planes(int8_t* planes, int row, int plane_ld, int j, uint4 t) {
+    const int gg = j >> 4;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(planes + static_cast<size_t>(row) * plane_ld + (gg >> 5) * 512) + (gg & 31);
+    dst[0] = t.x;
+    dst[32] = t.y;
+    dst[64] = t.z;
+    dst[96] = t.w;
+}
+
 // Register-resident variant for K % 16 == 0 and K <= 16 * G * blockDim (G <= 2, so K <= 32768): every thread keeps its
 // G groups of 16 elements in registers, so the row is read from memory exactly once and the kernel
 // is a single load -> reduce -> quantise -> store chain (what matters at decode batch sizes, where
@@ -222,7 +234,7 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
                          float q_max, int rms_mode, bool tie_away, const float* __restrict__ inv_norm_in,
                          int8_t* __restrict__ q, int8_t* __restrict__ qp, float* __restrict__ act_scales,
                          int32_t* __restrict__ q_sums, const int32_t* __restrict__ active_rows,
-                         int qp_rows, QuantSegments seg) {
+                         int qp_rows, QuantSegments seg, int plane_ld) {
     __shared__ float scratch[32];
     __shared__ int sum_scratch[32];
     const int row = blockIdx.x;
@@ -309,7 +321,10 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
             }
             const uint4 natural = make_uint4(words[0], words[1], words[2], words[3]);
             if (q) *reinterpret_cast<uint4*>(q + static_cast<size_t>(row) * K + j) = natural;
-            if (qp) *reinterpret_cast<uint4*>(qp + pbase + qp_offset(prow, prows, K, j)) = transpose4x4_bytes(natural);
+            if (qp && !plane_ld) *reinterpret_cast<uint4*>(qp + pbase + qp_offset(prow, prows, K, j)) = transpose4x4_bytes(natural);
+            if (qp && plane_ld) store_planes(qp, row, plane_ld, j, transpose4x4_bytes(natural));
+        } else if (qp && j < plane_ld) {
+            store_planes(qp, row, plane_ld, j, make_uint4(0u, 0u, 0u, 0u));     // the padding up to the row's leading dimension
         }
     }
     };
@@ -496,7 +511,13 @@ __global__ void expand_i8_tail_kernel(const uint32_t* __restrict__ words, int64_
 cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M, int K, int bits,
                                  int rms_mode, int tie_mode, int8_t* q, int8_t* qp, float* act_scales,
                                  int32_t* q_sums, float* inv_norm_scratch, const int32_t* active_rows,
-                                 QuantSegments segments, cudaStream_t stream) {
+                                 QuantSegments segments, cudaStream_t stream, int plane_ld) {
+    // plane_ld != 0: qp receives the plane-major codes (leading dimension plane_ld) instead of the interleaved copy;
+    // only the register kernel writes them
+    if (plane_ld && (!qp || segments.offsets || K % 16 || K > 32768 || plane_ld % 512 || plane_ld < K || plane_ld - K >= 512 ||
+                     (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(qp) & 15) ||
+                     (q && (reinterpret_cast<uintptr_t>(q) & 15))))
+        return cudaErrorInvalidValue;
     if (rms_mode == TBL_RMS_REFERENCE_ORDER) {
         rms_reference_order_kernel<<<(M + 63) / 64, 64, 0, stream>>>(x, row_index, M, K, 1e-6f,
                                                                      inv_norm_scratch, active_rows);
@@ -540,7 +561,7 @@ cudaError_t launch_quantize_rows(const float* x, const int32_t* row_index, int M
 #define TBL_LAUNCH_REG(G)                                                                                  \
     quantize_rows_reg_kernel<G><<<M, threads, 0, stream>>>(x, row_index, K, q_max, rms_mode, away,         \
                                                            inv_norm_scratch, q, qp, act_scales, q_sums,    \
-                                                           active_rows, M, segments)
+                                                           active_rows, M, segments, plane_ld)
         if (g <= 1) TBL_LAUNCH_REG(1);
         else TBL_LAUNCH_REG(2);
 #undef TBL_LAUNCH_REG

@@ -114,6 +114,8 @@ def test_chain_with_input_norm_matches_the_single_layer_calls(cuda, port, tbl):
     (3, [48, 32, 64], True, 0),             # widths that are not multiples of 256
     (2, [1024, 512, 1024], False, 0),       # canonical words only
     (2, [1024, 512, 1024], True, 2),        # reference-order input norm
+    (48, [768, 3072, 768], True, 0),        # mid-size batch: the widening tensor-core kernel, squared ReLU in its epilogue
+    (40, [1024, 768, 512], True, 2),
 ])
 def test_chain_layer_by_layer_route(cuda, port, tbl, rows, widths, strips, rms_mode):
     import gpu_helpers as H

@@ -44,10 +44,13 @@ def test_grouped_projections_share_one_quantised_row(cuda, port, tbl, K, outs, s
 
 @pytest.mark.parametrize("rows,K,outs,strips", [(8, 768, [1536, 1536, 16, 16, 24], True), (3, 4096, [100, 2064], True),
                                                 (16, 768, [768, 1536], True), (64, 1024, [40, 17], True),
-                                                (5, 48, [3, 33], False), (2, 32768, [20], True)])
+                                                (5, 48, [3, 33], False), (2, 32768, [20], True),
+                                                (48, 768, [1536, 1568, 24], True), (64, 768, [768, 1536], True),
+                                                (33, 1280, [100, 129, 16, 300], True)])
 def test_grouped_projections_on_a_batch_of_rows(cuda, port, tbl, rows, K, outs, strips):
     """Batched decode: the same projections on several rows, one grouped call (fused quantiser when
-    rows*K <= 16384, separate quantiser kernel above that, canonical-words fallback without strips)."""
+    rows*K <= 16384, separate quantiser kernel above that -- from 33 rows on followed by one launch of the widening
+    tensor-core kernel over all the views --, canonical-words fallback without strips)."""
     import gpu_helpers as H
     rng = np.random.default_rng(rows + K + len(outs))
     x = rng.standard_normal((rows, K)).astype(np.float32)

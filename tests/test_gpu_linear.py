@@ -204,10 +204,12 @@ def test_strip_relayout_is_a_permutation(cuda, port, tbl):
 
 
 @pytest.mark.parametrize("M,N,K,rms", [(33, 136, 1536, 0), (48, 1000, 2560, 1), (64, 776, 1536, 2), (100, 300, 1024, 0),
-                                       (128, 1024, 4096, 1), (40, 129, 512, 0)])
+                                       (128, 1024, 4096, 1), (40, 129, 512, 0), (64, 3352, 768, 0), (50, 200, 1280, 2),
+                                       (128, 140, 256, 1), (200, 260, 768, 0)])
 def test_mid_batch_widening_tensor_core_path(cuda, port, tbl, M, N, K, rms):
-    """33 <= M <= 128 on the strip-major 2-bit weights with K % 512 == 0: widened in shared memory and multiplied by
-    tcgen05 MMAs, 64 rows per pass; ragged row tiles, a short last slab (K % 1024 != 0), every RMS mode."""
+    """33 <= M <= 256 on the strip-major 2-bit weights with K % 256 == 0: widened in shared memory and multiplied by
+    tcgen05 MMAs, up to 128 rows per pass; ragged row tiles, a short last slab (K % 1024 != 0), half a last k-block
+    (K % 512 == 256: the plane-major codes are zero-padded), every RMS mode."""
     import gpu_helpers as H
     w, x, mag, bias = make_case(7 * M + N + K, N, K, M, affine=True, xscale=3.0)
     words, scale, *_ = port.pack_weights(w)
