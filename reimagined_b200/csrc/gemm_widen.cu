@@ -30,7 +30,9 @@
 //              warps run the epilogue (tcgen05.ld, exact recombination, two-scale epilogue, coalesced stores
 //              along n)
 // Every wait is bounded: on a timeout the role records the status word and falls through to the common exit,
-// where TMEM is released.
+// where TMEM is released.  The kernel is launched as a programmatic dependent of the kernel before it (the row
+// quantiser): weights are fetched and widened while that kernel still runs; only the activation producer and the
+// epilogue wait for it.
 //
 // Measured (16384 x 16384, B200): 41 us per pass for any batch up to 64 rows (tensor pipe 42 % busy).  An MMA of this shape
 // lasts 46 cycles for any N <= 64, so the 96 KB of widened planes that fit hold only ~1 100 cycles of tensor work,
@@ -195,6 +197,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             int hs = 0;
             bool alive = true;
             const uint32_t tx = 2u * n_pad * 128u;
+            griddep_wait();                          // the codes come from the kernel before this one
             for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
                 for (int kh = 0; kh < 2 * p.kblocks; ++kh, ++hs) {
                     const int s = hs % b_stages;
@@ -309,6 +312,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
+            griddep_wait();                          // scales and code sums come from the kernel before this one; y is written below
             const WidenTiles& vw = p.view[view_of(p, tile)];
             const int n = (tile - vw.tile0) * 128 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -408,9 +412,19 @@ cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int grid = p.tiles < kNumSmW ? p.tiles : kNumSmW;
-    gemm_widen_kernel<<<grid, kWidenThreads, smem, stream>>>(mq, p);
+    // Programmatic dependent launch: everything up to the first MMA -- TMEM allocation, the first weight slabs, the
+    // first widened planes -- depends on nothing the kernel before this one writes, so it may run beside that
+    // kernel's tail (the row quantiser releases its dependents at once); the activation producer and the epilogue
+    // wait for its completion (griddep_wait).
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kWidenThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_widen_kernel, mq, p);
     note_launch();
-    return cudaGetLastError();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 }  // namespace tbl
