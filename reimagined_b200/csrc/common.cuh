@@ -73,14 +73,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
-// while the kernel before it in the stream still runs, once every CTA of that kernel has called
-// griddep_launch_dependents() (or exited).  It must call griddep_wait() before it touches anything the earlier
-// kernel writes, and before its own first global write: the wait returns when the earlier kernel has completed and
-// its memory operations are visible.  Both are no-ops in a launch without the attribute.
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // 1-D bulk copy global -> shared (TMA engine), completion signalled on `bar` as bytes.
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -144,8 +136,10 @@ __device__ __forceinline__ float round_tie(float v, bool away) {
 }
 
 // Programmatic dependent launch (both are no-ops in a kernel that was launched without the attribute).
-// launch_dependents: the next kernel of the stream may be scheduled once every CTA has issued it.
-// wait: blocks until the preceding kernel has completed and its writes are visible.
+// launch_dependents: the next kernel of the stream, if it was launched with the programmatic-stream-serialization
+// attribute, may be scheduled once every CTA of this one has issued it (or exited).
+// wait: blocks until the preceding kernel has completed and its writes are visible; a dependent kernel calls it
+// before it touches anything that kernel writes and before its own first global write.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -303,6 +303,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return t;
 }
 
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = scratch[0];
+    for (int w = 1; w < nw; ++w) t = fmaxf(t, scratch[w]);
+    return t;
+}
+
+// Where a glue kernel leaves the rows it produces as 8-bit codes for the widening tensor-core GEMM
+// (gemm_widen.cu) instead of fp32 values, which saves the stand-alone row quantiser between the two: per row the
+// absmax, scale = 127 / (absmax + 1e-8), code = round-half-even(v * scale) -- the arithmetic of
+// quantize_rows_reg_kernel (quantize.cu) for 8 bits without an input norm, so the codes are the same bit for bit.
+// Plane-major layout: inside each block of 512 codes of a row (leading dimension ld, a multiple of 512, zero past
+// the row's width), byte 4g + e of plane p (128 bytes per plane) is element 16g + 4e + p.
+struct RowCodes {
+    int8_t* codes;         // null: the kernel writes fp32 as usual
+    float* act_scales;     // [rows] (absmax + 1e-8) / 127
+    int32_t* q_sums;       // [rows] sum of the row's codes
+    int ld;
+};
+
+__device__ __forceinline__ size_t plane_offset(int row, int ld, int k) {
+    return static_cast<size_t>(row) * ld + (k >> 9) * 512 + (k & 3) * 128 + ((k >> 4) & 31) * 4 + ((k >> 2) & 3);
+}
+
 // hidden_out = x + (a*ga [+ b*gb]) (or x itself when a == null; x = table[ids[row]] when ids != null), and up to two
 // RMSNorm x weight views of it (eps shared): out1 = rmsnorm(h)*w1, out2 = rmsnorm(h)*w2.  Replaces the residual
 // add that closes one block and the norm(s) that open the next (OXN/nsos/src/jamba.cpp:3175-3179, 3195-3251).
@@ -311,10 +340,13 @@ residual_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ id
                      int vocab, const float* __restrict__ a, const float* __restrict__ ga, const float* __restrict__ b,
                      const float* __restrict__ gb, int D, float eps, const float* __restrict__ w1,
                      const float* __restrict__ w2, float* __restrict__ hidden_out, float* __restrict__ trace,
-                     float* __restrict__ out1, float* __restrict__ out2) {
+                     float* __restrict__ out1, float* __restrict__ out2, RowCodes codes1) {
     extern __shared__ float sm[];
     float* row = sm;                 // [D]
     float* scratch = sm + D;         // [32]
+    __shared__ int code_sum;
+    // a dependent launch (the widening GEMM behind out1's codes) may fetch and widen its first weights meanwhile
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const float* src = x ? x + static_cast<size_t>(r) * D : nullptr;
     bool id_ok = true;
@@ -339,10 +371,32 @@ residual_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ id
     }
     const float total = block_sum(ss, scratch);
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(D)), eps)));
+    float mx = 0.0f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         const float n = __fmul_rn(row[d], inv);
-        if (out1) out1[static_cast<size_t>(r) * D + d] = w1 ? __fmul_rn(n, __ldg(w1 + d)) : n;
+        const float v1 = w1 ? __fmul_rn(n, __ldg(w1 + d)) : n;
+        if (out1) out1[static_cast<size_t>(r) * D + d] = v1;
         if (out2) out2[static_cast<size_t>(r) * D + d] = w2 ? __fmul_rn(n, __ldg(w2 + d)) : n;
+        if (codes1.codes) { row[d] = v1; mx = fmaxf(mx, fabsf(v1)); }     // the thread's own elements: no barrier needed
+    }
+    if (!codes1.codes) return;
+    if (threadIdx.x == 0) code_sum = 0;
+    mx = block_max(mx, scratch);
+    const float denom = __fadd_rn(mx, 1e-8f);
+    const float scale = __fdiv_rn(127.0f, denom);
+    int local = 0;
+    for (int d = threadIdx.x; d < codes1.ld; d += blockDim.x) {
+        int c = 0;
+        if (d < D) c = round_code(__fmul_rn(row[d], scale), false);
+        local += static_cast<int8_t>(c);
+        codes1.codes[plane_offset(r, codes1.ld, d)] = static_cast<int8_t>(c);
+    }
+    local = __reduce_add_sync(0xffffffffu, local);
+    if ((threadIdx.x & 31) == 0 && local != 0) atomicAdd(&code_sum, local);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        codes1.act_scales[r] = __fdiv_rn(denom, 127.0f);
+        codes1.q_sums[r] = code_sum;
     }
 }
 
@@ -519,8 +573,10 @@ mamba_mix_cluster_kernel(const float* __restrict__ xv, const float* __restrict__
                          const float* __restrict__ Cv, const float* __restrict__ dt, const float* __restrict__ conv_w,
                          const float* __restrict__ conv_b, const float* __restrict__ A_log, const float* __restrict__ Dp,
                          const float* __restrict__ norm_w, float* __restrict__ ring, float* __restrict__ state,
-                         int n_heads, int d_head, int n_groups, int K, float eps, float* __restrict__ out) {
+                         int n_heads, int d_head, int n_groups, int K, float eps, float* __restrict__ out, RowCodes codes) {
     namespace cg = cooperative_groups;
+    // a dependent launch (the widening GEMM of the out projection) may fetch and widen its first weights meanwhile
+    pdl_launch_dependents();
     cg::cluster_group cluster = cg::this_cluster();
     constexpr int N = 16, kMaxK = 4;
     extern __shared__ float sm[];
@@ -535,6 +591,8 @@ mamba_mix_cluster_kernel(const float* __restrict__ xv, const float* __restrict__
     float* decay_s = delta_s + n_heads;       // [n_heads]
     float* scratch = decay_s + n_heads;       // [32]
     float* parts = scratch + 32;              // [kMixCluster], rank 0's copy is the one used
+    float* maxes = parts + kMixCluster;       // [kMixCluster], likewise: the CTAs' absmax of the outputs
+    int* code_sums = reinterpret_cast<int*>(maxes + kMixCluster);   // [kMixCluster], likewise: the CTAs' sums of codes
     const int taps = K - 1;
     float* rr = ring + static_cast<size_t>(r) * (taps > 0 ? taps : 1) * conv_dim;
     // per-head step sizes and decays, by the last warp while the others start on the convolution
@@ -624,11 +682,47 @@ mamba_mix_cluster_kernel(const float* __restrict__ xv, const float* __restrict__
     float total = 0.0f;
     for (int k = 0; k < kMixCluster; ++k) total += all[k];        // fixed order: the same sum in every CTA
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(d_inner)), eps)));
+    float o = 0.0f;
     if (idx < n_own) {
         const float n = __fmul_rn(gv, inv);
-        out[static_cast<size_t>(r) * d_inner + chan] = norm_w ? __fmul_rn(n, __ldg(norm_w + chan)) : n;
+        o = norm_w ? __fmul_rn(n, __ldg(norm_w + chan)) : n;
+        if (!codes.codes) out[static_cast<size_t>(r) * d_inner + chan] = o;
     }
-    cluster.sync();          // rank 0's shared memory stays alive until every CTA has read the partial sums
+    if (codes.codes) {
+        // the row as 8-bit codes for the out projection: absmax over the cluster, then every thread rounds its channel
+        const float cta_max = block_max(fabsf(o), scratch);
+        if (threadIdx.x == 0) cluster.map_shared_rank(maxes, 0)[rank] = cta_max;
+        cluster.sync();
+        const float* all_max = cluster.map_shared_rank(maxes, 0);
+        float mx = 0.0f;
+        for (int k = 0; k < kMixCluster; ++k) mx = fmaxf(mx, all_max[k]);
+        const float denom = __fadd_rn(mx, 1e-8f);
+        const float scale = __fdiv_rn(127.0f, denom);
+        int c = 0;
+        if (idx < n_own) {
+            c = static_cast<int8_t>(round_code(__fmul_rn(o, scale), false));
+            codes.codes[plane_offset(r, codes.ld, chan)] = static_cast<int8_t>(c);
+        }
+        if (rank == kMixCluster - 1)            // the padding up to the leading dimension
+            for (int k = d_inner + idx; k < codes.ld; k += kMixThreads) codes.codes[plane_offset(r, codes.ld, k)] = 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        __syncthreads();                        // block_max's readers are done with scratch
+        int* iscratch = reinterpret_cast<int*>(scratch);
+        if ((threadIdx.x & 31) == 0) iscratch[threadIdx.x >> 5] = c;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < kMixThreads / 32; ++w) t += iscratch[w];
+            cluster.map_shared_rank(code_sums, 0)[rank] = t;
+            if (rank == 0) codes.act_scales[r] = __fdiv_rn(denom, 127.0f);
+        }
+    }
+    cluster.sync();          // rank 0's shared memory stays alive until every CTA has read (and written) what it exchanges there
+    if (codes.codes && rank == 0 && threadIdx.x == 0) {
+        int t = 0;
+        for (int k = 0; k < kMixCluster; ++k) t += code_sums[k];
+        codes.q_sums[r] = t;
+    }
 }
 
 // ---- out = x + (a * ga [+ b * gb]); ga == null: out = x + a ----------------------------------------------------
@@ -722,6 +816,10 @@ int check_model(const tbl_decode_model* m, int batch, int capacity) {
 struct Scratch {
     float *hidden[2], *core, *attn_in, *proj, *xbc, *y, *gated, *mamba_out, *qkv, *heads, *attn_out, *res, *ffn_in, *ffn_mid, *ffn_out;
     void* lin;
+    // rows that a glue kernel hands to the widening GEMM as 8-bit codes (RowCodes), with their scales and code sums
+    int8_t* codes;
+    float* code_scales;
+    int32_t* code_sums;
     size_t lin_bytes, proj_stride, qkv_stride, bytes;
 };
 
@@ -768,6 +866,11 @@ Scratch carve_scratch(const tbl_decode_model& m, int batch, void* base) {
     S.lin = p + off;
     S.lin_bytes = round_up(lin, 256);
     off += S.lin_bytes;
+    const int widest = max_inner > D ? max_inner : D;
+    S.codes = reinterpret_cast<int8_t*>(p + off);
+    off += round_up(static_cast<size_t>(batch) * gemm_widen_plane_ld(widest), 256);
+    S.code_scales = take(batch);
+    S.code_sums = reinterpret_cast<int32_t*>(take(batch));
     S.bytes = off;
     return S;
 }
@@ -911,10 +1014,33 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
     // two norms of the sum; with ids: x is the embedding row
     auto residual_norm = [&](const float* x, const int32_t* ids, const float* a, const float* ga, const float* b2,
                              const float* gb, float eps, const float* w1, const float* w2, float* hidden_out, float* trace,
-                             float* out1, float* out2) {
+                             float* out1, float* out2, RowCodes codes1 = RowCodes{}) {
         residual_norm_kernel<<<B, kFusedThreads, sizeof(float) * (D + 32), st>>>(x, ids, m.embedding, m.vocab, a, ga, b2, gb, D, eps,
-                                                                                 w1, w2, hidden_out, trace, out1, out2);
+                                                                                 w1, w2, hidden_out, trace, out1, out2, codes1);
         return launched();
+    };
+    // Mid-size batches (the widening GEMM's range): the kernel that produces a projection's input rows also
+    // quantises them (RowCodes), and the projections run straight on the codes -- no stand-alone quantiser launch.
+    const bool code_rows = B > 32 && B <= 64;
+    auto takes_codes = [&](const tbl_linear_view* v, int count) {
+        if (!code_rows || count > kWidenMaxViews) return false;
+        for (int g = 0; g < count; ++g) {
+            if (!v[g].strips || (reinterpret_cast<uintptr_t>(v[g].strips) & 15) || v[g].rms_input || v[g].activation_bits != 8 ||
+                v[g].inputs != v[0].inputs || !gemm_widen_supported(B, v[g].inputs, v[g].outputs))
+                return false;
+        }
+        return true;
+    };
+    auto row_codes = [&](int K) { return RowCodes{S.codes, S.code_scales, S.code_sums, gemm_widen_plane_ld(K)}; };
+    auto widen_on_codes = [&](const tbl_linear_view* v, int count, float* out, size_t stride) {
+        WidenView wv[kWidenMaxViews];
+        for (int g = 0; g < count; ++g) {
+            wv[g] = WidenView{};
+            wv[g].strips = v[g].strips; wv[g].magnitude = v[g].magnitude; wv[g].bias = v[g].bias;
+            wv[g].y = out + g * stride; wv[g].weight_scale = v[g].weight_scale; wv[g].N = v[g].outputs;
+        }
+        return launch_gemm_widen(wv, count, nullptr, S.codes, S.code_scales, S.code_sums, B, v[0].inputs, st) == cudaSuccess
+                   ? TBL_OK : TBL_ERR_CUDA;
     };
 
     // The residual add that ends a block is carried as "pending" and applied by the kernel that opens the next
@@ -948,10 +1074,13 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
             else if (rc != TBL_ERR_UNSUPPORTED) return rc;
         }
         if (!folded) {
+            const bool coded = takes_codes(proj, 5) && proj[0].inputs == D;
             if ((rc = residual_norm(pend.x, pend.ids, pend.a, pend.ga, pend.b, pend.gb, b.core_norm_eps, b.core_norm_w,
-                                    b.hybrid ? b.attn_norm_w : nullptr, h, trace, S.core, b.hybrid ? S.attn_in : nullptr)) != TBL_OK)
+                                    b.hybrid ? b.attn_norm_w : nullptr, h, trace, coded ? nullptr : S.core,
+                                    b.hybrid ? S.attn_in : nullptr, coded ? row_codes(D) : RowCodes{})) != TBL_OK)
                 return rc;
-            if ((rc = group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK) return rc;
+            if ((rc = coded ? widen_on_codes(proj, 5, S.proj, S.proj_stride) : group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK)
+                return rc;
         }
         // conv step + SSD step + gated norm in one kernel, then the out projection
         const int GS = mm.n_groups * mm.d_state, conv_dim = mm.d_inner + 2 * GS;
@@ -967,12 +1096,14 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
             }
         }
         const int per_cta = (mm.d_inner + kMixCluster - 1) / kMixCluster;
-        if (mm.d_state == 16 && mm.conv_kernel >= 1 && mm.conv_kernel <= 4 && per_cta + 2 * GS <= kMixThreads) {
+        const bool clustered = mm.d_state == 16 && mm.conv_kernel >= 1 && mm.conv_kernel <= 4 && per_cta + 2 * GS <= kMixThreads;
+        const bool out_coded = clustered && takes_codes(&mm.out, 1) && mm.out.inputs == mm.d_inner;
+        if (clustered) {
             // a sequence's channels over a cluster of 8 CTAs
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(static_cast<unsigned>(kMixCluster) * B);
             cfg.blockDim = dim3(kMixThreads);
-            cfg.dynamicSmemBytes = sizeof(float) * (per_cta + 2 * GS + 2 * mm.n_heads + 32 + kMixCluster);
+            cfg.dynamicSmemBytes = sizeof(float) * (per_cta + 2 * GS + 2 * mm.n_heads + 32 + 3 * kMixCluster);
             cfg.stream = st;
             cudaLaunchAttribute attr{};
             attr.id = cudaLaunchAttributeClusterDimension;
@@ -985,7 +1116,7 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                                    static_cast<const float*>(S.proj + 3 * S.proj_stride),
                                    static_cast<const float*>(S.proj + 4 * S.proj_stride), mm.conv_w, mm.conv_b, mm.A_log, mm.D,
                                    mm.norm_w, state.block[i].ring, state.block[i].ssm, mm.n_heads, mm.d_head, mm.n_groups,
-                                   mm.conv_kernel, mm.norm_eps, S.gated) != cudaSuccess)
+                                   mm.conv_kernel, mm.norm_eps, S.gated, out_coded ? row_codes(mm.d_inner) : RowCodes{}) != cudaSuccess)
                 return TBL_ERR_CUDA;
         } else {
             mamba_mix_kernel<<<B, kFusedThreads, mix_smem, st>>>(
@@ -994,7 +1125,7 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                 mm.d_state, mm.n_groups, mm.conv_kernel, mm.norm_eps, S.gated);
         }
         if ((rc = launched()) != TBL_OK) return rc;
-        if ((rc = linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
+        if ((rc = out_coded ? widen_on_codes(&mm.out, 1, S.mamba_out, 0) : linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
         if (!b.hybrid) {
             pend = Pending{h, nullptr, S.mamba_out, nullptr, nullptr, nullptr};
             cur ^= 1;

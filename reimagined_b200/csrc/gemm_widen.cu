@@ -197,7 +197,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             int hs = 0;
             bool alive = true;
             const uint32_t tx = 2u * n_pad * 128u;
-            griddep_wait();                          // the codes come from the kernel before this one
+            pdl_wait();                          // the codes come from the kernel before this one
             for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
                 for (int kh = 0; kh < 2 * p.kblocks; ++kh, ++hs) {
                     const int s = hs % b_stages;
@@ -312,7 +312,7 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
-            griddep_wait();                          // scales and code sums come from the kernel before this one; y is written below
+            pdl_wait();                          // scales and code sums come from the kernel before this one; y is written below
             const WidenTiles& vw = p.view[view_of(p, tile)];
             const int n = (tile - vw.tile0) * 128 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -415,7 +415,7 @@ cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q
     // Programmatic dependent launch: everything up to the first MMA -- TMEM allocation, the first weight slabs, the
     // first widened planes -- depends on nothing the kernel before this one writes, so it may run beside that
     // kernel's tail (the row quantiser releases its dependents at once); the activation producer and the epilogue
-    // wait for its completion (griddep_wait).
+    // wait for its completion (pdl_wait).
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kWidenThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -239,7 +239,7 @@ quantize_rows_reg_kernel(const float* __restrict__ x, const int32_t* __restrict_
     __shared__ int sum_scratch[32];
     // a dependent launch (the widening GEMM) may start its prologue and its weight stream now; it waits for this
     // kernel's completion before it reads the codes
-    griddep_launch_dependents();
+    pdl_launch_dependents();
     const int row = blockIdx.x;
     if (active_rows && row >= *active_rows) return;
     const int src = row_index ? row_index[row] : row;
