@@ -315,21 +315,27 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return t;
 }
 
-// Where a glue kernel leaves the rows it produces as 8-bit codes for the widening tensor-core GEMM
-// (gemm_widen.cu) instead of fp32 values, which saves the stand-alone row quantiser between the two: per row the
+// Where a glue kernel leaves the rows it produces as 8-bit codes for the GEMM behind it (the widening tensor-core
+// kernel, gemm_widen.cu, or the tiled strip GEMV, gemv_strip.cu) instead of fp32 values, which saves the stand-alone row quantiser between the two: per row the
 // absmax, scale = 127 / (absmax + 1e-8), code = round-half-even(v * scale) -- the arithmetic of
 // quantize_rows_reg_kernel (quantize.cu) for 8 bits without an input norm, so the codes are the same bit for bit.
-// Plane-major layout: inside each block of 512 codes of a row (leading dimension ld, a multiple of 512, zero past
-// the row's width), byte 4g + e of plane p (128 bytes per plane) is element 16g + 4e + p.
+// Two layouts, after the kernel that reads them:
+//   tile_rows == 0  plane-major (widening GEMM): inside each block of 512 codes of a row (leading dimension ld, a
+//                   multiple of 512, zero past the row's width), byte 4g + e of plane p (128 bytes per plane) is
+//                   element 16g + 4e + p;
+//   tile_rows > 0   the interleaved activation tiles of the strip GEMV (qp_offset) for a batch of tile_rows rows:
+//                   every 16-element group is stored as its 4x4 byte transpose (ld = the row's width).
 struct RowCodes {
     int8_t* codes;         // null: the kernel writes fp32 as usual
     float* act_scales;     // [rows] (absmax + 1e-8) / 127
     int32_t* q_sums;       // [rows] sum of the row's codes
     int ld;
+    int tile_rows;
 };
 
-__device__ __forceinline__ size_t plane_offset(int row, int ld, int k) {
-    return static_cast<size_t>(row) * ld + (k >> 9) * 512 + (k & 3) * 128 + ((k >> 4) & 31) * 4 + ((k >> 2) & 3);
+__device__ __forceinline__ size_t code_offset(const RowCodes& c, int row, int k) {
+    if (c.tile_rows > 0) return qp_offset(row, c.tile_rows, c.ld, k & ~15) + (k & 3) * 4 + ((k >> 2) & 3);
+    return static_cast<size_t>(row) * c.ld + (k >> 9) * 512 + (k & 3) * 128 + ((k >> 4) & 31) * 4 + ((k >> 2) & 3);
 }
 
 // hidden_out = x + (a*ga [+ b*gb]) (or x itself when a == null; x = table[ids[row]] when ids != null), and up to two
@@ -389,7 +395,7 @@ residual_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ id
         int c = 0;
         if (d < D) c = round_code(__fmul_rn(row[d], scale), false);
         local += static_cast<int8_t>(c);
-        codes1.codes[plane_offset(r, codes1.ld, d)] = static_cast<int8_t>(c);
+        codes1.codes[code_offset(codes1, r, d)] = static_cast<int8_t>(c);
     }
     local = __reduce_add_sync(0xffffffffu, local);
     if ((threadIdx.x & 31) == 0 && local != 0) atomicAdd(&code_sum, local);
@@ -701,10 +707,10 @@ mamba_mix_cluster_kernel(const float* __restrict__ xv, const float* __restrict__
         int c = 0;
         if (idx < n_own) {
             c = static_cast<int8_t>(round_code(__fmul_rn(o, scale), false));
-            codes.codes[plane_offset(r, codes.ld, chan)] = static_cast<int8_t>(c);
+            codes.codes[code_offset(codes, r, chan)] = static_cast<int8_t>(c);
         }
         if (rank == kMixCluster - 1)            // the padding up to the leading dimension
-            for (int k = d_inner + idx; k < codes.ld; k += kMixThreads) codes.codes[plane_offset(r, codes.ld, k)] = 0;
+            for (int k = d_inner + idx; k < codes.ld; k += kMixThreads) codes.codes[code_offset(codes, r, k)] = 0;
         c = __reduce_add_sync(0xffffffffu, c);
         __syncthreads();                        // block_max's readers are done with scratch
         int* iscratch = reinterpret_cast<int*>(scratch);
@@ -1019,28 +1025,48 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                                                                                  w1, w2, hidden_out, trace, out1, out2, codes1);
         return launched();
     };
-    // Mid-size batches (the widening GEMM's range): the kernel that produces a projection's input rows also
-    // quantises them (RowCodes), and the projections run straight on the codes -- no stand-alone quantiser launch.
-    const bool code_rows = B > 32 && B <= 64;
+    // Batches past the fused-prologue GEMV's range: the kernel that produces a projection's input rows also quantises
+    // them (RowCodes), and the projections run straight on the codes -- no stand-alone quantiser launch.  Up to 32
+    // rows the codes go to the tiled strip GEMV, from 33 to 64 rows to the widening tensor-core GEMM.
+    const bool fold = B <= gemv_strip_fused_rows(D);
+    const bool code_widen = B > 32 && B <= 64;
+    const bool code_strip = !fold && B <= 32;
     auto takes_codes = [&](const tbl_linear_view* v, int count) {
-        if (!code_rows || count > kWidenMaxViews) return false;
+        if (!(code_widen || code_strip) || count > (code_widen ? kWidenMaxViews : TBL_MAX_GROUPS)) return false;
         for (int g = 0; g < count; ++g) {
             if (!v[g].strips || (reinterpret_cast<uintptr_t>(v[g].strips) & 15) || v[g].rms_input || v[g].activation_bits != 8 ||
-                v[g].inputs != v[0].inputs || !gemm_widen_supported(B, v[g].inputs, v[g].outputs))
+                v[g].inputs != v[0].inputs)
                 return false;
+            if (code_widen ? !gemm_widen_supported(B, v[g].inputs, v[g].outputs) : !gemv_strip_supported(v[g].inputs)) return false;
         }
         return true;
     };
-    auto row_codes = [&](int K) { return RowCodes{S.codes, S.code_scales, S.code_sums, gemm_widen_plane_ld(K)}; };
-    auto widen_on_codes = [&](const tbl_linear_view* v, int count, float* out, size_t stride) {
-        WidenView wv[kWidenMaxViews];
-        for (int g = 0; g < count; ++g) {
-            wv[g] = WidenView{};
-            wv[g].strips = v[g].strips; wv[g].magnitude = v[g].magnitude; wv[g].bias = v[g].bias;
-            wv[g].y = out + g * stride; wv[g].weight_scale = v[g].weight_scale; wv[g].N = v[g].outputs;
+    auto row_codes = [&](int K) {
+        return RowCodes{S.codes, S.code_scales, S.code_sums, code_widen ? gemm_widen_plane_ld(K) : K, code_widen ? 0 : B};
+    };
+    auto gemm_on_codes = [&](const tbl_linear_view* v, int count, float* out, size_t stride) {
+        cudaError_t e;
+        if (code_widen) {
+            WidenView wv[kWidenMaxViews];
+            for (int g = 0; g < count; ++g) {
+                wv[g] = WidenView{};
+                wv[g].strips = v[g].strips; wv[g].magnitude = v[g].magnitude; wv[g].bias = v[g].bias;
+                wv[g].y = out + g * stride; wv[g].weight_scale = v[g].weight_scale; wv[g].N = v[g].outputs;
+            }
+            e = launch_gemm_widen(wv, count, nullptr, S.codes, S.code_scales, S.code_sums, B, v[0].inputs, st);
+        } else {
+            StripProblem pr[TBL_MAX_GROUPS];
+            for (int g = 0; g < count; ++g) {
+                pr[g] = StripProblem{};
+                pr[g].strips = static_cast<const uint8_t*>(v[g].strips); pr[g].qp = S.codes;
+                pr[g].act_scales = S.code_scales; pr[g].q_sums = S.code_sums;
+                pr[g].magnitude = v[g].magnitude; pr[g].bias = v[g].bias; pr[g].y = out + g * stride;
+                pr[g].weight_scale = v[g].weight_scale; pr[g].rows = B; pr[g].N = v[g].outputs; pr[g].K = v[g].inputs;
+                pr[g].ldy = v[g].outputs;
+            }
+            e = launch_gemv_strip(pr, count, st);
         }
-        return launch_gemm_widen(wv, count, nullptr, S.codes, S.code_scales, S.code_sums, B, v[0].inputs, st) == cudaSuccess
-                   ? TBL_OK : TBL_ERR_CUDA;
+        return e == cudaSuccess ? TBL_OK : TBL_ERR_CUDA;
     };
 
     // The residual add that ends a block is carried as "pending" and applied by the kernel that opens the next
@@ -1055,7 +1081,6 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         pre.norm_w = norm_w; pre.norm_eps = eps; pre.hidden_out = hidden_out; pre.trace_out = trace;
         return pre;
     };
-    const bool fold = B <= gemv_strip_fused_rows(D);
     int cur = 0;
     for (int i = 0; i < m.n_blocks; ++i) {
         const tbl_decode_block& b = m.blocks[i];
@@ -1079,7 +1104,7 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                                     b.hybrid ? b.attn_norm_w : nullptr, h, trace, coded ? nullptr : S.core,
                                     b.hybrid ? S.attn_in : nullptr, coded ? row_codes(D) : RowCodes{})) != TBL_OK)
                 return rc;
-            if ((rc = coded ? widen_on_codes(proj, 5, S.proj, S.proj_stride) : group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK)
+            if ((rc = coded ? gemm_on_codes(proj, 5, S.proj, S.proj_stride) : group(proj, 5, S.core, S.proj, S.proj_stride)) != TBL_OK)
                 return rc;
         }
         // conv step + SSD step + gated norm in one kernel, then the out projection
@@ -1125,7 +1150,7 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
                 mm.d_state, mm.n_groups, mm.conv_kernel, mm.norm_eps, S.gated);
         }
         if ((rc = launched()) != TBL_OK) return rc;
-        if ((rc = out_coded ? widen_on_codes(&mm.out, 1, S.mamba_out, 0) : linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
+        if ((rc = out_coded ? gemm_on_codes(&mm.out, 1, S.mamba_out, 0) : linear(mm.out, S.gated, S.mamba_out)) != TBL_OK) return rc;
         if (!b.hybrid) {
             pend = Pending{h, nullptr, S.mamba_out, nullptr, nullptr, nullptr};
             cur ^= 1;
