@@ -154,7 +154,7 @@ int tbl_gemm(const int8_t* q_dev, const float* act_scales_dev, const int8_t* w_i
 size_t tbl_linear_workspace_bytes(int M, int K, int N);
 
 /* x fp32 [M,K] (device) -> y fp32 [M,N] (device): [RMSNorm] -> quantise -> ternary GEMV
- * (M <= 32 on the strip copy; 33 <= M <= 256 with K % 512 == 0 on the strip copy too, widened to
+ * (M <= 32 on the strip copy; 33 <= M <= 256 with K % 256 == 0 on the strip copy too, widened to
  * bytes inside a tcgen05 kernel, so batches up to 256 rows need no int8 copy) or tcgen05 GEMM
  * (M > 64 when w_i8_dev != NULL) -> two-scale epilogue [* magnitude] [+ bias].  strips_dev /
  * w_i8_dev may be NULL: then the call runs on what it is given (canonical words alone serve
