@@ -479,8 +479,9 @@ MoeWorkspace carve_moe(void* base, int rows, int dim, int hidden_dim, int expert
     w.lists.total = reinterpret_cast<int32_t*>(take(sizeof(int32_t)));
     w.lists.slot_row = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * capacity));
     w.lists.slot_of = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * static_cast<size_t>(rows) * experts));
-    w.q1 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * dim));
-    w.q2 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * hidden_dim));
+    // (rows padded to 512 codes: the plane-major layout of the widening GEMM)
+    w.q1 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * round_up(static_cast<size_t>(dim), 512)));
+    w.q2 = reinterpret_cast<int8_t*>(take(static_cast<size_t>(capacity) * round_up(static_cast<size_t>(hidden_dim), 512)));
     w.scales1 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
     w.sums1 = reinterpret_cast<int32_t*>(take(sizeof(int32_t) * capacity));
     w.inv1 = reinterpret_cast<float*>(take(sizeof(float) * capacity));
@@ -801,6 +802,32 @@ int tbl_moe_forward(const tbl_linear_view* views_host, const float* routing_dev,
     }
     const bool mma1 = all_have_strips(views_host, experts);
     const bool mma2 = all_have_strips(views_host + experts, experts);
+    // enough rows per expert for the widening tensor-core kernel on the 2-bit weights: one grouped launch per stage,
+    // every expert's rows in passes of 128 by its device-side count
+    if (mma1 && mma2 && capacity >= 16 * experts && experts <= kWidenMaxViews && dim % 256 == 0 && hidden_dim % 256 == 0 &&
+        dim <= 32768 && hidden_dim <= 32768) {
+        const int rows_cap = rows;                      // a row reaches an expert at most once
+        auto stage = [&](const tbl_linear_view* v, const int8_t* planes, const float* scales, const int32_t* sums, int K,
+                         float* y, int squared) {
+            WidenView wv[kWidenMaxViews];
+            for (int x = 0; x < experts; ++x) {
+                wv[x] = WidenView{};
+                wv[x].strips = v[x].strips; wv[x].magnitude = v[x].magnitude; wv[x].bias = v[x].bias; wv[x].y = y;
+                wv[x].weight_scale = v[x].weight_scale; wv[x].N = v[x].outputs; wv[x].squared_relu = squared;
+            }
+            return launch_gemm_widen(wv, experts, nullptr, const_cast<int8_t*>(planes), scales, sums, rows_cap, K, st,
+                                     w.lists.counts, w.lists.offsets, capacity);
+        };
+        e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, nullptr, w.q1, w.scales1,
+                                 w.sums1, w.inv1, w.lists.total, QuantSegments{}, st, gemm_widen_plane_ld(dim));
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+        if (stage(views_host, w.q1, w.scales1, w.sums1, dim, w.hidden, 1) != cudaSuccess) return TBL_ERR_CUDA;
+        e = launch_quantize_rows(w.hidden, nullptr, capacity, hidden_dim, bits, mode, tie_mode, nullptr, w.q2, w.scales2,
+                                 w.sums2, w.inv2, w.lists.total, QuantSegments{}, st, gemm_widen_plane_ld(hidden_dim));
+        if (e != cudaSuccess) return TBL_ERR_CUDA;
+        if (stage(views_host + experts, w.q2, w.scales2, w.sums2, hidden_dim, w.contrib, 0) != cudaSuccess) return TBL_ERR_CUDA;
+        return cuda_status(launch_moe_merge(routing_dev, w.contrib, w.lists.slot_of, rows, experts, dim, out_dev, st));
+    }
     e = launch_quantize_rows(x_dev, w.lists.slot_row, capacity, dim, bits, mode, tie_mode, mma1 ? nullptr : w.q1,
                              mma1 ? w.q1 : nullptr, w.scales1, w.sums1, w.inv1, w.lists.total, seg, st);
     if (e != cudaSuccess) return TBL_ERR_CUDA;

@@ -69,8 +69,10 @@ struct WidenTiles {            // one weight matrix of the launch
     float* y;
     float weight_scale;
     int N, nstrips;
-    int tile0;                 // its first tile in the launch's tile list (128 weight rows per tile)
+    int tile0;                 // its first tile in a row pass's tile list (128 weight rows per tile)
     int squared_relu;
+    const int32_t* rows_dev;   // device row count of this matrix (null: the launch's M)
+    const int32_t* offset_dev; // device index of its first row in the codes / scales / sums / y (null: 0)
 };
 
 struct WidenParams {
@@ -78,15 +80,33 @@ struct WidenParams {
     const int32_t* q_sums;
     WidenTiles view[kWidenMaxViews];
     int views;
-    int M, K, n_pad, kblocks, tiles;
+    int M, K, n_pad, kblocks;
+    int tiles;                 // row_passes x tiles_per_pass
+    int tiles_per_pass;        // weight-row tiles of all the views
     int* status;
 };
 
-// the view a tile belongs to (the views' tile ranges are consecutive)
-__device__ __forceinline__ int view_of(const WidenParams& p, int tile) {
+// One unit of work: 128 weight rows of one view times one pass of up to 128 activation rows.  The tile list is
+// pass-major (every view's first 128 rows come first), so the passes that device-side row counts leave empty are
+// at its end.
+struct WidenTile {
+    int view;
+    int wtile;                 // tile of 128 weight rows inside the view
+    int row0;                  // first activation row (index into the codes / scales / sums / y)
+    int rows;                  // activation rows of this pass; <= 0: nothing to do
+};
+
+__device__ __forceinline__ WidenTile decode_widen_tile(const WidenParams& p, int tile) {
+    const int pass = tile / p.tiles_per_pass, t = tile - pass * p.tiles_per_pass;
     int v = 0;
-    while (v + 1 < p.views && tile >= p.view[v + 1].tile0) ++v;
-    return v;
+    while (v + 1 < p.views && t >= p.view[v + 1].tile0) ++v;
+    const WidenTiles& vw = p.view[v];
+    const int total = vw.rows_dev ? __ldg(vw.rows_dev) : p.M;
+    const int base = vw.offset_dev ? __ldg(vw.offset_dev) : 0;
+    WidenTile w;
+    w.view = v; w.wtile = t - vw.tile0; w.row0 = base + pass * kMaxNpad;
+    w.rows = min(kMaxNpad, total - pass * kMaxNpad);
+    return w;
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -174,8 +194,10 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             int it = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
-                const WidenTiles& vw = p.view[view_of(p, tile)];
-                const int first = (tile - vw.tile0) * 8, cnt = min(8, vw.nstrips - first);
+                const WidenTile wt = decode_widen_tile(p, tile);
+                if (wt.rows <= 0) continue;
+                const WidenTiles& vw = p.view[wt.view];
+                const int first = wt.wtile * 8, cnt = min(8, vw.nstrips - first);
                 for (int sl = 0; sl < slabs; ++sl, ++it) {
                     const int s = it % kRawStages;
                     if (it >= kRawStages) {
@@ -199,6 +221,8 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             const uint32_t tx = 2u * n_pad * 128u;
             pdl_wait();                          // the codes come from the kernel before this one
             for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
+                const WidenTile wt = decode_widen_tile(p, tile);
+                if (wt.rows <= 0) continue;
                 for (int kh = 0; kh < 2 * p.kblocks; ++kh, ++hs) {
                     const int s = hs % b_stages;
                     if (hs >= b_stages) {
@@ -208,8 +232,9 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
                     uint8_t* dst = b_buf + s * b_stage_bytes;
                     mbar_arrive_expect_tx(&b_full[s], tx);
                     const int x0 = (kh >> 1) * kBlockK + (kh & 1) * 256;
-                    tma_load_2d(dst, &map_q, x0, 0, &b_full[s]);
-                    tma_load_2d(dst + n_pad * 128, &map_q, x0 + 128, 0, &b_full[s]);
+                    // rows past the pass's own (another view's, or past the end: zero-filled) are multiplied and ignored
+                    tma_load_2d(dst, &map_q, x0, wt.row0, &b_full[s]);
+                    tma_load_2d(dst + n_pad * 128, &map_q, x0 + 128, wt.row0, &b_full[s]);
                 }
             }
         }
@@ -225,11 +250,13 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             const uint32_t b_plane = static_cast<uint32_t>(n_pad) * 128u >> 4;
             int hs = 0, local = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x, ++local) {
+            for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
+                if (decode_widen_tile(p, tile).rows <= 0) continue;
                 if (local >= 1) {
                     alive = mbar_wait_bounded(tmem_empty, (local - 1) & 1, p.status);
                     if (!alive) break;
                 }
+                ++local;
                 tc_fence_after();
                 for (int kh = 0; kh < 2 * p.kblocks; ++kh, ++hs) {
                     const int sa = hs % kAStages, sb = hs % b_stages;
@@ -264,7 +291,9 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
         const int nblk = p.K >> 8;
         int it = 0, sit = 0, local = 0;             // k-blocks and slabs consumed so far
         bool alive = true;
-        for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; alive && tile < p.tiles; tile += gridDim.x) {
+            const WidenTile wt = decode_widen_tile(p, tile);
+            if (wt.rows <= 0) continue;
             for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                 const int sl = kb >> 1, sbs = min(4, nblk - 4 * sl);
                 const int s = sit % kRawStages;
@@ -313,8 +342,9 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
             if (!alive) break;
             tc_fence_after();
             pdl_wait();                          // scales and code sums come from the kernel before this one; y is written below
-            const WidenTiles& vw = p.view[view_of(p, tile)];
-            const int n = (tile - vw.tile0) * 128 + quarter * 32 + lane;
+            ++local;
+            const WidenTiles& vw = p.view[wt.view];
+            const int n = wt.wtile * 128 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             const float mag = (vw.magnitude && n < vw.N) ? __ldg(vw.magnitude + n) : 1.0f;
             const float bia = (vw.bias && n < vw.N) ? __ldg(vw.bias + n) : 0.0f;
@@ -332,15 +362,16 @@ gemm_widen_kernel(const __grid_constant__ CUtensorMap map_q, const WidenParams p
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + j;
-                    if (m < p.M) {
+                    if (m < wt.rows) {
+                        const int row = wt.row0 + m;
                         // exact: plane p's sum is a multiple of 4^p
                         const int total = static_cast<int>(d0[j]) + (static_cast<int>(d1[j]) >> 2) + (static_cast<int>(d2[j]) >> 4) +
-                                          (static_cast<int>(d3[j]) >> 6) - __ldg(p.q_sums + m);
-                        float v = __fmul_rn(static_cast<float>(total), __fmul_rn(__ldg(p.act_scales + m), wscale));
+                                          (static_cast<int>(d3[j]) >> 6) - __ldg(p.q_sums + row);
+                        float v = __fmul_rn(static_cast<float>(total), __fmul_rn(__ldg(p.act_scales + row), wscale));
                         if (has_mag) v = __fmul_rn(v, mag);
                         if (has_bias) v = __fadd_rn(v, bia);
                         if (sq) { v = fmaxf(v, 0.0f); v = __fmul_rn(v, v); }
-                        if (n < N) yv[static_cast<size_t>(m) * N + n] = v;
+                        if (n < N) yv[static_cast<size_t>(row) * N + n] = v;
                     }
                 }
             }
@@ -374,23 +405,33 @@ size_t gemm_widen_scratch_bytes(int M, int K) {
 }
 
 cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q, int8_t* planes, const float* act_scales,
-                              const int32_t* q_sums, int M, int K, cudaStream_t stream) {
-    if (!views || count < 1 || count > kWidenMaxViews || !planes) return cudaErrorInvalidValue;
+                              const int32_t* q_sums, int M, int K, cudaStream_t stream, const int32_t* rows_dev,
+                              const int32_t* offsets_dev, int total_rows) {
+    if (!views || count < 1 || count > kWidenMaxViews || !planes || M < 1) return cudaErrorInvalidValue;
+    // device-side row counts (the experts of a MoE stage): view v multiplies rows offsets_dev[v] .. + rows_dev[v] of the
+    // total_rows rows of codes, at most M of them, in passes of 128
+    const bool counted = rows_dev != nullptr;
+    if (counted ? (!offsets_dev || q || total_rows < 1) : M > kMaxNpad) return cudaErrorInvalidValue;
+    const int pass_rows = M < kMaxNpad ? M : kMaxNpad;
     const int K_pad = gemm_widen_plane_ld(K);
     WidenParams p{};
     p.act_scales = act_scales; p.q_sums = q_sums; p.M = M; p.K = K; p.views = count;
-    p.n_pad = (M + 15) & ~15;
+    p.n_pad = (pass_rows + 15) & ~15;
     p.kblocks = K_pad / kBlockK;
     int tiles = 0;
     for (int v = 0; v < count; ++v) {
-        if (!gemm_widen_supported(M, K, views[v].N) || !views[v].strips || !views[v].y) return cudaErrorInvalidValue;
+        if (!gemm_widen_supported(pass_rows, K, views[v].N) || !views[v].strips || !views[v].y) return cudaErrorInvalidValue;
         WidenTiles& t = p.view[v];
         t.strips = static_cast<const uint8_t*>(views[v].strips); t.magnitude = views[v].magnitude; t.bias = views[v].bias;
         t.y = views[v].y; t.weight_scale = views[v].weight_scale; t.N = views[v].N; t.nstrips = (views[v].N + 15) / 16;
         t.tile0 = tiles; t.squared_relu = views[v].squared_relu;
+        t.rows_dev = counted ? rows_dev + v : nullptr;
+        t.offset_dev = counted ? offsets_dev + v : nullptr;
         tiles += (views[v].N + 127) / 128;
     }
-    p.tiles = tiles;
+    p.tiles_per_pass = tiles;
+    p.tiles = tiles * ((M + kMaxNpad - 1) / kMaxNpad);
+    const int map_rows = counted ? total_rows : M;
     if (q) {
         const long long groups = static_cast<long long>(M) * (K_pad >> 4);
         const int grid = static_cast<int>((groups + 255) / 256 < 1184 ? (groups + 255) / 256 : 1184);
@@ -400,8 +441,8 @@ cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorUnknown;
     CUtensorMap mq;
-    // the plane-major codes [M rows, K_pad bytes], box 128 bytes x n_pad rows
-    if (!make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, M, K_pad, 128, p.n_pad)) return cudaErrorUnknown;
+    // the plane-major codes [rows, K_pad bytes], box 128 bytes x n_pad rows
+    if (!make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, planes, map_rows, K_pad, 128, p.n_pad)) return cudaErrorUnknown;
     const size_t smem = 1024 + kAStages * kAHalfBytes + kRawStages * kRawBytes + kBRingBytes + 512;
     static bool configured[64] = {};
     int dev = 0;

@@ -149,12 +149,12 @@ int linear_view_forward_pre(const tbl_linear_view& v, const float* x, int rows, 
 int linear_view_forward(const tbl_linear_view& v, const float* x, int rows, int rms_mode, bool squared_relu, float* y,
                         void* workspace, size_t workspace_bytes, cudaStream_t st);
 
-// gemm_widen.cu -- up to 128 rows per launch on the strip-major 2-bit weights: widened to bytes inside the kernel,
+// gemm_widen.cu -- up to 128 rows per pass on the strip-major 2-bit weights: widened to bytes inside the kernel,
 // tcgen05 int8 MMAs with the weights as the A operand.  Up to kWidenMaxViews weight matrices that share the input
 // rows (and K) run in one launch.  `planes` holds gemm_widen_scratch_bytes(M, K) bytes: the plane-major codes,
 // written by the row quantiser itself (plane_ld = gemm_widen_plane_ld(K)) or, when `q` (row-major codes) is given,
 // by a permutation pass inside the launcher.
-constexpr int kWidenMaxViews = 8;
+constexpr int kWidenMaxViews = 16;
 struct WidenView {
     const void* strips;
     const float* magnitude;
@@ -167,8 +167,12 @@ struct WidenView {
 bool gemm_widen_supported(int M, int K, int N);
 int gemm_widen_plane_ld(int K);
 size_t gemm_widen_scratch_bytes(int M, int K);
+// rows_dev / offsets_dev (device, one entry per view; optional): view v multiplies only rows offsets_dev[v] ..
+// + rows_dev[v] of the total_rows rows of codes (the experts of a MoE stage); M is then the upper bound of a view's
+// row count and may exceed 128 (passes of 128 rows inside the launch; q must be null).
 cudaError_t launch_gemm_widen(const WidenView* views, int count, const int8_t* q, int8_t* planes, const float* act_scales,
-                              const int32_t* q_sums, int M, int K, cudaStream_t stream);
+                              const int32_t* q_sums, int M, int K, cudaStream_t stream, const int32_t* rows_dev = nullptr,
+                              const int32_t* offsets_dev = nullptr, int total_rows = 0);
 
 // gemm_tcgen05.cu — M > 64, tcgen05 int8 MMA, TMEM accumulators, TMA operands.
 // `scatter` (optional): instead of y, the epilogue writes every output tile into `count` arrays -- this GPU's and

@@ -149,6 +149,30 @@ def test_moe_grouped_tensor_core_gemm_matches_oracle(cuda, port, tbl, rows, D, H
     assert H.device_status() == 0
 
 
+@pytest.mark.parametrize("rows,D,Hd,E,top_k", [(130, 256, 256, 3, 1), (300, 512, 768, 4, 2), (257, 768, 1280, 5, 3),
+                                               (64, 1024, 256, 8, 2)])
+def test_moe_widening_tensor_core_path_matches_oracle(cuda, port, tbl, rows, D, Hd, E, top_k):
+    """Views with strip-major 2-bit weights only and >= 16 routed rows per expert: both expert stages run as one
+    grouped launch of the widening tcgen05 kernel each (device-side row counts, passes of 128 rows, experts with few
+    or no rows, K % 512 == 256)."""
+    import gpu_helpers as H
+    rng = np.random.default_rng(rows * 17 + D)
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    up = (rng.standard_normal((E, Hd, D)) * 0.02).astype(np.float32)
+    down = (rng.standard_normal((E, D, Hd)) * 0.02).astype(np.float32)
+    logits = rng.standard_normal((rows, E)).astype(np.float32)
+    logits[:, E - 1] -= 4.0                      # the last expert gets (almost) no rows
+    routing = port.router_topk(logits, top_k)
+    views, keep, packed = _moe_setup(port, H, x, up, down, True)
+    want = port.moe_forward(x, routing, [p[0] for p in packed], [p[1] for p in packed], [p[2] for p in packed],
+                            [p[3] for p in packed], Hd, rms_input=1)
+    before = tbl.tbl_launch_count()
+    out = H.moe_forward(views, H.dev(routing), H.dev(x), Hd, top_k, rms_mode=2).cpu().numpy()
+    assert tbl.tbl_launch_count() - before == 8      # route, 2 x (rms, quantise, grouped widening GEMM), merge
+    assert bits_equal(out, want), f"max diff {np.abs(out - want).max()}"
+    assert H.device_status() == 0
+
+
 def test_moe_inactive_experts_are_never_read(cuda, port, tbl):
     """The reference's inactive_experts_contract (tests/gpu/test_gpu_decode_runtime.cpp:98-144): experts
     with routing weight 0 must not contribute -- here their scale and bias are NaN-poisoned."""
