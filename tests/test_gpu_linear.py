@@ -298,7 +298,7 @@ def test_reference_gemv_contract_fixture(cuda, tbl):
 
 
 def test_roundtrip_properties_at_scale(cuda, port, tbl):
-    """Size-independent checks at a BASELINE-size shape (K=N=4096): linearity in the weight scale,
+    """Size-independent checks at a benchmark-size shape (K=N=4096): linearity in the weight scale,
     zero input -> bias only, and a checksum of int32 accumulators against a row-sampled oracle."""
     import gpu_helpers as H
     N = K = 4096
