@@ -1026,11 +1026,14 @@ int tbl_decode_step(const tbl_decode_model* model, int batch, int capacity, void
         return launched();
     };
     // Batches past the fused-prologue GEMV's range: the kernel that produces a projection's input rows also quantises
-    // them (RowCodes), and the projections run straight on the codes -- no stand-alone quantiser launch.  Up to 32
-    // rows the codes go to the tiled strip GEMV, from 33 to 64 rows to the widening tensor-core GEMM.
+    // them (RowCodes), and the projections run straight on the codes -- no stand-alone quantiser launch.  Up to 16
+    // rows the codes go to the tiled strip GEMV, from 17 to 64 rows to the widening tensor-core GEMM.
     const bool fold = B <= gemv_strip_fused_rows(D);
-    const bool code_widen = B > 32 && B <= 64;
-    const bool code_strip = !fold && B <= 32;
+    // (the widening kernel's fixed cost per launch beats the strip GEMV's 8-row passes from 17 rows on at the widths of
+    // a decode step; on their own, large matrices switch at 33 rows)
+    constexpr int kCodeWidenMinRows = 16;
+    const bool code_widen = B > kCodeWidenMinRows && B <= 64;
+    const bool code_strip = !fold && B <= kCodeWidenMinRows;
     auto takes_codes = [&](const tbl_linear_view* v, int count) {
         if (!(code_widen || code_strip) || count > (code_widen ? kWidenMaxViews : TBL_MAX_GROUPS)) return false;
         for (int g = 0; g < count; ++g) {

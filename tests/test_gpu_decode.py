@@ -228,7 +228,7 @@ def test_decode_step_batch_rows_are_independent(cuda, port, tbl):
             assert rel_err(lb[r], l1[0]) <= 1e-5
 
 
-@pytest.mark.parametrize("rows", [12, 40, 64])
+@pytest.mark.parametrize("rows", [12, 24, 40, 64])
 def test_decode_step_mid_size_batches_match_single_rows(cuda, port, tbl, rows):
     """Batches that take the separate-quantiser routes (9..32 rows: tiled strip GEMV; 33..64 rows: the glue kernels
     hand 8-bit codes to the widening tensor-core GEMM) against engines of batch one on the same tokens: the rows are
