@@ -166,3 +166,18 @@ def test_new_entry_points_validate_before_touching_a_device(tbl):
     assert tbl.tbl_edge_pack_open(b"DGE1", 4, C.byref(version), C.byref(layers)) == -11
     assert tbl.tbl_status_string(-11).decode().startswith("edge pack")
     assert tbl.tbl_status_string(-12).decode().startswith("edge pack")
+
+
+def test_workspace_sizes_cover_the_plane_major_codes(tbl):
+    """Mid-size batches keep a second copy of the codes with every row padded to 512 (the widening GEMM's layout):
+    the workspace queries must account for the padding when K % 512 == 256, for the grouped call, the MoE block and
+    the single layer alike (pure host arithmetic)."""
+    for M, K in ((64, 768), (200, 1280), (33, 256), (64, 16384)):
+        padded = (K + 511) // 512 * 512
+        assert tbl.tbl_linear_workspace_bytes(M, K, 128) >= M * K + M * padded + 3 * 4 * M
+    assert tbl.tbl_grouped_rows_workspace_bytes(5, 64, 768) >= 64 * 768 + 64 * 1024
+    rows, D, Hd, E, top = 256, 768, 1280, 8, 2
+    need = rows * top * (1024 + 1536) + 4 * rows * top * (Hd + D)      # both stages' codes + hidden + contributions
+    assert tbl.tbl_moe_workspace_bytes(rows, D, Hd, E, top) >= need
+    # sizes are monotonic in the row count
+    assert tbl.tbl_linear_workspace_bytes(65, 768, 128) > tbl.tbl_linear_workspace_bytes(64, 768, 128)
